@@ -1,0 +1,89 @@
+"""ctypes binding of the C ABI declared in ``include/deers_b200.h``."""
+from __future__ import annotations
+
+import ctypes
+import os
+
+from .errors import CudaError
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "lib", "libdeers_b200.so")
+
+OK, ERR_NULL, ERR_SHAPE, ERR_DTYPE, ERR_LAYOUT, ERR_WORKSPACE, ERR_CUDA, ERR_KERNEL, ERR_UNSUPPORTED, ERR_DEVICE = range(10)
+F16, F32 = 0, 1
+
+# Every symbol include/deers_b200.h declares.
+SYMBOLS = [
+    "deers_b200_attn_desc_compact", "deers_b200_init", "deers_b200_destroy", "deers_b200_set_stream",
+    "deers_b200_stream", "deers_b200_alloc", "deers_b200_free", "deers_b200_memcpy_h2d",
+    "deers_b200_memcpy_d2h", "deers_b200_memcpy_d2d", "deers_b200_sync", "deers_b200_attn_workspace_bytes",
+    "deers_b200_attn_fwd", "deers_b200_attn_bwd", "deers_b200_status_string", "deers_b200_last_error",
+    "deers_b200_launch_count", "deers_b200_selftest_umma",
+]
+
+
+class AttnDesc(ctypes.Structure):
+    _fields_ = [("B", ctypes.c_int32), ("H", ctypes.c_int32), ("T", ctypes.c_int32), ("D", ctypes.c_int32),
+                ("dtype", ctypes.c_int32), ("causal", ctypes.c_int32), ("scale", ctypes.c_float),
+                ("q_strides", ctypes.c_int64 * 4), ("k_strides", ctypes.c_int64 * 4),
+                ("v_strides", ctypes.c_int64 * 4), ("o_strides", ctypes.c_int64 * 4),
+                ("do_strides", ctypes.c_int64 * 4), ("dq_strides", ctypes.c_int64 * 4),
+                ("dk_strides", ctypes.c_int64 * 4), ("dv_strides", ctypes.c_int64 * 4)]
+
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    """Loads the shared library; raises if it has not been built (no fallback exists)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(f"{LIB_PATH} is missing: run `python -m deers_b200.build` "
+                          "(the attention path has no CPU or PyTorch fallback)")
+    L = ctypes.CDLL(LIB_PATH)
+    vp, sz, i32 = ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int
+    dp = ctypes.POINTER(AttnDesc)
+    L.deers_b200_attn_desc_compact.argtypes = [dp, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
+                                               ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_float]
+    L.deers_b200_attn_desc_compact.restype = None
+    L.deers_b200_init.argtypes = [i32, vp, ctypes.POINTER(vp)]
+    L.deers_b200_destroy.argtypes = [vp]
+    L.deers_b200_destroy.restype = None
+    L.deers_b200_set_stream.argtypes = [vp, vp]
+    L.deers_b200_stream.argtypes = [vp]
+    L.deers_b200_stream.restype = vp
+    L.deers_b200_alloc.argtypes = [vp, sz, ctypes.POINTER(vp)]
+    L.deers_b200_free.argtypes = [vp, vp]
+    for n in ("h2d", "d2h", "d2d"):
+        getattr(L, f"deers_b200_memcpy_{n}").argtypes = [vp, vp, vp, sz]
+    L.deers_b200_sync.argtypes = [vp]
+    L.deers_b200_attn_workspace_bytes.argtypes = [dp, i32]
+    L.deers_b200_attn_workspace_bytes.restype = sz
+    L.deers_b200_attn_fwd.argtypes = [vp, dp, vp, vp, vp, vp, vp, vp, sz]
+    L.deers_b200_attn_bwd.argtypes = [vp, dp] + [vp] * 10 + [sz]
+    L.deers_b200_status_string.argtypes = [i32]
+    L.deers_b200_status_string.restype = ctypes.c_char_p
+    L.deers_b200_last_error.argtypes = [vp]
+    L.deers_b200_last_error.restype = ctypes.c_char_p
+    L.deers_b200_launch_count.argtypes = [vp]
+    L.deers_b200_launch_count.restype = ctypes.c_uint64
+    L.deers_b200_selftest_umma.argtypes = [vp, ctypes.POINTER(ctypes.c_float)]
+    _lib = L
+    return L
+
+
+def status_string(status: int) -> str:
+    return lib().deers_b200_status_string(status).decode()
+
+
+def check(status: int, ctx=None) -> None:
+    """Maps a non-zero status to CudaError, like Error::Cuda(String) on the deers side."""
+    if status != OK:
+        text = status_string(status)
+        if ctx is not None:
+            detail = lib().deers_b200_last_error(ctx).decode()
+            if detail:
+                text = f"{text} [{detail}]"
+        raise CudaError(status, text)

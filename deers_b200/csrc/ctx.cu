@@ -1,0 +1,253 @@
+// Context, buffers, copies, status strings and argument validation of the
+// deers_b200 C ABI.  The attention entry points validate here and dispatch to the
+// f32 (FFMA) or f16 (tcgen05) kernel files; there is no CPU fallback.
+#include "common.cuh"
+
+#include <new>
+
+static const char* kStatus[] = {
+    "ok",
+    "null pointer argument",
+    "unsupported shape",
+    "unsupported dtype",
+    "layout not accepted (inner stride must be 1, rows 16-byte aligned): compact and retry",
+    "workspace missing or too small",
+    "CUDA call failed",
+    "kernel gave up on a bounded wait",
+    "no kernel for this request",
+    "device is not sm_100",
+};
+
+extern "C" const char* deers_b200_status_string(int status) {
+    if (status < 0 || status > DEERS_ERR_DEVICE) return "unknown status";
+    return kStatus[status];
+}
+
+extern "C" const char* deers_b200_last_error(deers_ctx* ctx) { return ctx ? ctx->last_error : ""; }
+
+extern "C" uint64_t deers_b200_launch_count(deers_ctx* ctx) { return ctx ? ctx->launches : 0; }
+
+extern "C" void deers_b200_attn_desc_compact(deers_attn_desc* d, int32_t B, int32_t H, int32_t T,
+                                             int32_t D, int32_t dtype, int32_t causal, float scale) {
+    if (!d) return;
+    d->B = B; d->H = H; d->T = T; d->D = D;
+    d->dtype = dtype; d->causal = causal; d->scale = scale;
+    const int64_t s[4] = {(int64_t)H * T * D, (int64_t)T * D, (int64_t)D, 1};
+    int64_t* all[8] = {d->q_strides, d->k_strides, d->v_strides, d->o_strides,
+                       d->do_strides, d->dq_strides, d->dk_strides, d->dv_strides};
+    for (int t = 0; t < 8; ++t)
+        for (int i = 0; i < 4; ++i) all[t][i] = s[i];
+}
+
+extern "C" int deers_b200_init(int device_ordinal, void* stream, deers_ctx** out) {
+    if (!out) return DEERS_ERR_NULL;
+    *out = nullptr;
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || device_ordinal < 0 || device_ordinal >= count)
+        return DEERS_ERR_CUDA;
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, device_ordinal) != cudaSuccess) return DEERS_ERR_CUDA;
+    if (prop.major != 10) return DEERS_ERR_DEVICE;
+    if (cudaSetDevice(device_ordinal) != cudaSuccess) return DEERS_ERR_CUDA;
+
+    deers_ctx* ctx = new (std::nothrow) deers_ctx();
+    if (!ctx) return DEERS_ERR_CUDA;
+    memset(ctx, 0, sizeof(*ctx));
+    ctx->device = device_ordinal;
+    ctx->sm_count = prop.multiProcessorCount;
+    if (stream) {
+        ctx->stream = (cudaStream_t)stream;
+        ctx->owns_stream = false;
+    } else {
+        if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess) {
+            delete ctx;
+            return DEERS_ERR_CUDA;
+        }
+        ctx->owns_stream = true;
+    }
+    if (cudaHostAlloc((void**)&ctx->host_err, sizeof(unsigned int), cudaHostAllocMapped) != cudaSuccess ||
+        cudaHostGetDevicePointer((void**)&ctx->dev_err, ctx->host_err, 0) != cudaSuccess) {
+        if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
+        delete ctx;
+        return DEERS_ERR_CUDA;
+    }
+    *ctx->host_err = 0;
+    cudaDriverEntryPointQueryResult qres;
+    void* fn = nullptr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+        fn = nullptr;
+    ctx->encode_tiled = fn;
+    *out = ctx;
+    return DEERS_OK;
+}
+
+extern "C" void deers_b200_destroy(deers_ctx* ctx) {
+    if (!ctx) return;
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
+    if (ctx->host_err) cudaFreeHost(ctx->host_err);
+    delete ctx;
+}
+
+extern "C" int deers_b200_set_stream(deers_ctx* ctx, void* stream) {
+    if (!ctx) return DEERS_ERR_NULL;
+    if (ctx->owns_stream) {
+        cudaStreamSynchronize(ctx->stream);
+        cudaStreamDestroy(ctx->stream);
+        ctx->owns_stream = false;
+    }
+    ctx->stream = (cudaStream_t)stream;
+    return DEERS_OK;
+}
+
+extern "C" void* deers_b200_stream(deers_ctx* ctx) { return ctx ? (void*)ctx->stream : nullptr; }
+
+extern "C" int deers_b200_alloc(deers_ctx* ctx, size_t bytes, void** dptr) {
+    if (!ctx || !dptr) return DEERS_ERR_NULL;
+    DEERS_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    DEERS_CUDA_TRY(ctx, cudaMallocAsync(dptr, bytes ? bytes : 1, ctx->stream));
+    return DEERS_OK;
+}
+
+extern "C" int deers_b200_free(deers_ctx* ctx, void* dptr) {
+    if (!ctx) return DEERS_ERR_NULL;
+    if (!dptr) return DEERS_OK;
+    DEERS_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    DEERS_CUDA_TRY(ctx, cudaFreeAsync(dptr, ctx->stream));
+    return DEERS_OK;
+}
+
+extern "C" int deers_b200_memcpy_h2d(deers_ctx* ctx, void* dst, const void* src, size_t bytes) {
+    if (!ctx || (bytes && (!dst || !src))) return DEERS_ERR_NULL;
+    DEERS_CUDA_TRY(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    return DEERS_OK;
+}
+
+extern "C" int deers_b200_memcpy_d2h(deers_ctx* ctx, void* dst, const void* src, size_t bytes) {
+    if (!ctx || (bytes && (!dst || !src))) return DEERS_ERR_NULL;
+    DEERS_CUDA_TRY(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+    DEERS_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    return DEERS_OK;
+}
+
+extern "C" int deers_b200_memcpy_d2d(deers_ctx* ctx, void* dst, const void* src, size_t bytes) {
+    if (!ctx || (bytes && (!dst || !src))) return DEERS_ERR_NULL;
+    DEERS_CUDA_TRY(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+    return DEERS_OK;
+}
+
+extern "C" int deers_b200_sync(deers_ctx* ctx) {
+    if (!ctx) return DEERS_ERR_NULL;
+    DEERS_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    const unsigned int e = *(volatile unsigned int*)ctx->host_err;
+    if (e != 0) {
+        *(volatile unsigned int*)ctx->host_err = 0;
+        snprintf(ctx->last_error, sizeof(ctx->last_error),
+                 "kernel error word 0x%x (kernel family 0x%x, wait id %u)", e, e & 0xf00u, e & 0xffu);
+        return DEERS_ERR_KERNEL;
+    }
+    return DEERS_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Validation shared by forward and backward
+// ---------------------------------------------------------------------------
+static int check_tensor(const deers_attn_desc* d, const void* p, const int64_t* s, size_t esize) {
+    if (!p) return DEERS_ERR_NULL;
+    if (s[3] != 1) return DEERS_ERR_LAYOUT;
+    // f16 (TMA) needs 16-byte aligned bases and row starts; the f32 kernels fall
+    // back to scalar loads when a row is not 16-byte aligned, so 4 bytes suffice.
+    const uintptr_t mask = (esize == 2) ? 15u : 3u;
+    if (((uintptr_t)p & mask) != 0) return DEERS_ERR_LAYOUT;
+    for (int i = 0; i < 3; ++i) {
+        if (s[i] < 0) return DEERS_ERR_LAYOUT;
+        const int64_t extent = (i == 0) ? d->B : (i == 1) ? d->H : d->T;
+        if (extent > 1 && ((s[i] * (int64_t)esize) & (int64_t)mask) != 0) return DEERS_ERR_LAYOUT;
+    }
+    return DEERS_OK;
+}
+
+static int check_desc(const deers_attn_desc* d) {
+    if (!d) return DEERS_ERR_NULL;
+    if (d->dtype != DEERS_F16 && d->dtype != DEERS_F32) return DEERS_ERR_DTYPE;
+    if (d->B < 1 || d->H < 1 || d->T < 1 || d->D < 1) return DEERS_ERR_SHAPE;
+    if ((int64_t)d->B * d->H > 0x7fffffffLL / 64) return DEERS_ERR_SHAPE;
+    if (d->T > (1 << 20)) return DEERS_ERR_SHAPE;
+    if (d->dtype == DEERS_F32) {
+        if (d->D > 128) return DEERS_ERR_SHAPE;
+    } else {
+        if (d->D != 64 && d->D != 128) return DEERS_ERR_SHAPE;           // tcgen05 tile shapes
+    }
+    if (!(d->scale == d->scale)) return DEERS_ERR_SHAPE;
+    return DEERS_OK;
+}
+
+static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+static size_t delta_bytes(const deers_attn_desc* d) {
+    return align_up((size_t)d->B * d->H * d->T * sizeof(float), 256);
+}
+
+extern "C" size_t deers_b200_attn_workspace_bytes(const deers_attn_desc* d, int pass) {
+    if (check_desc(d) != DEERS_OK || pass == 0) return 0;
+    size_t n = delta_bytes(d);
+    if (d->dtype == DEERS_F16) n += attn_bwd_f16_dqacc_bytes(d);
+    return n;
+}
+
+extern "C" int deers_b200_attn_fwd(deers_ctx* ctx, const deers_attn_desc* d, const void* q,
+                                   const void* k, const void* v, void* o, float* lse, void* workspace,
+                                   size_t workspace_bytes) {
+    (void)workspace; (void)workspace_bytes;
+    if (!ctx) return DEERS_ERR_NULL;
+    int rc = check_desc(d);
+    if (rc) return rc;
+    if (!lse) return DEERS_ERR_NULL;
+    const size_t es = d->dtype == DEERS_F16 ? 2 : 4;
+    if ((rc = check_tensor(d, q, d->q_strides, es))) return rc;
+    if ((rc = check_tensor(d, k, d->k_strides, es))) return rc;
+    if ((rc = check_tensor(d, v, d->v_strides, es))) return rc;
+    if ((rc = check_tensor(d, o, d->o_strides, es))) return rc;
+    DEERS_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    if (d->dtype == DEERS_F32)
+        return launch_attn_fwd_f32(ctx, d, (const float*)q, (const float*)k, (const float*)v, (float*)o, lse);
+    return launch_attn_fwd_f16(ctx, d, q, k, v, o, lse);
+}
+
+extern "C" int deers_b200_attn_bwd(deers_ctx* ctx, const deers_attn_desc* d, const void* q,
+                                   const void* k, const void* v, const void* o, const float* lse,
+                                   const void* d_o, void* dq, void* dk, void* dv, void* workspace,
+                                   size_t workspace_bytes) {
+    if (!ctx) return DEERS_ERR_NULL;
+    int rc = check_desc(d);
+    if (rc) return rc;
+    if (!lse) return DEERS_ERR_NULL;
+    const size_t es = d->dtype == DEERS_F16 ? 2 : 4;
+    if ((rc = check_tensor(d, q, d->q_strides, es))) return rc;
+    if ((rc = check_tensor(d, k, d->k_strides, es))) return rc;
+    if ((rc = check_tensor(d, v, d->v_strides, es))) return rc;
+    if ((rc = check_tensor(d, o, d->o_strides, es))) return rc;
+    if ((rc = check_tensor(d, d_o, d->do_strides, es))) return rc;
+    if ((rc = check_tensor(d, dq, d->dq_strides, es))) return rc;
+    if ((rc = check_tensor(d, dk, d->dk_strides, es))) return rc;
+    if ((rc = check_tensor(d, dv, d->dv_strides, es))) return rc;
+    const size_t need = deers_b200_attn_workspace_bytes(d, 1);
+    if (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 255u) != 0)
+        return DEERS_ERR_WORKSPACE;
+    DEERS_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    float* delta = (float*)workspace;
+    if (d->dtype == DEERS_F32)
+        return launch_attn_bwd_f32(ctx, d, (const float*)q, (const float*)k, (const float*)v,
+                                   (const float*)o, lse, (const float*)d_o, (float*)dq, (float*)dk,
+                                   (float*)dv, delta);
+    float* dq_acc = (float*)((char*)workspace + delta_bytes(d));
+    return launch_attn_bwd_f16(ctx, d, q, k, v, o, lse, d_o, dq, dk, dv, delta, dq_acc);
+}
+
+extern "C" int deers_b200_selftest_umma(deers_ctx* ctx, float* max_abs_err) {
+    if (!ctx || !max_abs_err) return DEERS_ERR_NULL;
+    DEERS_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    return run_selftest_umma(ctx, max_abs_err);
+}

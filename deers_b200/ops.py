@@ -1,0 +1,212 @@
+"""Host-side mirror of the deers operator interface for the fused attention op.
+
+deers builds its graph from ``TensorOp`` objects (src/ops.rs:82-97): ``forward``
+consumes the op and returns the output tensor with the op stored in it,
+``backward(grads, out_grad)`` accumulates input gradients into a
+``GradientStore`` (src/backprop.rs:74-128) and ``dependencies`` lists the inputs.
+``CausalAttention`` is that op for the chain of src/models/gpt.rs:139-144; the
+storage-level pair ``attention_fwd`` / ``attention_bwd`` is what a new
+``BackendStorage::attention_fwd/bwd`` (added like ``log_softmax_fwd/bwd``,
+src/storage.rs:284-302) would call through the C ABI.
+
+torch tensors stand in for ``CudaStorage`` + ``Layout`` (device memory, strides,
+stream); all arithmetic happens in ``libdeers_b200.so``.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from . import _lib
+from .errors import DeviceMismatch, DTypeMismatch, LayoutMismatch
+
+_DTYPES = {torch.float16: _lib.F16, torch.float32: _lib.F32}
+
+
+class Context:
+    """One library context per (device, stream): the analogue of deers' global CudaRuntime
+    (src/storage/cuda.rs:455-521).  Work is enqueued on torch's current stream."""
+
+    _cache: Dict[Tuple[int, int], "Context"] = {}
+
+    def __init__(self, device: int, stream_ptr: int):
+        self.handle = ctypes.c_void_p()
+        self.device = device
+        _lib.check(_lib.lib().deers_b200_init(device, ctypes.c_void_p(stream_ptr), ctypes.byref(self.handle)))
+
+    @classmethod
+    def current(cls, device: torch.device) -> "Context":
+        if device.type != "cuda":
+            raise DeviceMismatch("the fused attention op only exists on the CUDA device (no CPU fallback)")
+        idx = device.index if device.index is not None else torch.cuda.current_device()
+        stream = torch.cuda.current_stream(idx).cuda_stream
+        key = (idx, stream)
+        ctx = cls._cache.get(key)
+        if ctx is None:
+            ctx = cls(idx, stream)
+            cls._cache[key] = ctx
+        return ctx
+
+    def sync(self) -> None:
+        """Device::synchronize (src/device.rs:66-72); raises if a kernel reported an error."""
+        _lib.check(_lib.lib().deers_b200_sync(self.handle), self.handle)
+
+    def launch_count(self) -> int:
+        return int(_lib.lib().deers_b200_launch_count(self.handle))
+
+    def selftest_umma(self) -> List[float]:
+        errs = (ctypes.c_float * 4)()
+        _lib.check(_lib.lib().deers_b200_selftest_umma(self.handle, errs), self.handle)
+        return [float(e) for e in errs]
+
+
+def _strides(t: torch.Tensor):
+    return (ctypes.c_int64 * 4)(*t.stride())
+
+
+def _check_inputs(name: str, tensors) -> None:
+    q = tensors[0]
+    if q.dim() != 4:
+        raise LayoutMismatch(f"{name}: expected [B, H, T, D], got {tuple(q.shape)}")
+    for t in tensors[1:]:
+        if t.shape != q.shape:
+            raise LayoutMismatch(f"{name}: {tuple(t.shape)} vs {tuple(q.shape)}")
+        if t.dtype != q.dtype:
+            raise DTypeMismatch(f"{name}: {t.dtype} vs {q.dtype}")
+        if t.device != q.device:
+            raise DeviceMismatch(f"{name}: {t.device} vs {q.device}")
+    if q.dtype not in _DTYPES:
+        raise DTypeMismatch(f"{name}: unsupported dtype {q.dtype}")
+
+
+def _usable(t: torch.Tensor) -> bool:
+    """True if the kernels can read `t` in place: inner stride 1 and aligned rows."""
+    if t.stride(3) != 1 and t.shape[3] > 1:
+        return False
+    esize = t.element_size()
+    align = 16 if t.dtype == torch.float16 else 4
+    if t.data_ptr() % align:
+        return False
+    return all((t.stride(i) * esize) % align == 0 or t.shape[i] == 1 for i in range(3))
+
+
+def _compact(t: torch.Tensor) -> torch.Tensor:
+    # Inputs that need contiguity are compacted by the op, as in src/ops.rs:1330,1405,1494.
+    return t if _usable(t) else t.contiguous()
+
+
+def _desc(q, k, v, o, d_o=None, dq=None, dk=None, dv=None, scale=1.0, causal=True) -> _lib.AttnDesc:
+    B, H, T, D = q.shape
+    d = _lib.AttnDesc()
+    _lib.lib().deers_b200_attn_desc_compact(ctypes.byref(d), B, H, T, D, _DTYPES[q.dtype], int(causal), scale)
+    d.q_strides, d.k_strides, d.v_strides, d.o_strides = _strides(q), _strides(k), _strides(v), _strides(o)
+    if d_o is not None:
+        d.do_strides, d.dq_strides, d.dk_strides, d.dv_strides = (_strides(d_o), _strides(dq), _strides(dk),
+                                                                 _strides(dv))
+    return d
+
+
+def default_scale(head_dim: int) -> float:
+    """1/sqrt(head_dim) computed in f64 as the module does (src/models/gpt.rs:139)."""
+    return 1.0 / math.sqrt(float(head_dim))
+
+
+def attention_fwd(q, k, v, scale: float, causal: bool = True):
+    """Storage-level forward: returns (o [B,H,T,D] compact, lse [B,H,T] float32)."""
+    _check_inputs("attention_fwd", (q, k, v))
+    q, k, v = _compact(q), _compact(k), _compact(v)
+    ctx = Context.current(q.device)
+    o = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+    lse = torch.empty(q.shape[:3], dtype=torch.float32, device=q.device)
+    d = _desc(q, k, v, o, scale=scale, causal=causal)
+    _lib.check(_lib.lib().deers_b200_attn_fwd(ctx.handle, ctypes.byref(d), q.data_ptr(), k.data_ptr(),
+                                              v.data_ptr(), o.data_ptr(), lse.data_ptr(), None, 0), ctx.handle)
+    return o, lse
+
+
+def workspace_bytes(q, scale: float = 1.0, causal: bool = True, pass_: int = 1) -> int:
+    d = _desc(q, q, q, q, scale=scale, causal=causal)
+    return int(_lib.lib().deers_b200_attn_workspace_bytes(ctypes.byref(d), pass_))
+
+
+def attention_bwd(q, k, v, o, lse, d_o, scale: float, causal: bool = True, workspace: Optional[torch.Tensor] = None):
+    """Storage-level backward: returns (dq, dk, dv), each compact [B,H,T,D]."""
+    _check_inputs("attention_bwd", (q, k, v, o, d_o))
+    q, k, v, o, d_o = _compact(q), _compact(k), _compact(v), _compact(o), _compact(d_o)
+    ctx = Context.current(q.device)
+    dq, dk, dv = (torch.empty(q.shape, dtype=q.dtype, device=q.device) for _ in range(3))
+    d = _desc(q, k, v, o, d_o, dq, dk, dv, scale=scale, causal=causal)
+    need = int(_lib.lib().deers_b200_attn_workspace_bytes(ctypes.byref(d), 1))
+    if workspace is None or workspace.numel() * workspace.element_size() < need:
+        workspace = torch.empty(max(need, 256), dtype=torch.uint8, device=q.device)
+    _lib.check(_lib.lib().deers_b200_attn_bwd(ctx.handle, ctypes.byref(d), q.data_ptr(), k.data_ptr(),
+                                              v.data_ptr(), o.data_ptr(), lse.data_ptr(), d_o.data_ptr(),
+                                              dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), workspace.data_ptr(),
+                                              workspace.numel() * workspace.element_size()), ctx.handle)
+    return dq, dk, dv
+
+
+class GradientStore:
+    """Insert-or-add gradient map keyed by tensor identity (src/backprop.rs:74-128)."""
+
+    def __init__(self):
+        self._grads: Dict[int, torch.Tensor] = {}
+
+    def accumulate(self, tensor: torch.Tensor, grad: torch.Tensor) -> None:
+        key = id(tensor)
+        if key in self._grads:
+            self._grads[key] = self._grads[key] + grad
+        else:
+            self._grads[key] = grad
+
+    def get(self, tensor: torch.Tensor) -> Optional[torch.Tensor]:
+        return self._grads.get(id(tensor))
+
+
+class CausalAttention:
+    """The fused op: ``softmax(scale * q @ k^T + causal_mask) @ v`` on ``[B, H, T, D]`` tensors.
+
+    Same life cycle as deers ops: ``CausalAttention.new(...)`` validates (raising
+    LayoutMismatch / DTypeMismatch / DeviceMismatch), ``forward()`` returns the
+    output and keeps what the backward needs (O and the row lse) in ``self``, the
+    pattern of LogSumExp / FusedLogSoftmax (src/ops.rs:1152-1159, 1214-1220).
+    """
+
+    def __init__(self, q, k, v, scale: float, causal: bool = True):
+        self.q, self.k, self.v = q, k, v
+        self.scale, self.causal = float(scale), bool(causal)
+        self.o: Optional[torch.Tensor] = None
+        self.lse: Optional[torch.Tensor] = None
+
+    @classmethod
+    def new(cls, q, k, v, scale: Optional[float] = None, causal: bool = True) -> "CausalAttention":
+        _check_inputs("CausalAttention", (q, k, v))
+        if q.device.type != "cuda":
+            raise DeviceMismatch("CausalAttention: the fused op runs on the CUDA device only")
+        return cls(q, k, v, default_scale(q.shape[3]) if scale is None else scale, causal)
+
+    def forward(self) -> torch.Tensor:
+        self.o, self.lse = attention_fwd(self.q, self.k, self.v, self.scale, self.causal)
+        return self.o
+
+    def backward(self, grads: GradientStore, out_grad: torch.Tensor) -> None:
+        if self.o is None:
+            raise RuntimeError("CausalAttention.backward before forward")
+        dq, dk, dv = attention_bwd(self.q, self.k, self.v, self.o, self.lse, out_grad, self.scale, self.causal)
+        grads.accumulate(self.q, dq)
+        grads.accumulate(self.k, dk)
+        grads.accumulate(self.v, dv)
+
+    def dependencies(self) -> List[torch.Tensor]:
+        return [self.q, self.k, self.v]
+
+    def name(self) -> str:
+        return "CausalAttention"
+
+
+def causal_attention(q, k, v, scale: Optional[float] = None) -> torch.Tensor:
+    """Tensor-method form (house style of src/tensor.rs:379-381): new(..).forward()."""
+    return CausalAttention.new(q, k, v, scale).forward()

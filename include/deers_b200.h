@@ -1,0 +1,173 @@
+/*
+ * deers_b200 — C ABI of the B200 (sm_100a) causal self-attention path for deers.
+ *
+ * The deers repository has no FFI of its own: its CUDA backend is Rust over
+ * cudarc.  These entry points are what `src/storage/cuda.rs` would bind (with
+ * `extern "C"` declarations, linked by a `build.rs` that runs nvcc) to replace
+ * the matmul -> scale -> mask -> softmax -> matmul chain of
+ * `src/models/gpt.rs:139-144` and its autograd backward by one fused op.  Each
+ * declaration cites the reference interface it stands in for.
+ *
+ * Conventions
+ *  - Every pointer named q/k/v/o/d_o/dq/dk/dv/lse/workspace is a DEVICE pointer
+ *    owned by the caller.  Tensors are [B, H, T, D]; strides are in elements;
+ *    the innermost (D) stride must be 1 and every base pointer and every row
+ *    start must be 16-byte aligned, otherwise DEERS_ERR_LAYOUT is returned so
+ *    that the caller can compact() and retry.  Outputs are written with the
+ *    strides given in the descriptor.
+ *  - Work is enqueued on the context's stream and the call returns at once; no
+ *    allocation and no synchronisation happens inside attn_fwd / attn_bwd.
+ *  - Nothing aborts or traps.  Every function returns a status (0 = OK) and
+ *    device-side waits are bounded: a kernel that gives up records a code that
+ *    deers_b200_sync() reports as DEERS_ERR_KERNEL.
+ *  - lse is float32 [B, H, T], the natural-log row sums of exp(scale * scores)
+ *    over the unmasked columns: the quantity `CpuStorage::log_sum_exp`
+ *    (`src/storage/cpu.rs:755-770`) produces on the scaled, masked scores.
+ */
+#ifndef DEERS_B200_H
+#define DEERS_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#pragma GCC visibility push(default)
+#endif
+
+typedef struct deers_ctx deers_ctx;
+
+enum {
+    DEERS_OK = 0,
+    DEERS_ERR_NULL = 1,        /* a required pointer was NULL                           */
+    DEERS_ERR_SHAPE = 2,       /* B,H,T,D out of the supported range                    */
+    DEERS_ERR_DTYPE = 3,       /* dtype not DEERS_F16 / DEERS_F32                       */
+    DEERS_ERR_LAYOUT = 4,      /* inner stride != 1 or misaligned: compact() and retry  */
+    DEERS_ERR_WORKSPACE = 5,   /* workspace missing or too small                        */
+    DEERS_ERR_CUDA = 6,        /* a CUDA runtime/driver call failed (see last_error)    */
+    DEERS_ERR_KERNEL = 7,      /* a kernel gave up on a bounded wait (see last_error)   */
+    DEERS_ERR_UNSUPPORTED = 8, /* valid request this build has no kernel for            */
+    DEERS_ERR_DEVICE = 9       /* device is not an sm_100 part                          */
+};
+
+enum { DEERS_F16 = 0, DEERS_F32 = 1 };
+
+/*
+ * One attention problem.  Mirrors the arguments the reference passes down its
+ * storage layer: a Layout (shape + strides in elements, `src/layout.rs:151-202`)
+ * per operand, the dtype (`src/dtype.rs:14-21`) and the scale the module
+ * computes (`src/models/gpt.rs:139`).
+ */
+typedef struct {
+    int32_t B, H, T, D;
+    int32_t dtype;            /* DEERS_F16 (f32 accumulate) or DEERS_F32 (FFMA, no TF32)  */
+    int32_t causal;           /* 1: column j > row i is masked (`src/nn/functional.rs:38-51`) */
+    float scale;              /* multiplies q.k^T, normally (float)(1/sqrt((double)D))    */
+    int64_t q_strides[4];     /* strides of [B,H,T,D] in elements; [3] must be 1          */
+    int64_t k_strides[4];
+    int64_t v_strides[4];
+    int64_t o_strides[4];     /* o in fwd (written) and in bwd (read)                     */
+    int64_t do_strides[4];    /* bwd only                                                 */
+    int64_t dq_strides[4];    /* bwd only: strides the gradients are written with         */
+    int64_t dk_strides[4];
+    int64_t dv_strides[4];
+} deers_attn_desc;
+
+/* Fills every stride field for compact [B,H,T,D] tensors. */
+void deers_b200_attn_desc_compact(deers_attn_desc* desc, int32_t B, int32_t H, int32_t T, int32_t D,
+                                  int32_t dtype, int32_t causal, float scale);
+
+/*
+ * Context: device, stream, error word.  Stands in for the process-global
+ * `CudaRuntime` of `src/storage/cuda.rs:455-521` (context on device 0, default
+ * stream, module, cuBLAS), with a device ordinal added so that one process per
+ * GPU can shard (batch x head) slices.  `stream` may be NULL (the context then
+ * creates its own non-blocking stream) or an existing cudaStream_t to enqueue on
+ * (the reference's single default stream, `src/storage/cuda.rs:505`).
+ */
+int deers_b200_init(int device_ordinal, void* stream, deers_ctx** out);
+void deers_b200_destroy(deers_ctx* ctx);
+int deers_b200_set_stream(deers_ctx* ctx, void* stream);
+void* deers_b200_stream(deers_ctx* ctx);
+
+/*
+ * Buffers and copies: `CudaStorage` allocation, upload and read-back
+ * (`src/storage/cuda.rs:637-706`, `:1541-1555`).  alloc/free are stream-ordered;
+ * memcpy_d2h synchronises the stream, the other copies are asynchronous.
+ */
+int deers_b200_alloc(deers_ctx* ctx, size_t bytes, void** dptr);
+int deers_b200_free(deers_ctx* ctx, void* dptr);
+int deers_b200_memcpy_h2d(deers_ctx* ctx, void* dst, const void* src, size_t bytes);
+int deers_b200_memcpy_d2h(deers_ctx* ctx, void* dst, const void* src, size_t bytes);
+int deers_b200_memcpy_d2d(deers_ctx* ctx, void* dst, const void* src, size_t bytes);
+
+/*
+ * `Device::synchronize` (`src/device.rs:66-72` -> `src/storage/cuda.rs:1598-1602`).
+ * Also reads the device error word: returns DEERS_ERR_KERNEL if any kernel since
+ * the last sync gave up on a bounded wait, and clears the word.
+ */
+int deers_b200_sync(deers_ctx* ctx);
+
+/*
+ * Scratch memory a pass needs (pass 0 = forward, 1 = backward), in bytes.
+ * Forward needs none.  Backward keeps rowsum(dO * O) per row and, for f16, a
+ * float32 dQ accumulator.  The reference allocates the equivalent temporaries
+ * inside each op (`src/storage/cuda.rs:637-644`).
+ */
+size_t deers_b200_attn_workspace_bytes(const deers_attn_desc* desc, int pass);
+
+/*
+ * Fused forward: O = softmax(scale * Q K^T + causal mask) V and the per-row lse.
+ * Replaces `src/models/gpt.rs:139-144` (MatMul `src/ops.rs:1013-1106`, ScalarMul
+ * `:613-648`, causal_mask + Broadcast + EWiseAdd, softmax `src/tensor.rs:408-458`,
+ * MatMul) — the storage-level hook is a new `BackendStorage::attention_fwd` added
+ * the way `log_softmax_fwd` was (`src/storage.rs:284-302,379-418`).
+ */
+int deers_b200_attn_fwd(deers_ctx* ctx, const deers_attn_desc* desc, const void* q, const void* k,
+                        const void* v, void* o, float* lse, void* workspace, size_t workspace_bytes);
+
+/*
+ * Fused backward: dQ, dK, dV from dO, recomputing P from lse.  Replaces the
+ * chain `MatMul::backward` (`src/ops.rs:1089-1101`), `EWiseExp::backward`
+ * (`:422-425`), log-softmax backward (`:210-214,777-799,1162-1175`),
+ * `ScalarMul::backward` (`:638-643`), `MatMul::backward`.  dK and dV are
+ * accumulated per KV tile without atomics (bitwise reproducible).
+ */
+int deers_b200_attn_bwd(deers_ctx* ctx, const deers_attn_desc* desc, const void* q, const void* k,
+                        const void* v, const void* o, const float* lse, const void* d_o, void* dq,
+                        void* dk, void* dv, void* workspace, size_t workspace_bytes);
+
+/*
+ * Status text, the way backend failures become `Error::Cuda(String)`
+ * (`src/error.rs:40-41`).  last_error adds the detail of the most recent failure
+ * on this context (CUDA error string, or which kernel wait gave up).
+ */
+const char* deers_b200_status_string(int status);
+const char* deers_b200_last_error(deers_ctx* ctx);
+
+/*
+ * Number of kernel launches this context has enqueued so far (the reference
+ * counts launches per op in its profiler, `src/profiler.rs:160-224`).
+ */
+uint64_t deers_b200_launch_count(deers_ctx* ctx);
+
+/*
+ * Tensor-core self-test: runs one small tcgen05 GEMM per operand layout the f16
+ * kernels rely on (K-major and MN-major shared-memory operands, TMA 128-byte
+ * swizzle) and compares with a host product.  `max_abs_err` (4 floats, host
+ * memory) receives the error of each case.  No counterpart in the reference,
+ * whose GEMMs are cuBLAS calls (`src/storage/cuda.rs:1098-1177`).
+ */
+int deers_b200_selftest_umma(deers_ctx* ctx, float* max_abs_err);
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DEERS_B200_H */

@@ -1,0 +1,174 @@
+/*
+ * TEST INFRASTRUCTURE, NOT PRODUCT CODE.
+ *
+ * CPU restatement (plain C, f32, OpenMP over (batch, head) slices) of the causal
+ * self-attention path of vitillo/deers as its CPU backend executes it, op by op,
+ * materialising every T x T tensor exactly like the reference graph does.  It is
+ * the parity checker for the CUDA kernels and the timed CPU baseline; nothing in
+ * the shipped library links or calls it.
+ *
+ * PARITY UNPINNED for attention itself: the reference is Rust (no toolchain in
+ * the build image), its GEMM is the un-vendored crate `gemm 0.19.0` and its own
+ * tests compute expected values with candle at test time, so no stored golden
+ * vector for attention exists.  What IS pinned by stored reference values is
+ * the mask (ref_causal_mask, literal vectors in tests/nn.rs:194-232).  The
+ * restatement is additionally cross-checked against an independent float64
+ * autograd implementation (tests/golden/make_golden.py).
+ *
+ * Reference lines followed (paths inside the deers repository):
+ *   src/models/gpt.rs:139-144      scores = (q @ k^T) * scale; softmax(scores + mask); @ v
+ *   src/storage/cpu.rs:688-753     batched matmul, serial over the batch, f32 accumulate
+ *   src/storage.rs:105-123         scalar multiply: the f64 scale is cast to f32 first
+ *   src/nn/functional.rs:12-55     additive mask: 0 where j <= i, -inf where j > i
+ *   src/storage/cpu.rs:755-770     log_sum_exp: max, left-to-right f32 sum of exp(x-max), ln + max
+ *   src/tensor.rs:408-425,456-458  softmax = exp(x - lse)
+ *   src/ops.rs:1089-1101           matmul backward: dA = dC @ B^T, dB = A^T @ dC
+ *   src/ops.rs:422-425             exp backward: g * exp(x)
+ *   src/ops.rs:210-214,777-799,1162-1175  x - lse backward: g - softmax * rowsum(g)
+ *   src/ops.rs:638-643             scalar multiply backward: g * scale
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+#define API __attribute__((visibility("default")))
+
+API int ref_num_threads(void) {
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
+
+/* src/nn/functional.rs:12-55 — [batch, 1, tgt_len, tgt_len + offset], 0 or -inf. */
+API void ref_causal_mask(int batch, int tgt_len, int offset, float* out) {
+    const int total = tgt_len + offset;
+    for (int b = 0; b < batch; ++b)
+        for (int i = 0; i < tgt_len; ++i)
+            for (int j = 0; j < total; ++j)
+                out[((size_t)b * tgt_len + i) * total + j] =
+                    (j >= offset && j - offset > i) ? -INFINITY : 0.0f;
+}
+
+/* C[m,n] = sum_k A[m,k] * B[n,k]   (A @ B^T), f32 accumulate; src/storage/cpu.rs:729-747 */
+static void gemm_nt(const float* A, const float* B, float* C, int M, int N, int K) {
+    for (int m = 0; m < M; ++m) {
+        const float* a = A + (size_t)m * K;
+        for (int n = 0; n < N; ++n) {
+            const float* b = B + (size_t)n * K;
+            float acc = 0.0f;
+            for (int k = 0; k < K; ++k) acc += a[k] * b[k];
+            C[(size_t)m * N + n] = acc;
+        }
+    }
+}
+
+/* C[m,n] = sum_k A[m,k] * B[k,n]   (A @ B) */
+static void gemm_nn(const float* A, const float* B, float* C, int M, int N, int K) {
+    for (int m = 0; m < M; ++m) {
+        float* c = C + (size_t)m * N;
+        for (int n = 0; n < N; ++n) c[n] = 0.0f;
+        for (int k = 0; k < K; ++k) {
+            const float a = A[(size_t)m * K + k];
+            const float* b = B + (size_t)k * N;
+            for (int n = 0; n < N; ++n) c[n] += a * b[n];
+        }
+    }
+}
+
+/* C[m,n] = sum_k A[k,m] * B[k,n]   (A^T @ B) */
+static void gemm_tn(const float* A, const float* B, float* C, int M, int N, int K) {
+    for (size_t i = 0; i < (size_t)M * N; ++i) C[i] = 0.0f;
+    for (int k = 0; k < K; ++k) {
+        const float* a = A + (size_t)k * M;
+        const float* b = B + (size_t)k * N;
+        for (int m = 0; m < M; ++m) {
+            const float am = a[m];
+            float* c = C + (size_t)m * N;
+            for (int n = 0; n < N; ++n) c[n] += am * b[n];
+        }
+    }
+}
+
+/* One (batch, head) slice, forward.  P (T x T) is left in `P` for the backward. */
+static void slice_fwd(const float* q, const float* k, const float* v, int T, int D, float scale,
+                      int causal, float* o, float* lse, float* P) {
+    gemm_nt(q, k, P, T, T, D);                               /* gpt.rs:140 */
+    for (size_t i = 0; i < (size_t)T * T; ++i) P[i] *= scale; /* gpt.rs:139-140, storage.rs:115-117 */
+    if (causal)
+        for (int i = 0; i < T; ++i)                           /* functional.rs:38-51, gpt.rs:142 */
+            for (int j = i + 1; j < T; ++j) P[(size_t)i * T + j] += -INFINITY;
+    for (int i = 0; i < T; ++i) {                             /* cpu.rs:759-770 */
+        float* row = P + (size_t)i * T;
+        float mx = -INFINITY;
+        for (int j = 0; j < T; ++j) mx = fmaxf(mx, row[j]);
+        float sum = 0.0f;
+        for (int j = 0; j < T; ++j) sum += expf(row[j] - mx);
+        const float l = logf(sum) + mx;
+        lse[i] = l;
+        for (int j = 0; j < T; ++j) row[j] = expf(row[j] - l); /* tensor.rs:419-424,456-458 */
+    }
+    gemm_nn(P, v, o, T, D, T);                                /* gpt.rs:143-144 */
+}
+
+/*
+ * Forward over compact [B,H,T,D] f32 tensors.  o: [B,H,T,D], lse: [B,H,T]
+ * (natural log of the row sums of exp(scaled, masked scores)).
+ */
+API int ref_attn_fwd(const float* q, const float* k, const float* v, int B, int H, int T, int D,
+                     float scale, int causal, float* o, float* lse) {
+    const int BH = B * H;
+    const size_t n = (size_t)T * D;
+    int fail = 0;
+#pragma omp parallel for schedule(dynamic, 1)
+    for (int s = 0; s < BH; ++s) {
+        float* P = (float*)malloc((size_t)T * T * sizeof(float));
+        if (!P) { fail = 1; continue; }
+        slice_fwd(q + s * n, k + s * n, v + s * n, T, D, scale, causal, o + s * n, lse + (size_t)s * T, P);
+        free(P);
+    }
+    return fail;
+}
+
+/*
+ * Forward + backward over compact [B,H,T,D] f32 tensors, the way the reference
+ * graph runs it: the forward's P is kept and the backward is the chain of the
+ * per-op backward rules.  Any of o/lse may be NULL.
+ */
+API int ref_attn_fwd_bwd(const float* q, const float* k, const float* v, const float* d_o, int B,
+                         int H, int T, int D, float scale, int causal, float* o, float* lse,
+                         float* dq, float* dk, float* dv) {
+    const int BH = B * H;
+    const size_t n = (size_t)T * D;
+    int fail = 0;
+#pragma omp parallel for schedule(dynamic, 1)
+    for (int s = 0; s < BH; ++s) {
+        float* P = (float*)malloc((size_t)T * T * sizeof(float));
+        float* G = (float*)malloc((size_t)T * T * sizeof(float));
+        float* o_s = (float*)malloc(n * sizeof(float));
+        float* lse_s = (float*)malloc((size_t)T * sizeof(float));
+        if (!P || !G || !o_s || !lse_s) { fail = 1; free(P); free(G); free(o_s); free(lse_s); continue; }
+        slice_fwd(q + s * n, k + s * n, v + s * n, T, D, scale, causal, o_s, lse_s, P);
+        if (o) memcpy(o + s * n, o_s, n * sizeof(float));
+        if (lse) memcpy(lse + (size_t)s * T, lse_s, (size_t)T * sizeof(float));
+        const float* go = d_o + s * n;
+        gemm_tn(P, go, dv + s * n, T, D, T);          /* dV = P^T @ dO      ops.rs:1089-1101 */
+        gemm_nt(go, v + s * n, G, T, T, D);           /* dP = dO @ V^T      ops.rs:1089-1101 */
+        for (int i = 0; i < T; ++i) {
+            float* g = G + (size_t)i * T;
+            const float* p = P + (size_t)i * T;
+            float rs = 0.0f;
+            for (int j = 0; j < T; ++j) { g[j] *= p[j]; rs += g[j]; }  /* ops.rs:422-425; Broadcast bwd sum ops.rs:777-799 */
+            for (int j = 0; j < T; ++j) g[j] = (g[j] - p[j] * rs) * scale; /* ops.rs:210-214,1162-1175; 638-643 */
+        }
+        gemm_nn(G, k + s * n, dq + s * n, T, D, T);   /* dQ = dS @ K        ops.rs:1089-1101 */
+        gemm_tn(G, q + s * n, dk + s * n, T, D, T);   /* dK = dS^T @ Q      ops.rs:1089-1101 */
+        free(P); free(G); free(o_s); free(lse_s);
+    }
+    return fail;
+}

@@ -1,0 +1,134 @@
+"""GPU parity of the f16 (tcgen05 / TMEM / TMA) kernels against the f32 CPU oracle
+evaluated on the f16-rounded inputs, through the C ABI.  Tolerance 2e-2 (max-abs
+error over the reference tensor's max-abs) as the north star states."""
+import numpy as np
+import pytest
+import torch
+
+from tests.helpers import TOL_F16, assert_close
+
+pytestmark = pytest.mark.gpu
+
+
+def test_umma_selftest_operand_layouts():
+    # Inputs are multiples of 1/64 in [-2, 2): every product and partial sum is exact in f32.
+    from deers_b200 import ops
+    errs = ops.Context.current(torch.device("cuda", 0)).selftest_umma()
+    assert errs == [0.0, 0.0, 0.0, 0.0], errs
+
+
+@pytest.mark.parametrize("shape", [
+    (1, 1, 128, 64),
+    (1, 1, 128, 128),
+    (1, 2, 256, 128),
+    (2, 3, 384, 64),
+    (1, 2, 1, 64),       # single token
+    (1, 2, 100, 128),    # T below one tile
+    (1, 2, 130, 64),     # two rows into the second tile
+    (1, 1, 777, 128),    # ragged last tile
+])
+def test_forward_shapes(shape):
+    from deers_b200 import ops
+    from oracle import ref
+    from tests.gpu_util import make_inputs, to_dev
+    q, k, v, _ = make_inputs(*shape, torch.float16, seed=sum(shape))
+    want_o, want_lse = ref.attn_fwd(q, k, v)
+    o, lse = ops.attention_fwd(*(to_dev(a, torch.float16) for a in (q, k, v)), ops.default_scale(shape[3]))
+    ops.Context.current(o.device).sync()
+    assert_close(o.float().cpu().numpy(), want_o, TOL_F16, f"{shape}/o")
+    assert_close(lse.cpu().numpy(), want_lse, TOL_F16, f"{shape}/lse")
+
+
+def test_forward_noncausal_and_scale():
+    from deers_b200 import ops
+    from oracle import ref
+    from tests.gpu_util import make_inputs, to_dev
+    q, k, v, _ = make_inputs(1, 2, 300, 64, torch.float16, seed=21)
+    for scale, causal in ((0.2, True), (0.125, False)):
+        want_o, want_lse = ref.attn_fwd(q, k, v, scale=scale, causal=causal)
+        o, lse = ops.attention_fwd(*(to_dev(a, torch.float16) for a in (q, k, v)), scale, causal)
+        assert_close(o.float().cpu().numpy(), want_o, TOL_F16, "o")
+        assert_close(lse.cpu().numpy(), want_lse, TOL_F16, "lse")
+
+
+def test_forward_rescale_path():
+    # Keys whose scores grow along the sequence force the running max to jump by far
+    # more than 2^8 between tiles, exercising the in-TMEM rescale of O.
+    from deers_b200 import ops
+    from oracle import ref
+    from tests.gpu_util import to_dev
+    B, H, T, D = 1, 1, 512, 64
+    rng = np.random.default_rng(2)
+    q = np.abs(rng.standard_normal((B, H, T, D))).astype(np.float16).astype(np.float32)
+    k = np.abs(rng.standard_normal((B, H, T, D))).astype(np.float32)
+    k *= (1.0 + 6.0 * (np.arange(T) // 128))[None, None, :, None]
+    k = k.astype(np.float16).astype(np.float32)
+    v = rng.standard_normal((B, H, T, D)).astype(np.float16).astype(np.float32)
+    want_o, want_lse = ref.attn_fwd(q, k, v)
+    o, lse = ops.attention_fwd(*(to_dev(a, torch.float16) for a in (q, k, v)), ops.default_scale(D))
+    assert_close(o.float().cpu().numpy(), want_o, TOL_F16, "o")
+    assert_close(lse.cpu().numpy(), want_lse, TOL_F16, "lse")
+
+
+def test_cfg2_forward_backward():
+    # BASELINE config 2: f16, B=8, T=1024, H=12, head_dim=64; every slice checked.
+    from tests.gpu_util import check_case
+    check_case(8, 12, 1024, 64, torch.float16, TOL_F16, seed=0)
+
+
+@pytest.mark.parametrize("shape", [
+    (1, 1, 128, 64), (1, 1, 128, 128), (1, 2, 256, 128), (2, 2, 384, 64), (1, 2, 100, 128),
+    (1, 2, 130, 64), (1, 1, 777, 128), (1, 1, 1, 64),
+])
+def test_backward_shapes(shape):
+    from tests.gpu_util import check_case
+    check_case(*shape, torch.float16, TOL_F16, seed=sum(shape) + 1)
+
+
+def test_backward_noncausal():
+    from tests.gpu_util import check_case
+    check_case(1, 2, 300, 64, torch.float16, TOL_F16, seed=8, causal=False)
+
+
+def test_dk_dv_bitwise_reproducible():
+    from tests.gpu_util import make_inputs, run_fwd_bwd
+    args = make_inputs(2, 2, 640, 128, torch.float16, 9)
+    a = run_fwd_bwd(*args, torch.float16)
+    b = run_fwd_bwd(*args, torch.float16)
+    for idx in (0, 1, 3, 4):      # o, lse, dk, dv: no atomics anywhere on their path
+        assert np.array_equal(a[idx], b[idx])
+
+
+def _sampled_slices(B, H, T, D, n_random, seed):
+    """Full-size run on the device, oracle on a fixed sample of (b, h) slices."""
+    from deers_b200 import ops
+    from oracle import ref
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    q, k, v, do = (torch.randn(B, H, T, D, device="cuda", dtype=torch.float16, generator=g) for _ in range(4))
+    op = ops.CausalAttention.new(q, k, v)
+    o = op.forward()
+    grads = ops.GradientStore()
+    op.backward(grads, do)
+    ops.Context.current(q.device).sync()
+    rng = np.random.default_rng(seed)
+    picks = {(0, 0), (B - 1, H - 1)} | {(int(rng.integers(B)), int(rng.integers(H))) for _ in range(n_random)}
+    for b, h in sorted(picks):
+        host = [t[b:b + 1, h:h + 1].float().cpu().numpy() for t in (q, k, v, do)]
+        want = ref.attn_fwd_bwd(*host)
+        got = [o, op.lse, grads.get(q), grads.get(k), grads.get(v)]
+        for name, gt, w in zip(("o", "lse", "dq", "dk", "dv"), got, want):
+            assert_close(gt[b:b + 1, h:h + 1].float().cpu().numpy(), w, TOL_F16, f"slice({b},{h})/{name}")
+    # Size-independent properties over the whole tensor: finite everywhere, causal row 0 == v[0].
+    for t in (o, grads.get(q), grads.get(k), grads.get(v)):
+        assert torch.isfinite(t).all()
+    assert torch.allclose(o[:, :, 0].float(), v[:, :, 0].float(), atol=2e-3)
+
+
+def test_cfg4_long_context_sampled_slices():
+    # BASELINE config 4: B=2, T=8192, H=16, head_dim=128.
+    _sampled_slices(2, 16, 8192, 128, n_random=2, seed=4)
+
+
+def test_cfg5_shape_sampled_slices():
+    # BASELINE config 5 at full size on one GPU: B=64, T=2048, H=32, head_dim=128.
+    _sampled_slices(64, 32, 2048, 128, n_random=6, seed=5)

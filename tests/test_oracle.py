@@ -1,0 +1,82 @@
+"""CPU tests of the oracle: pinned mask values, golden vectors, and properties."""
+import numpy as np
+
+from oracle import ref
+from tests.helpers import TOL_F32, assert_close
+
+NEG = -np.inf
+
+
+def test_causal_mask_known_answer():
+    # Literal expected values of the reference's test (tests/nn.rs:194-218).
+    want = [0.0, NEG, NEG, 0.0, 0.0, NEG, 0.0, 0.0, 0.0] * 2
+    got = ref.causal_mask(2, 3, 0)
+    assert got.shape == (2, 1, 3, 3)
+    assert got.ravel().tolist() == want
+
+
+def test_causal_mask_with_offset_known_answer():
+    # tests/nn.rs:220-232
+    got = ref.causal_mask(1, 2, 3)
+    assert got.shape == (1, 1, 2, 5)
+    assert got.ravel().tolist() == [0.0, 0.0, 0.0, 0.0, NEG, 0.0, 0.0, 0.0, 0.0, 0.0]
+
+
+def test_oracle_matches_golden(golden):
+    for name, c in golden.items():
+        causal = bool(c["causal"])
+        o, lse, dq, dk, dv = ref.attn_fwd_bwd(c["q"], c["k"], c["v"], c["do"], causal=causal)
+        for label, got in (("o", o), ("lse", lse), ("dq", dq), ("dk", dk), ("dv", dv)):
+            assert_close(got, c[label], TOL_F32, f"{name}/{label}")
+        o2, lse2 = ref.attn_fwd(c["q"], c["k"], c["v"], causal=causal)
+        assert np.array_equal(o2, o) and np.array_equal(lse2, lse)
+
+
+def test_softmax_rows_known_inputs():
+    # The literal rows the reference feeds its softmax / log_sum_exp tests
+    # (tests/tensor.rs:296,1887,2119): with V = identity the op returns the softmax itself.
+    x = np.array([[1.0, 2.0, 3.0], [1.5, 0.5, -1.0]], np.float32)
+    T, D = 2, 3
+    # Build q, k so that q @ k^T = x on a non-causal 2 x 3 problem padded to square T=3.
+    q = np.zeros((1, 1, 3, 3), np.float32); q[0, 0, :2, :] = x
+    k = np.eye(3, dtype=np.float32)[None, None]
+    v = np.eye(3, dtype=np.float32)[None, None]
+    o, lse = ref.attn_fwd(q, k, v, scale=1.0, causal=False)
+    want = np.exp(x - x.max(1, keepdims=True)); want /= want.sum(1, keepdims=True)
+    assert np.abs(o[0, 0, :2] - want).max() < 1e-6
+    assert np.abs(lse[0, 0, :2] - np.log(np.exp(x.astype(np.float64)).sum(1))).max() < 1e-6
+
+
+def test_first_row_is_v0_and_rows_sum():
+    rng = np.random.default_rng(3)
+    q, k, v = (rng.standard_normal((2, 2, 9, 4)).astype(np.float32) for _ in range(3))
+    o, lse = ref.attn_fwd(q, k, v)
+    # Causal row 0 attends to key 0 only.
+    assert np.allclose(o[:, :, 0], v[:, :, 0], atol=1e-6)
+    # Linearity in V.
+    o2, _ = ref.attn_fwd(q, k, 2.0 * v)
+    assert np.allclose(o2, 2.0 * o, atol=1e-5)
+
+
+def test_gradients_by_finite_differences():
+    rng = np.random.default_rng(5)
+    B, H, T, D = 1, 1, 5, 4
+    q, k, v, do = (rng.standard_normal((B, H, T, D)) for _ in range(4))
+    _, _, dq, dk, dv = ref.attn_fwd_bwd(q, k, v, do)
+
+    def loss(q_, k_, v_):
+        q64, k64, v64 = (np.asarray(x, np.float64)[0, 0] for x in (q_, k_, v_))
+        s = q64 @ k64.T * ref.default_scale(D)
+        s = np.where(np.triu(np.ones((T, T), bool), 1), -np.inf, s)
+        p = np.exp(s - s.max(1, keepdims=True)); p /= p.sum(1, keepdims=True)
+        return float(((p @ v64) * do[0, 0]).sum())
+
+    eps = 1e-5
+    for name, x, g in (("q", q, dq), ("k", k, dk), ("v", v, dv)):
+        for idx in [(0, 0, 1, 2), (0, 0, 4, 0), (0, 0, 2, 3)]:
+            xp, xm = x.copy(), x.copy()
+            xp[idx] += eps; xm[idx] -= eps
+            args_p = {"q": q, "k": k, "v": v}; args_m = dict(args_p)
+            args_p[name] = xp; args_m[name] = xm
+            fd = (loss(args_p["q"], args_p["k"], args_p["v"]) - loss(args_m["q"], args_m["k"], args_m["v"])) / (2 * eps)
+            assert abs(fd - g[idx]) < 2e-3, (name, idx, fd, g[idx])
