@@ -192,9 +192,7 @@ static size_t delta_bytes(const deers_attn_desc* d) {
 
 extern "C" size_t deers_b200_attn_workspace_bytes(const deers_attn_desc* d, int pass) {
     if (check_desc(d) != DEERS_OK || pass == 0) return 0;
-    size_t n = delta_bytes(d);
-    if (d->dtype == DEERS_F16) n += attn_bwd_f16_dqacc_bytes(d);
-    return n;
+    return d->dtype == DEERS_F16 ? attn_bwd_f16_workspace_bytes(d) : delta_bytes(d);
 }
 
 extern "C" int deers_b200_attn_fwd(deers_ctx* ctx, const deers_attn_desc* d, const void* q,
@@ -237,13 +235,11 @@ extern "C" int deers_b200_attn_bwd(deers_ctx* ctx, const deers_attn_desc* d, con
     if (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 255u) != 0)
         return DEERS_ERR_WORKSPACE;
     DEERS_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
-    float* delta = (float*)workspace;
     if (d->dtype == DEERS_F32)
         return launch_attn_bwd_f32(ctx, d, (const float*)q, (const float*)k, (const float*)v,
                                    (const float*)o, lse, (const float*)d_o, (float*)dq, (float*)dk,
-                                   (float*)dv, delta);
-    float* dq_acc = (float*)((char*)workspace + delta_bytes(d));
-    return launch_attn_bwd_f16(ctx, d, q, k, v, o, lse, d_o, dq, dk, dv, delta, dq_acc);
+                                   (float*)dv, (float*)workspace);
+    return launch_attn_bwd_f16(ctx, d, q, k, v, o, lse, d_o, dq, dk, dv, workspace);
 }
 
 extern "C" int deers_b200_selftest_umma(deers_ctx* ctx, float* max_abs_err) {
