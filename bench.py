@@ -1,0 +1,368 @@
+#!/usr/bin/env python
+"""Benchmark of the causal-attention path: forward + backward TFLOP/s on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg5] [--impl ours|reference]
+
+One "step" is one forward + backward of the whole workload (for N > 1: of this
+rank's (batch x head) shard, plus the all-gather of O overlapped with the
+backward).  The default workload is the one the headline metric is quoted on:
+f16, B=64, T=2048, H=32, head_dim=128 (7.7 TFLOP per step counting causal FLOPs
+as 7*B*H*T^2*D).  Rank 0 prints ONE JSON line.
+
+  value      device-timed throughput with inputs resident in HBM (CUDA events, max over ranks)
+  e2e        same metric through the C ABI with HOST buffers: pinned host -> device copies of
+             Q, K, V, dO and device -> host copies of O, dQ, dK, dV inside the timed region
+  roofline   the dominant kernel (the backward main kernel) against the measured dense
+             tensor peak in MEASURED_PEAKS.json
+  cpu_baseline  the CPU oracle (a C restatement of the reference's CPU path) on a bounded
+             sample of (b, h) slices of the same workload, on this box's host cores
+
+--impl reference times that CPU restatement alone (the reference is Rust and cannot be
+built in this image), with all host threads, on a bounded sample per step.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (dtype, B, T, H, D)
+    "cfg1": ("f32", 4, 256, 6, 32),
+    "cfg2": ("f16", 8, 1024, 12, 64),
+    "cfg4": ("f16", 2, 8192, 16, 128),
+    "cfg5": ("f16", 64, 2048, 32, 128),
+}
+METRIC = "attn_fwd_bwd_tflops"
+UNIT = "TFLOP/s"
+
+
+def flops_fwd_bwd(n_slices: int, T: int, D: int) -> float:
+    """Causal fwd+bwd FLOPs, FlashAttention convention: 7 * slices * T^2 * D."""
+    return 7.0 * n_slices * T * T * D
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"tflops_burst": p["bf16_tflops"], "tflops_sustained": p.get("bf16_tflops_sustained", p["bf16_tflops"]),
+                "hbm_gbs": p["hbm_gbs"], "source": "measured"}
+    return {"tflops_burst": 1590.0, "tflops_sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, power, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0])); mx.append(float(parts[1])); power.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        # "under load": samples in the upper half of the power range seen
+        thr = (max(power) + min(power)) / 2
+        loaded = [c for c, w in zip(sm, power) if w >= thr] or sm
+        return {"sm_mhz": statistics.median(loaded), "sm_max_mhz": max(mx), "power_w_max": max(power),
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def cpu_baseline(T: int, D: int, n_slices: int, repeats: int):
+    """Times the CPU oracle (fwd + bwd, materialising, OpenMP over slices) on `n_slices` slices."""
+    import numpy as np
+    from oracle import ref
+    rng = np.random.default_rng(0)
+    base = min(n_slices, 32)
+    q, k, v, do = (np.tile(rng.standard_normal((base, 1, T, D), dtype=np.float32), (n_slices // base, 1, 1, 1))
+                   for _ in range(4))
+    n = q.shape[0]
+    best = None
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        ref.attn_fwd_bwd(q, k, v, do)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return {"value": flops_fwd_bwd(n, T, D) / best / 1e12, "unit": UNIT, "cores": ref.num_threads(), "kind": "port",
+            "sample": f"{n} of the workload's (b,h) slices at T={T}, D={D} ({base} distinct seeded N(0,1) slices "
+                      f"tiled), fwd+bwd, best of {repeats} runs, {best:.2f} s; f32 C restatement of the reference's "
+                      "CPU path (the Rust reference cannot be built here)",
+            "seconds": best}
+
+
+def cpu_sample_size(T: int, D: int, threads: int, target_s: float) -> int:
+    # ~0.6 s per (T=2048, D=128) slice per thread measured on a GPU box's host: scale by T^2 * D.
+    per = 0.6 * (T / 2048.0) ** 2 * (D / 128.0)
+    n = int(target_s * threads / max(per, 1e-6))
+    return max(threads, min(n, 4096))
+
+
+def run_reference(args, dtype, B, T, H, D):
+    """--impl reference: the CPU restatement alone, all host threads, bounded sample per step."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import ref
+    threads = ref.num_threads()
+    total_budget = 100.0                                    # seconds for the whole run
+    n = cpu_sample_size(T, D, threads, total_budget / (args.steps + args.warmup))
+    n = max(1, min(n, B * H))
+    import numpy as np
+    rng = np.random.default_rng(0)
+    base = min(n, 32)
+    n = n // base * base
+    q, k, v, do = (np.tile(rng.standard_normal((base, 1, T, D), dtype=np.float32), (n // base, 1, 1, 1))
+                   for _ in range(4))
+    for _ in range(args.warmup):
+        ref.attn_fwd_bwd(q, k, v, do)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        ref.attn_fwd_bwd(q, k, v, do)
+    dt = (time.perf_counter() - t0) / args.steps
+    val = flops_fwd_bwd(n, T, D) / dt / 1e12
+    sample = (f"{n} of {B * H} (b,h) slices per step (f32 C restatement of the reference CPU path; the workload's "
+              f"f16 inputs as f32), {threads} threads")
+    line = {"impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": workload_name(args.workload, dtype, B, T, H, D), "sample": sample},
+            "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+            "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def workload_name(name, dtype, B, T, H, D):
+    return f"{name}: causal attention fwd+bwd, {dtype}, B={B} T={T} H={H} head_dim={D}, scale 1/sqrt(D)"
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", default="cfg5", choices=sorted(WORKLOADS))
+    ap.add_argument("--shape", default=None, help="B,T,H,D: a custom shape (profiling captures on a small case)")
+    ap.add_argument("--dtype", default=None, choices=["f16", "f32"], help="dtype for --shape")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--gather", default="overlap", choices=["overlap", "none"],
+                    help="N>1: all-gather O over NCCL on a side stream (overlap) or keep O sharded (none)")
+    ap.add_argument("--e2e-steps", type=int, default=5)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    dtype, B, T, H, D = WORKLOADS[args.workload]
+    if args.shape:
+        B, T, H, D = (int(x) for x in args.shape.split(","))
+        dtype = args.dtype or "f16"
+        args.workload = "custom"
+    if args.impl == "reference":
+        run_reference(args, dtype, B, T, H, D)
+        return
+
+    import torch
+    import torch.distributed as dist
+    from deers_b200 import _lib, ops, shard
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run (one rank per GPU)")
+        args.gpus = world
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a B200: there is no CPU fallback for the attention path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    tdtype = torch.float16 if dtype == "f16" else torch.float32
+    esize = 2 if dtype == "f16" else 4
+    n_total = B * H
+    begin, end = shard.partition(n_total, world, rank)
+    n_local = end - begin
+    Bs, Hs = shard.shard_shape(B, H, world, rank)
+    scale = ops.default_scale(D)
+
+    gen = torch.Generator(device=dev).manual_seed(1234 + rank)
+    q, k, v, do = (torch.randn(Bs, Hs, T, D, device=dev, dtype=torch.float32, generator=gen).to(tdtype)
+                   for _ in range(4))
+    ctx = ops.Context.current(dev)
+    ws_bytes = ops.workspace_bytes(q, scale)
+    workspace = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=dev)
+    gatherer = None
+    if world > 1 and args.gather == "overlap":
+        gatherer = shard.OverlappedGather(n_total, T, D, tdtype, dev)
+
+    def step():
+        o, lse = ops.attention_fwd(q, k, v, scale, True)
+        if gatherer is not None:
+            gatherer.start(o)
+        grads = ops.attention_bwd(q, k, v, o, lse, do, scale, True, workspace=workspace)
+        if gatherer is not None:
+            gatherer.finish()
+        return o, grads
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local) if rank == 0 else None     # started early: nvidia-smi needs a moment
+    for _ in range(args.warmup):
+        step()
+    barrier()
+
+    ctx.kernel_timing(True)
+    launches0 = ctx.launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    ev0.record()
+    for _ in range(args.steps):
+        step()
+    ev1.record()
+    barrier()
+    ms = ev0.elapsed_time(ev1) / args.steps
+    launches = ctx.launch_count() - launches0
+    ktimes = {name: ctx.kernel_time(kind) for name, kind in
+              (("fwd", _lib.K_FWD), ("bwd_prep", _lib.K_BWD_PREP), ("bwd_main", _lib.K_BWD_MAIN),
+               ("bwd_dq", _lib.K_BWD_DQ))}
+    ctx.kernel_timing(False)
+    ctx.sync()
+    clocks = sampler.stop() if sampler else None
+
+    ms_t = torch.tensor([ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(ms_t, op=dist.ReduceOp.MAX)
+    ms_max = float(ms_t.item())
+    total_flops = flops_fwd_bwd(n_total, T, D)
+    value = total_flops / (ms_max * 1e-3) / 1e12
+
+    # ---- e2e: host buffers through the C ABI, copies inside the timed region ----
+    e2e = None
+    if not args.no_e2e:
+        L = _lib.lib()
+        host_in = [torch.empty(t.shape, dtype=tdtype, pin_memory=True) for t in (q, k, v, do)]
+        for h_, d_ in zip(host_in, (q, k, v, do)):
+            h_.copy_(d_)
+        host_out = [torch.empty(q.shape, dtype=tdtype, pin_memory=True) for _ in range(4)]
+        nbytes = q.numel() * esize
+
+        def e2e_step():
+            for h_, d_ in zip(host_in, (q, k, v, do)):
+                _lib.check(L.deers_b200_memcpy_h2d(ctx.handle, d_.data_ptr(), h_.data_ptr(), nbytes), ctx.handle)
+            o, (dq, dk, dv) = step()
+            for h_, d_ in zip(host_out, (o, dq, dk, dv)):
+                _lib.check(L.deers_b200_memcpy_d2h(ctx.handle, h_.data_ptr(), d_.data_ptr(), nbytes), ctx.handle)
+
+        e2e_step()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.e2e_steps):
+            e2e_step()
+        e1.record()
+        barrier()
+        e_ms = torch.tensor([e0.elapsed_time(e1) / args.e2e_steps], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(e_ms, op=dist.ReduceOp.MAX)
+        e2e = {"value": total_flops / (float(e_ms.item()) * 1e-3) / 1e12, "unit": UNIT,
+               "h2d_bytes_per_step": 4 * nbytes, "d2h_bytes_per_step": 4 * nbytes,
+               "ms_per_step": float(e_ms.item()), "steps": args.e2e_steps,
+               "api": "deers_b200_memcpy_h2d x4 -> attn_fwd -> attn_bwd -> deers_b200_memcpy_d2h x4 (pinned host buffers)"}
+        del host_in, host_out
+
+    if rank == 0:
+        peaks = load_peaks()
+        bwd_ms, bwd_n = ktimes["bwd_main"]
+        bwd_avg = bwd_ms / max(bwd_n, 1)
+        bwd_flops = 5.0 * n_local * T * T * D               # the 5 GEMMs of the backward, causal-counted
+        peak = peaks["tflops_sustained"] if dtype == "f16" else None
+        roofline = None
+        if dtype == "f16":
+            achieved = bwd_flops / (bwd_avg * 1e-3) / 1e12
+            roofline = {"bound": "tensor", "kernel": "attn_bwd_f16_kernel", "achieved": achieved, "peak": peak,
+                        "unit": UNIT, "frac": achieved / peak, "traffic": None,
+                        "peak_source": f"{peaks['source']} sustained bf16 (kernel timed inside a long step)",
+                        "avg_launch_ms": bwd_avg}
+        else:
+            # f32 FFMA path at this size is HBM/latency bound: algorithmic bytes of the whole step.
+            alg_bytes = 12.0 * n_local * T * D * esize + 3.0 * n_local * T * 4
+            kms = sum(v_[0] for v_ in ktimes.values()) / max(args.steps, 1)
+            achieved = alg_bytes / (kms * 1e-3) / 1e9
+            roofline = {"bound": "hbm", "kernel": "attn f32 fwd + bwd kernels", "achieved": achieved,
+                        "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "traffic": None,
+                        "peak_source": f"{peaks['source']} copy bandwidth"}
+        fwd_ms, fwd_n = ktimes["fwd"]
+        kernels = {name: {"launches": n_, "avg_ms": (ms_ / n_ if n_ else None)} for name, (ms_, n_) in ktimes.items()}
+        if dtype == "f16" and fwd_n:
+            kernels["fwd"]["tflops"] = 2.0 * n_local * T * T * D / (fwd_ms / fwd_n * 1e-3) / 1e12
+        cb = None
+        if not args.no_cpu_baseline:
+            from oracle import ref
+            threads = ref.num_threads()
+            n_cpu = cpu_sample_size(T, D, threads, 12.0)
+            n_cpu = max(1, min(n_cpu, n_total))
+            n_cpu = max(32, n_cpu // 32 * 32) if n_cpu >= 32 else n_cpu
+            cb = cpu_baseline(T, D, n_cpu, repeats=1)
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms_max, "higher_is_better": True, "scaling": "strong",
+                "vs_baseline": None, "dtype": dtype, "data": "synthetic",
+                "config": {"workload": workload_name(args.workload, dtype, B, T, H, D),
+                           "flops_per_step": total_flops, "flop_convention": "7*B*H*T^2*D (causal fwd 2, bwd 5)",
+                           "parallelism": f"(b x h) shards over {world} GPU(s), {n_local} slices on rank 0",
+                           "gather": (args.gather if world > 1 else "n/a (1 GPU)"),
+                           "l2": "inputs larger than L2 (no flush needed)" if 4 * q.numel() * esize > 126e6
+                                 else "inputs fit in L2 (not flushed)",
+                           "frac_of_dense_peak": value / world / peaks["tflops_sustained"],
+                           "peak_tflops": peaks["tflops_sustained"], "peak_source": peaks["source"]},
+                "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "roofline": roofline,
+                "kernels": kernels, "cpu_baseline": cb}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

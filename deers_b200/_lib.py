@@ -18,8 +18,10 @@ SYMBOLS = [
     "deers_b200_stream", "deers_b200_alloc", "deers_b200_free", "deers_b200_memcpy_h2d",
     "deers_b200_memcpy_d2h", "deers_b200_memcpy_d2d", "deers_b200_sync", "deers_b200_attn_workspace_bytes",
     "deers_b200_attn_fwd", "deers_b200_attn_bwd", "deers_b200_status_string", "deers_b200_last_error",
-    "deers_b200_launch_count", "deers_b200_selftest_umma",
+    "deers_b200_launch_count", "deers_b200_selftest_umma", "deers_b200_kernel_timing",
+    "deers_b200_kernel_time",
 ]
+K_FWD, K_BWD_PREP, K_BWD_MAIN, K_BWD_DQ = range(4)
 
 
 class AttnDesc(ctypes.Structure):
@@ -70,6 +72,9 @@ def lib() -> ctypes.CDLL:
     L.deers_b200_launch_count.argtypes = [vp]
     L.deers_b200_launch_count.restype = ctypes.c_uint64
     L.deers_b200_selftest_umma.argtypes = [vp, ctypes.POINTER(ctypes.c_float)]
+    L.deers_b200_kernel_timing.argtypes = [vp, i32]
+    L.deers_b200_kernel_time.argtypes = [vp, i32, i32, ctypes.POINTER(ctypes.c_double),
+                                         ctypes.POINTER(ctypes.c_uint64)]
     _lib = L
     return L
 

@@ -384,9 +384,12 @@ int bwd_launch(deers_ctx* ctx, const deers_attn_desc* d, const void* q, const vo
     float* dq_acc = (float*)((char*)workspace + 2 * stat_bytes);
 
     const long long prep_rows = BH * Tpad;
-    attn_bwd_prep_f16_kernel<D><<<(unsigned)((prep_rows + 7) / 8), 256, 0, ctx->stream>>>(
-        (const __half*)o, (const __half*)d_o, lse, delta, lse2, dq_acc, d->B, d->H, d->T, Tpad, d->o_strides[0], d->o_strides[1],
-        d->o_strides[2], d->do_strides[0], d->do_strides[1], d->do_strides[2]);
+    {
+        KernelTimerScope ts(ctx, DEERS_K_BWD_PREP);
+        attn_bwd_prep_f16_kernel<D><<<(unsigned)((prep_rows + 7) / 8), 256, 0, ctx->stream>>>(
+            (const __half*)o, (const __half*)d_o, lse, delta, lse2, dq_acc, d->B, d->H, d->T, Tpad, d->o_strides[0],
+            d->o_strides[1], d->o_strides[2], d->do_strides[0], d->do_strides[1], d->do_strides[2]);
+    }
     DEERS_CUDA_TRY(ctx, cudaGetLastError());
 
     BwdParams p;
@@ -400,12 +403,18 @@ int bwd_launch(deers_ctx* ctx, const deers_attn_desc* d, const void* q, const vo
     DEERS_CUDA_TRY(ctx, cudaFuncSetAttribute(attn_bwd_f16_kernel<D, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const long long grid = BH * nq;
     if (grid > 0x7fffffffLL) return DEERS_ERR_SHAPE;
-    attn_bwd_f16_kernel<D, STAGES><<<(unsigned)grid, 192, smem, ctx->stream>>>(tq, tk, tv, tdo, p);
+    {
+        KernelTimerScope ts(ctx, DEERS_K_BWD_MAIN);
+        attn_bwd_f16_kernel<D, STAGES><<<(unsigned)grid, 192, smem, ctx->stream>>>(tq, tk, tv, tdo, p);
+    }
     DEERS_CUDA_TRY(ctx, cudaGetLastError());
 
     const long long total = BH * d->T * (D / 8);
-    attn_bwd_dq_convert_kernel<D><<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(
-        dq_acc, (__half*)dq, d->B, d->H, d->T, Tpad, d->scale, d->dq_strides[0], d->dq_strides[1], d->dq_strides[2]);
+    {
+        KernelTimerScope ts(ctx, DEERS_K_BWD_DQ);
+        attn_bwd_dq_convert_kernel<D><<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(
+            dq_acc, (__half*)dq, d->B, d->H, d->T, Tpad, d->scale, d->dq_strides[0], d->dq_strides[1], d->dq_strides[2]);
+    }
     DEERS_CUDA_TRY(ctx, cudaGetLastError());
     ctx->launches += 3;
     return DEERS_OK;

@@ -443,7 +443,10 @@ int fwd_impl(deers_ctx* ctx, const F32Params& p) {
     int rc = set_smem(ctx, attn_fwd_f32_kernel<DP>, smem);
     if (rc) return rc;
     dim3 grid((p.T + BM - 1) / BM, p.B * p.H);
-    attn_fwd_f32_kernel<DP><<<grid, NT, smem, ctx->stream>>>(p);
+    {
+        KernelTimerScope ts(ctx, DEERS_K_FWD);
+        attn_fwd_f32_kernel<DP><<<grid, NT, smem, ctx->stream>>>(p);
+    }
     ctx->launches += 1;
     DEERS_CUDA_TRY(ctx, cudaGetLastError());
     return DEERS_OK;
@@ -452,7 +455,10 @@ int fwd_impl(deers_ctx* ctx, const F32Params& p) {
 template <int DP>
 int bwd_impl(deers_ctx* ctx, const F32Params& p) {
     const long long rows = (long long)p.B * p.H * p.T;
-    attn_delta_f32_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, ctx->stream>>>(p);
+    {
+        KernelTimerScope ts(ctx, DEERS_K_BWD_PREP);
+        attn_delta_f32_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, ctx->stream>>>(p);
+    }
     DEERS_CUDA_TRY(ctx, cudaGetLastError());
     const size_t smem_kv = (size_t)(4 * BM * (DP + 4) + 2 * BM * PLD + 2 * BM) * sizeof(float);
     const size_t smem_q = (size_t)(4 * BM * (DP + 4) + BM * PLD + 2 * BM) * sizeof(float);
@@ -461,9 +467,15 @@ int bwd_impl(deers_ctx* ctx, const F32Params& p) {
     rc = set_smem(ctx, attn_bwd_dq_f32_kernel<DP>, smem_q);
     if (rc) return rc;
     dim3 grid((p.T + BM - 1) / BM, p.B * p.H);
-    attn_bwd_dkdv_f32_kernel<DP><<<grid, NT, smem_kv, ctx->stream>>>(p);
+    {
+        KernelTimerScope ts(ctx, DEERS_K_BWD_MAIN);
+        attn_bwd_dkdv_f32_kernel<DP><<<grid, NT, smem_kv, ctx->stream>>>(p);
+    }
     DEERS_CUDA_TRY(ctx, cudaGetLastError());
-    attn_bwd_dq_f32_kernel<DP><<<grid, NT, smem_q, ctx->stream>>>(p);
+    {
+        KernelTimerScope ts(ctx, DEERS_K_BWD_DQ);
+        attn_bwd_dq_f32_kernel<DP><<<grid, NT, smem_q, ctx->stream>>>(p);
+    }
     DEERS_CUDA_TRY(ctx, cudaGetLastError());
     ctx->launches += 3;
     return DEERS_OK;

@@ -306,7 +306,10 @@ int fwd_launch(deers_ctx* ctx, const deers_attn_desc* d, const void* q, const vo
     const long long nq = (d->T + BM - 1) / BM;
     const long long grid = nq * d->B * d->H;
     if (grid > 0x7fffffffLL) return DEERS_ERR_SHAPE;
-    attn_fwd_f16_kernel<D><<<(unsigned)grid, 192, smem, ctx->stream>>>(tq, tk, tv, p);
+    {
+        KernelTimerScope ts(ctx, DEERS_K_FWD);
+        attn_fwd_f16_kernel<D><<<(unsigned)grid, 192, smem, ctx->stream>>>(tq, tk, tv, p);
+    }
     ctx->launches += 1;
     DEERS_CUDA_TRY(ctx, cudaGetLastError());
     return DEERS_OK;

@@ -9,13 +9,23 @@
 
 #include "../../include/deers_b200.h"
 
+constexpr int DEERS_KT_RING = 512;
+
+struct deers_ktimer {
+    cudaEvent_t* start;     // DEERS_KT_RING events each, created when timing is first enabled
+    cudaEvent_t* stop;
+    int pending;            // recorded pairs not yet folded into total_ms
+    double total_ms;
+    uint64_t launches;
+};
+
 struct deers_ctx {
     int device;
     cudaStream_t stream;
     bool owns_stream;
     int sm_count;
-    // Error word the kernels write when a bounded wait gives up.  Pinned, mapped
-    // host memory: the kernels use dev_err, the host reads host_err after a sync.
+    // Error word the kernels write when a bounded wait gives up: dev_err in device
+    // memory, host_err its pinned host mirror, refreshed by deers_b200_sync().
     unsigned int* host_err;
     unsigned int* dev_err;
     uint64_t launches;
@@ -23,6 +33,26 @@ struct deers_ctx {
     // cuTensorMapEncodeTiled, fetched through the runtime so that the library
     // does not link against the driver.
     void* encode_tiled;
+    bool timing;
+    deers_ktimer kt[DEERS_K_COUNT];
+};
+
+// Brackets one kernel launch with events when timing is on.  A full ring drops the sample.
+struct KernelTimerScope {
+    deers_ctx* ctx;
+    deers_ktimer* t;
+    KernelTimerScope(deers_ctx* c, int kind) : ctx(c), t(nullptr) {
+        if (c->timing && c->kt[kind].start && c->kt[kind].pending < DEERS_KT_RING) {
+            t = &c->kt[kind];
+            cudaEventRecord(t->start[t->pending], c->stream);
+        }
+    }
+    ~KernelTimerScope() {
+        if (t) {
+            cudaEventRecord(t->stop[t->pending], ctx->stream);
+            t->pending += 1;
+        }
+    }
 };
 
 #define DEERS_CUDA_TRY(ctx, expr)                                                            \

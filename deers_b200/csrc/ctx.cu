@@ -65,9 +65,14 @@ extern "C" int deers_b200_init(int device_ordinal, void* stream, deers_ctx** out
         }
         ctx->owns_stream = true;
     }
-    if (cudaHostAlloc((void**)&ctx->host_err, sizeof(unsigned int), cudaHostAllocMapped) != cudaSuccess ||
-        cudaHostGetDevicePointer((void**)&ctx->dev_err, ctx->host_err, 0) != cudaSuccess) {
+    // The error word lives in device memory (every CTA reads it once at start-up; a
+    // host-mapped word would cost each of them a PCIe round trip) with a pinned host
+    // mirror that sync() refreshes.
+    if (cudaHostAlloc((void**)&ctx->host_err, sizeof(unsigned int), cudaHostAllocDefault) != cudaSuccess ||
+        cudaMalloc((void**)&ctx->dev_err, sizeof(unsigned int)) != cudaSuccess ||
+        cudaMemset(ctx->dev_err, 0, sizeof(unsigned int)) != cudaSuccess) {
         if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
+        if (ctx->host_err) cudaFreeHost(ctx->host_err);
         delete ctx;
         return DEERS_ERR_CUDA;
     }
@@ -88,6 +93,14 @@ extern "C" void deers_b200_destroy(deers_ctx* ctx) {
     cudaStreamSynchronize(ctx->stream);
     if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
     if (ctx->host_err) cudaFreeHost(ctx->host_err);
+    if (ctx->dev_err) cudaFree(ctx->dev_err);
+    for (int k = 0; k < DEERS_K_COUNT; ++k) {
+        deers_ktimer* t = &ctx->kt[k];
+        if (t->start && t->stop)
+            for (int i = 0; i < DEERS_KT_RING; ++i) { cudaEventDestroy(t->start[i]); cudaEventDestroy(t->stop[i]); }
+        delete[] t->start;
+        delete[] t->stop;
+    }
     delete ctx;
 }
 
@@ -140,10 +153,13 @@ extern "C" int deers_b200_memcpy_d2d(deers_ctx* ctx, void* dst, const void* src,
 
 extern "C" int deers_b200_sync(deers_ctx* ctx) {
     if (!ctx) return DEERS_ERR_NULL;
+    DEERS_CUDA_TRY(ctx, cudaMemcpyAsync(ctx->host_err, ctx->dev_err, sizeof(unsigned int), cudaMemcpyDeviceToHost,
+                                        ctx->stream));
     DEERS_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
     const unsigned int e = *(volatile unsigned int*)ctx->host_err;
     if (e != 0) {
         *(volatile unsigned int*)ctx->host_err = 0;
+        DEERS_CUDA_TRY(ctx, cudaMemsetAsync(ctx->dev_err, 0, sizeof(unsigned int), ctx->stream));
         snprintf(ctx->last_error, sizeof(ctx->last_error),
                  "kernel error word 0x%x (kernel family 0x%x, wait id %u)", e, e & 0xf00u, e & 0xffu);
         return DEERS_ERR_KERNEL;
@@ -240,6 +256,52 @@ extern "C" int deers_b200_attn_bwd(deers_ctx* ctx, const deers_attn_desc* d, con
                                    (const float*)o, lse, (const float*)d_o, (float*)dq, (float*)dk,
                                    (float*)dv, (float*)workspace);
     return launch_attn_bwd_f16(ctx, d, q, k, v, o, lse, d_o, dq, dk, dv, workspace);
+}
+
+static int drain_timer(deers_ctx* ctx, deers_ktimer* t) {
+    for (int i = 0; i < t->pending; ++i) {
+        float ms = 0.f;
+        DEERS_CUDA_TRY(ctx, cudaEventElapsedTime(&ms, t->start[i], t->stop[i]));
+        t->total_ms += ms;
+        t->launches += 1;
+    }
+    t->pending = 0;
+    return DEERS_OK;
+}
+
+extern "C" int deers_b200_kernel_timing(deers_ctx* ctx, int enable) {
+    if (!ctx) return DEERS_ERR_NULL;
+    DEERS_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    if (enable) {
+        for (int k = 0; k < DEERS_K_COUNT; ++k) {
+            deers_ktimer* t = &ctx->kt[k];
+            if (!t->start) {
+                t->start = new (std::nothrow) cudaEvent_t[DEERS_KT_RING];
+                t->stop = new (std::nothrow) cudaEvent_t[DEERS_KT_RING];
+                if (!t->start || !t->stop) return DEERS_ERR_CUDA;
+                for (int i = 0; i < DEERS_KT_RING; ++i) {
+                    DEERS_CUDA_TRY(ctx, cudaEventCreate(&t->start[i]));
+                    DEERS_CUDA_TRY(ctx, cudaEventCreate(&t->stop[i]));
+                }
+            }
+            t->pending = 0; t->total_ms = 0.0; t->launches = 0;
+        }
+    }
+    ctx->timing = enable != 0;
+    return DEERS_OK;
+}
+
+extern "C" int deers_b200_kernel_time(deers_ctx* ctx, int kind, int reset, double* total_ms, uint64_t* launches) {
+    if (!ctx || !total_ms || !launches) return DEERS_ERR_NULL;
+    if (kind < 0 || kind >= DEERS_K_COUNT) return DEERS_ERR_SHAPE;
+    DEERS_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    deers_ktimer* t = &ctx->kt[kind];
+    int rc = drain_timer(ctx, t);
+    if (rc) return rc;
+    *total_ms = t->total_ms;
+    *launches = t->launches;
+    if (reset) { t->total_ms = 0.0; t->launches = 0; }
+    return DEERS_OK;
 }
 
 extern "C" int deers_b200_selftest_umma(deers_ctx* ctx, float* max_abs_err) {

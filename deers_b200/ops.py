@@ -35,6 +35,9 @@ class Context:
     def __init__(self, device: int, stream_ptr: int):
         self.handle = ctypes.c_void_p()
         self.device = device
+        # torch's default stream is the legacy NULL stream; the C ABI reads NULL as "create
+        # your own stream", so name the legacy stream by its CUDA handle value 1.
+        stream_ptr = stream_ptr or 1
         _lib.check(_lib.lib().deers_b200_init(device, ctypes.c_void_p(stream_ptr), ctypes.byref(self.handle)))
 
     @classmethod
@@ -56,6 +59,16 @@ class Context:
 
     def launch_count(self) -> int:
         return int(_lib.lib().deers_b200_launch_count(self.handle))
+
+    def kernel_timing(self, enable: bool) -> None:
+        _lib.check(_lib.lib().deers_b200_kernel_timing(self.handle, int(enable)), self.handle)
+
+    def kernel_time(self, kind: int, reset: bool = False):
+        """(total milliseconds, launches) of one kernel kind since timing was enabled."""
+        ms, n = ctypes.c_double(), ctypes.c_uint64()
+        _lib.check(_lib.lib().deers_b200_kernel_time(self.handle, kind, int(reset), ctypes.byref(ms),
+                                                     ctypes.byref(n)), self.handle)
+        return ms.value, int(n.value)
 
     def selftest_umma(self) -> List[float]:
         errs = (ctypes.c_float * 4)()

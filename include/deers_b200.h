@@ -86,7 +86,8 @@ void deers_b200_attn_desc_compact(deers_attn_desc* desc, int32_t B, int32_t H, i
  * stream, module, cuBLAS), with a device ordinal added so that one process per
  * GPU can shard (batch x head) slices.  `stream` may be NULL (the context then
  * creates its own non-blocking stream) or an existing cudaStream_t to enqueue on
- * (the reference's single default stream, `src/storage/cuda.rs:505`).
+ * (the reference's single default stream, `src/storage/cuda.rs:505`); pass
+ * cudaStreamLegacy to name the legacy default stream.
  */
 int deers_b200_init(int device_ordinal, void* stream, deers_ctx** out);
 void deers_b200_destroy(deers_ctx* ctx);
@@ -153,6 +154,18 @@ const char* deers_b200_last_error(deers_ctx* ctx);
  * counts launches per op in its profiler, `src/profiler.rs:160-224`).
  */
 uint64_t deers_b200_launch_count(deers_ctx* ctx);
+
+/*
+ * Per-kernel device timing, the counterpart of the reference's profiler hook that
+ * brackets every launch with two CUDA events (`src/storage/cuda.rs:530-561`).
+ * While enabled, each launch of the attention path is bracketed by events on the
+ * context's stream.  kernel_time() synchronises the stream and returns the total
+ * milliseconds and the number of launches of one kernel kind since timing was
+ * enabled (or since the last call with reset != 0).
+ */
+enum { DEERS_K_FWD = 0, DEERS_K_BWD_PREP = 1, DEERS_K_BWD_MAIN = 2, DEERS_K_BWD_DQ = 3, DEERS_K_COUNT = 4 };
+int deers_b200_kernel_timing(deers_ctx* ctx, int enable);
+int deers_b200_kernel_time(deers_ctx* ctx, int kind, int reset, double* total_ms, uint64_t* launches);
 
 /*
  * Tensor-core self-test: runs one small tcgen05 GEMM per operand layout the f16
