@@ -86,10 +86,15 @@ attn_bwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     __shared__ __align__(16) float lse2_s[STAGES][BT], delta_s[STAGES][BT];
 
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-    const int BH = p.B * p.H;
     const int nq = (p.T + BT - 1) / BT;
-    const int kt = (int)(blockIdx.x / BH);                  // low KV tiles (most work) first
-    const int bh = (int)(blockIdx.x % BH);
+    // Launch order: groups of 16 slices; inside a group the low KV tiles (most work) of all its
+    // slices come first, and the group's Q, dO and dQ accumulator stay in L2 while it runs.
+    const int BH = p.B * p.H;
+    const int group = (int)(blockIdx.x / (16u * nq));
+    const int gsize = min(16, BH - group * 16);
+    const int within = (int)(blockIdx.x - (unsigned)group * 16u * nq);
+    const int kt = within / gsize;
+    const int bh = group * 16 + within % gsize;
     const int b = bh / p.H, h = bh % p.H;
     const int k0 = kt * BT;
     const int i0 = p.causal ? kt : 0;

@@ -63,10 +63,15 @@ attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     __shared__ uint32_t tmem_base_s, abort_s, skip_s;
 
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-    const int BH = p.B * p.H;
     const int nq = (p.T + BM - 1) / BM;
-    const int qt = nq - 1 - (int)(blockIdx.x / BH);       // heavy (late) query tiles first
-    const int bh = (int)(blockIdx.x % BH);
+    // Launch order: groups of 16 slices; inside a group the heaviest tiles of all its slices
+    // come first (balance), and the group's K and V (a few MB) fit in L2 together.
+    const int BH = p.B * p.H;
+    const int group = (int)(blockIdx.x / (16u * nq));
+    const int gsize = min(16, BH - group * 16);
+    const int within = (int)(blockIdx.x - (unsigned)group * 16u * nq);
+    const int qt = nq - 1 - within / gsize;
+    const int bh = group * 16 + within % gsize;
     const int b = bh / p.H, h = bh % p.H;
     const int q0 = qt * BM;
     const int ntiles = p.causal ? qt + 1 : (p.T + BN - 1) / BN;

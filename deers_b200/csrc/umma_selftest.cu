@@ -1,9 +1,10 @@
 // Self-test of the tcgen05 operand layouts the f16 attention kernels rely on.
 // One CTA multiplies a 128 x 128 (f16) A by a 128 x N B into TMEM and writes the
-// f32 product out; the host compares with its own product.  The four cases cover
+// f32 product out; the host compares with its own product.  The cases cover
 // TMA-written K-major operands (Q K^T), thread-written K-major A with an
-// MN-major B (P V), MN-major A and B (the transposed products of the backward)
-// and the N = 64 shapes of head_dim 64.
+// MN-major B (P V), MN-major A and B (the transposed products of the backward),
+// the N = 64 shapes of head_dim 64, and an A operand that threads stored into
+// TMEM (P^T kept in tensor memory for dV += P^T dO).
 #include "sm100_ptx.cuh"
 #include "tma_host.cuh"
 
@@ -19,7 +20,7 @@ struct SelftestParams {
     float* out;               // [128][N]
     unsigned int* err;
     int N;
-    int a_mn, b_mn, a_manual;
+    int a_mn, b_mn, a_manual;  // a_manual: 1 = threads write A into shared memory, 2 = into TMEM
 };
 
 constexpr int ST_K = 128;
@@ -45,7 +46,7 @@ __global__ void __launch_bounds__(128) umma_selftest_kernel(const __grid_constan
     }
     __syncwarp();
     if (warp == 0) {
-        tmem_alloc(&tmem_base_s, 128);
+        tmem_alloc(&tmem_base_s, 256);
         tmem_relinquish();
     }
     tc_fence_before_sync();
@@ -53,7 +54,19 @@ __global__ void __launch_bounds__(128) umma_selftest_kernel(const __grid_constan
     tc_fence_after_sync();
     const uint32_t tmem = tmem_base_s;
 
-    if (p.a_manual) {
+    if (p.a_manual == 2) {
+        // Thread r writes row r of A into TMEM lane r, columns 128..191: two f16 per 32-bit column.
+        const uint32_t* src = reinterpret_cast<const uint32_t*>(p.a_global + (size_t)threadIdx.x * ST_K);
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+            uint32_t r[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = src[c * 32 + i];
+            tmem_st_x32(tmem + ((uint32_t)(warp * 32) << 16) + 128u + (uint32_t)c * 32u, r);
+        }
+        tmem_wait_st();
+        tc_fence_before_sync();
+    } else if (p.a_manual) {
         // Thread r writes row r of A (K-major): 16 chunks of 8 f16 into two 64-column blocks.
         const int r = threadIdx.x;
         const uint4* src = reinterpret_cast<const uint4*>(p.a_global + (size_t)r * ST_K);
@@ -85,7 +98,8 @@ __global__ void __launch_bounds__(128) umma_selftest_kernel(const __grid_constan
             for (int ks = 0; ks < ST_K / 16; ++ks) {
                 const uint64_t da = p.a_mn ? desc_mnmajor(smem_u32(sA), ks, 16384u) : desc_kmajor(smem_u32(sA), ks, 16384u);
                 const uint64_t db = p.b_mn ? desc_mnmajor(smem_u32(sB), ks, b_block) : desc_kmajor(smem_u32(sB), ks, b_block);
-                umma_ss(tmem, da, db, idesc, ks > 0);
+                if (p.a_manual == 2) umma_ts(tmem, tmem + 128u + (uint32_t)ks * 8u, db, idesc, ks > 0);
+                else umma_ss(tmem, da, db, idesc, ks > 0);
             }
         }
         umma_commit(&bar_mma);
@@ -105,7 +119,7 @@ __global__ void __launch_bounds__(128) umma_selftest_kernel(const __grid_constan
     }
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 0) tmem_dealloc(tmem, 128);
+    if (warp == 0) tmem_dealloc(tmem, 256);
 }
 
 int make_tmap_2d(deers_ctx* ctx, CUtensorMap* out, const __half* base, int rows, int cols, int box_rows) {
@@ -118,8 +132,9 @@ int make_tmap_2d(deers_ctx* ctx, CUtensorMap* out, const __half* base, int rows,
 int run_selftest_umma(deers_ctx* ctx, float* max_abs_err) {
     const int M = 128, K = ST_K;
     struct Case { int N, a_mn, b_mn, a_manual; };
-    const Case cases[4] = {{128, 0, 0, 0}, {128, 0, 1, 1}, {128, 1, 1, 0}, {64, 0, 1, 0}};
-    for (int i = 0; i < 4; ++i) max_abs_err[i] = INFINITY;
+    const Case cases[DEERS_SELFTEST_CASES] = {{128, 0, 0, 0}, {128, 0, 1, 1}, {128, 1, 1, 0}, {64, 0, 1, 0},
+                                              {128, 0, 1, 2}, {64, 0, 0, 2}};
+    for (int i = 0; i < DEERS_SELFTEST_CASES; ++i) max_abs_err[i] = INFINITY;
 
     __half *dA = nullptr, *dB = nullptr;
     float* dO = nullptr;
@@ -130,7 +145,7 @@ int run_selftest_umma(deers_ctx* ctx, float* max_abs_err) {
     DEERS_CUDA_TRY(ctx, cudaFuncSetAttribute(umma_selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
 
     int rc = DEERS_OK;
-    for (int ci = 0; ci < 4 && rc == DEERS_OK; ++ci) {
+    for (int ci = 0; ci < DEERS_SELFTEST_CASES && rc == DEERS_OK; ++ci) {
         const Case c = cases[ci];
         // Logical A[m][k], B[k][n]; storage depends on the operand's major-ness.
         std::vector<float> A((size_t)M * K), Bm((size_t)K * c.N);

@@ -71,7 +71,7 @@ class Context:
         return ms.value, int(n.value)
 
     def selftest_umma(self) -> List[float]:
-        errs = (ctypes.c_float * 4)()
+        errs = (ctypes.c_float * 6)()
         _lib.check(_lib.lib().deers_b200_selftest_umma(self.handle, errs), self.handle)
         return [float(e) for e in errs]
 

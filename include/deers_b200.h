@@ -170,10 +170,12 @@ int deers_b200_kernel_time(deers_ctx* ctx, int kind, int reset, double* total_ms
 /*
  * Tensor-core self-test: runs one small tcgen05 GEMM per operand layout the f16
  * kernels rely on (K-major and MN-major shared-memory operands, TMA 128-byte
- * swizzle) and compares with a host product.  `max_abs_err` (4 floats, host
- * memory) receives the error of each case.  No counterpart in the reference,
+ * swizzle, A operand in tensor memory) and compares with a host product.
+ * `max_abs_err` (DEERS_SELFTEST_CASES floats, host memory) receives the error of
+ * each case.  No counterpart in the reference,
  * whose GEMMs are cuBLAS calls (`src/storage/cuda.rs:1098-1177`).
  */
+enum { DEERS_SELFTEST_CASES = 6 };
 int deers_b200_selftest_umma(deers_ctx* ctx, float* max_abs_err);
 
 #if defined(__GNUC__)

@@ -14,7 +14,7 @@ def test_umma_selftest_operand_layouts():
     # Inputs are multiples of 1/64 in [-2, 2): every product and partial sum is exact in f32.
     from deers_b200 import ops
     errs = ops.Context.current(torch.device("cuda", 0)).selftest_umma()
-    assert errs == [0.0, 0.0, 0.0, 0.0], errs
+    assert errs == [0.0] * 6, errs
 
 
 @pytest.mark.parametrize("shape", [
