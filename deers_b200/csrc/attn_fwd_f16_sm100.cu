@@ -128,14 +128,17 @@ attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         if (lane == 0) {
             constexpr uint32_t IDESC_S = idesc_f16(BM, BN, 0, 0);
             constexpr uint32_t IDESC_O = idesc_f16(BM, D, 0, 1);
-            const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
+            // Step-0 descriptors built once; each MMA adds a constant (single-thread issue must
+            // stay faster than MMA execution).
+            constexpr uint64_t STAGE_STEP = TILE_BYTES >> 4;
+            const uint64_t q_km = desc_kmajor(smem_u32(sQ), 0, BLOCK_BYTES), p_km = desc_kmajor(smem_u32(sP), 0, BLOCK_BYTES);
+            const uint64_t k_km0 = desc_kmajor(smem_u32(sK), 0, BLOCK_BYTES), v_mn0 = desc_mnmajor(smem_u32(sV), 0, BLOCK_BYTES);
             auto issue_s = [&](int j) {
-                const uint32_t k_addr = smem_u32(sK + (j % KV_STAGES) * TILE_BYTES);
+                const uint64_t k_km = k_km0 + (uint64_t)(j % KV_STAGES) * STAGE_STEP;
                 const uint32_t d_tmem = tmem + TM_S0 + (uint32_t)(j & 1) * 128u;
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks)
-                    umma_ss(d_tmem, desc_kmajor(q_addr, ks, BLOCK_BYTES), desc_kmajor(k_addr, ks, BLOCK_BYTES),
-                            IDESC_S, ks > 0);
+                    umma_ss(d_tmem, q_km + kmajor_step(ks, BLOCK_BYTES), k_km + kmajor_step(ks, BLOCK_BYTES), IDESC_S, ks > 0);
                 umma_commit(&s_full[j & 1]);
                 umma_commit(&k_empty[j % KV_STAGES]);
             };
@@ -155,11 +158,10 @@ attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 if (!mbar_wait(ws, &p_full, (uint32_t)j & 1u, DEERS_KERR_FWD_F16 | 6)) break;
                 if (!mbar_wait(ws, &v_full[j % KV_STAGES], (uint32_t)(j / KV_STAGES) & 1u, DEERS_KERR_FWD_F16 | 7)) break;
                 tc_fence_after_sync();
-                const uint32_t v_addr = smem_u32(sV + (j % KV_STAGES) * TILE_BYTES);
+                const uint64_t v_mn = v_mn0 + (uint64_t)(j % KV_STAGES) * STAGE_STEP;
 #pragma unroll
                 for (int ks = 0; ks < BN / 16; ++ks)
-                    umma_ss(tmem + TM_O, desc_kmajor(p_addr, ks, BLOCK_BYTES), desc_mnmajor(v_addr, ks, BLOCK_BYTES),
-                            IDESC_O, (j > 0 || ks > 0));
+                    umma_ss(tmem + TM_O, p_km + kmajor_step(ks, BLOCK_BYTES), v_mn + mnmajor_step(ks), IDESC_O, (j > 0 || ks > 0));
                 umma_commit(&pv_done);
                 umma_commit(&v_empty[j % KV_STAGES]);
             }

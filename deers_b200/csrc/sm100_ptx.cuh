@@ -172,6 +172,14 @@ __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t tile_saddr, int kstep,
     return smem_desc_sw128(tile_saddr + (uint32_t)kstep * 2048u, block_bytes, 1024u);
 }
 
+// Descriptor increments for step k relative to the descriptor of step 0 (added to the 64-bit
+// descriptor; the address field never carries out).  The issuing thread is a single thread,
+// so building every descriptor from scratch would make MMA issue slower than MMA execution.
+__host__ __device__ constexpr uint64_t kmajor_step(int kstep, uint32_t block_bytes) {
+    return (uint64_t)(((uint32_t)(kstep >> 2) * block_bytes + (uint32_t)(kstep & 3) * 32u) >> 4);
+}
+__host__ __device__ constexpr uint64_t mnmajor_step(int kstep) { return (uint64_t)kstep * (2048u >> 4); }
+
 // Instruction descriptor for kind::f16 with f16 inputs and f32 accumulation.
 __host__ __device__ constexpr uint32_t idesc_f16(int M, int N, int a_mn_major, int b_mn_major) {
     return (1u << 4)                       // D format: f32
