@@ -43,7 +43,9 @@ def build(force: bool = False, verbose: bool = False) -> str:
         o = os.path.join(LIB_DIR, src.replace(".cu", ".o"))
         objs.append(o)
         if force or _stale(o, [s] + headers):
+            trace = os.environ.get("DEERS_TRACE")      # development aid: per-iteration clock stamps
             cmd = [_nvcc()] + [f for f in NVCC_FLAGS if not f.startswith("--use_fast_math")] + \
+                  ([f"-DDEERS_TRACE={trace}"] if trace else []) + \
                   (["-Xptxas", "-v"] if verbose else []) + ["-c", s, "-o", o]
             procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
     failed = False

@@ -114,8 +114,8 @@ int deers_b200_sync(deers_ctx* ctx);
 
 /*
  * Scratch memory a pass needs (pass 0 = forward, 1 = backward), in bytes.
- * Forward needs none.  Backward keeps rowsum(dO * O) per row and, for f16, a
- * float32 dQ accumulator.  The reference allocates the equivalent temporaries
+ * Forward needs none.  Backward keeps rowsum(dO * O) per row (and, for f16, the
+ * row lse in log2 units), padded to whole tiles.  The reference allocates the equivalent temporaries
  * inside each op (`src/storage/cuda.rs:637-644`).
  */
 size_t deers_b200_attn_workspace_bytes(const deers_attn_desc* desc, int pass);
@@ -134,8 +134,8 @@ int deers_b200_attn_fwd(deers_ctx* ctx, const deers_attn_desc* desc, const void*
  * Fused backward: dQ, dK, dV from dO, recomputing P from lse.  Replaces the
  * chain `MatMul::backward` (`src/ops.rs:1089-1101`), `EWiseExp::backward`
  * (`:422-425`), log-softmax backward (`:210-214,777-799,1162-1175`),
- * `ScalarMul::backward` (`:638-643`), `MatMul::backward`.  dK and dV are
- * accumulated per KV tile without atomics (bitwise reproducible).
+ * `ScalarMul::backward` (`:638-643`), `MatMul::backward`.  dQ, dK and dV are
+ * accumulated per tile without atomics (bitwise reproducible).
  */
 int deers_b200_attn_bwd(deers_ctx* ctx, const deers_attn_desc* desc, const void* q, const void* k,
                         const void* v, const void* o, const float* lse, const void* d_o, void* dq,
