@@ -4,12 +4,12 @@
 //   1. attn_bwd_prep_f16_kernel   delta[row] = sum_d dO*O (= rowsum(dP*P)) and lse*log2(e), both
 //                                  padded to whole 128-row tiles so that the main kernels can
 //                                  fetch a tile's values with one aligned bulk copy
-//   2. attn_bwd_dkdv_f16_kernel   one CTA per (batch*head, KV tile of 128 rows), KV-stationary:
-//                                  walks the query tiles at or below its diagonal with the dK and
-//                                  dV accumulators resident in TMEM for the whole walk
-//   3. attn_bwd_dq_f16_kernel     one CTA per (batch*head, query tile of 128 rows), Q-stationary:
-//                                  walks the KV tiles at or left of its diagonal with the dQ
-//                                  accumulator resident in TMEM
+//   2. attn_bwd_dkdv_f16_kernel   per (batch*head, KV tile of 128 rows), KV-stationary: walks the
+//                                  query tiles at or below the diagonal with the dK and dV
+//                                  accumulators resident in TMEM for the whole walk
+//   3. attn_bwd_dq_f16_kernel     per (batch*head, query tile of 128 rows), Q-stationary: walks the
+//                                  KV tiles at or left of the diagonal with the dQ accumulator
+//                                  resident in TMEM
 // Both main kernels recompute P from the saved lse.  Recomputing S and dP in the dQ kernel costs
 // two extra products per tile pair (7 instead of 5), but the alternative - adding every
 // 128 x D partial dQ tile into a float32 accumulator in global memory - was measured to be
@@ -27,17 +27,17 @@
 //   S  = Q K^T, dP = dO V^T -> TMEM;  dS = P * (dP - delta) in place;  dQ += dS K (B = K MN-major)
 // Warp roles in both: warp 0 TMA producer, warp 1 MMA issuer, warps 2-9 two compute
 // warpgroups that split the 128 columns of S / dP (and the head_dim columns of the outputs).
+// Both kernels are persistent (one CTA per SM walking a strided list of tiles), so that the
+// loads and first products of the next tile overlap the tail and the epilogue of the current one.
 #include "sm100_ptx.cuh"
 #include "tma_host.cuh"
-
-#include <stdlib.h>
 
 #ifdef DEERS_TRACE
 // Development aid: clock64() stamps of CTA 0's first iterations, read back by a debug entry point.
 __device__ unsigned long long g_bwd_trace[16 * 3 * 8];
 #define BWD_TRACE(role, ev)                                                                              \
     do {                                                                                                 \
-        if (blockIdx.x == 0 && it < 16) g_bwd_trace[(it * 3 + (role)) * 8 + (ev)] = clock64();           \
+        if (blockIdx.x == gridDim.x - 1 && it < 16) g_bwd_trace[(it * 3 + (role)) * 8 + (ev)] = clock64();           \
     } while (0)
 extern "C" __attribute__((visibility("default"))) int deers_b200_debug_bwd_trace(unsigned long long* out) {
     return (int)cudaMemcpyFromSymbol(out, g_bwd_trace, sizeof(g_bwd_trace));
@@ -87,14 +87,15 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
                  : "memory");
 }
 
-// Launch order shared by both kernels: groups of 16 slices; inside a group the heaviest tiles
+// Work order shared by both kernels: groups of 16 slices; inside a group the heaviest tiles
 // of all its slices come first (balance) and the group's tensors (a few MB) stay in L2.
-__device__ __forceinline__ void tile_of_block(int B, int H, int ntile, int& slot, int& bh) {
+// Work item w -> (slot, slice); slot 0 is the heaviest tile of the slice.
+__device__ __forceinline__ void item_tile(int B, int H, int ntile, int w, int& slot, int& bh) {
     const int BH = B * H;
-    const int group = (int)(blockIdx.x / (16u * ntile));
+    const int group = w / (16 * ntile);
     const int gsize = min(16, BH - group * 16);
-    const int within = (int)(blockIdx.x - (unsigned)group * 16u * ntile);
-    slot = within / gsize;                                   // 0 = heaviest
+    const int within = w - group * 16 * ntile;
+    slot = within / gsize;
     bh = group * 16 + within % gsize;
 }
 
@@ -112,7 +113,7 @@ __device__ __forceinline__ void store_row32(__half* dst, const uint32_t (&r)[32]
 }
 
 // ---------------------------------------------------------------------------------------------
-// dK / dV kernel
+// dK / dV kernel (persistent: each CTA walks a strided list of KV tiles)
 // ---------------------------------------------------------------------------------------------
 // Dynamic shared memory only; the base must be 1024-byte aligned for the 128-byte swizzle (checked).
 template <int D>
@@ -120,15 +121,17 @@ struct DkvSmem {
     static constexpr uint32_t TILE = 128u * D * 2u;
     static constexpr uint32_t K = 0;
     static constexpr uint32_t V = K + TILE;
-    static constexpr uint32_t Q = V + TILE;                  // two stages
-    static constexpr uint32_t DO = Q + 2 * TILE;             // two stages
+    static constexpr uint32_t Q = V + TILE;                  // three stages: Q(i+1) feeds S^T while Q(i) still feeds dK
+    static constexpr uint32_t DO = Q + 3 * TILE;             // two stages
     static constexpr uint32_t LSE2 = DO + 2 * TILE;          // two stages of 128 floats
     static constexpr uint32_t DELTA = LSE2 + 2 * BT * 4;
     static constexpr uint32_t BARS = DELTA + 2 * BT * 4;
-    static constexpr uint32_t TOTAL = BARS + 256;
+    static constexpr uint32_t TOTAL = BARS + 192;
 };
 
-enum DkvBar { A_KV = 0, A_QDO_FULL = 1, A_QDO_EMPTY = 3, A_S = 5, A_DP = 6, A_P = 7, A_DS = 8, A_DONE = 9, A_COUNT = 10 };
+enum DkvBar { A_KV_FULL = 0, A_KV_EMPTY = 1, A_Q_FULL = 2, A_Q_EMPTY = 5, A_DO_FULL = 8, A_DO_EMPTY = 10,
+              A_ST_FULL = 12, A_ST_EMPTY = 14, A_S = 16, A_DP = 17, A_P = 18, A_DS = 19, A_DONE = 20, A_ACC_FREE = 21,
+              A_COUNT = 22 };
 
 template <int D>
 __global__ void __launch_bounds__(320, 1)
@@ -157,12 +160,7 @@ attn_bwd_dkdv_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
 
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const int nq = (p.T + BT - 1) / BT;
-    int kt, bh;
-    tile_of_block(p.B, p.H, nq, kt, bh);                    // low KV tiles carry the most work
-    const int b = bh / p.H, h = bh % p.H;
-    const int k0 = kt * BT;
-    const int i0 = p.causal ? kt : 0;
-    const int niter = nq - i0;
+    const int n_items = p.B * p.H * nq;
 
     if (threadIdx.x == 0) {
         *abort_s = 0;
@@ -172,13 +170,19 @@ attn_bwd_dkdv_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
             skip = 1;
         }
         *skip_s = skip;
-        mbar_init(&bars[A_KV], 1);
-        for (int s = 0; s < 2; ++s) { mbar_init(&bars[A_QDO_FULL + s], 1); mbar_init(&bars[A_QDO_EMPTY + s], 1); }
+        mbar_init(&bars[A_KV_FULL], 1);
+        mbar_init(&bars[A_KV_EMPTY], 1);
+        for (int s = 0; s < 3; ++s) { mbar_init(&bars[A_Q_FULL + s], 1); mbar_init(&bars[A_Q_EMPTY + s], 1); }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&bars[A_DO_FULL + s], 1); mbar_init(&bars[A_DO_EMPTY + s], 1);
+            mbar_init(&bars[A_ST_FULL + s], 1); mbar_init(&bars[A_ST_EMPTY + s], 256);
+        }
         mbar_init(&bars[A_S], 1);
         mbar_init(&bars[A_DP], 1);
         mbar_init(&bars[A_P], 256);
         mbar_init(&bars[A_DS], 256);
         mbar_init(&bars[A_DONE], 1);
+        mbar_init(&bars[A_ACC_FREE], 256);
         fence_barrier_init();
         tma_prefetch_desc(&tmap_q); tma_prefetch_desc(&tmap_k); tma_prefetch_desc(&tmap_v); tma_prefetch_desc(&tmap_do);
     }
@@ -197,25 +201,39 @@ attn_bwd_dkdv_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
-            mbar_arrive_expect_tx(&bars[A_KV], 2 * TILE_BYTES);
-#pragma unroll
-            for (int blk = 0; blk < DBLK; ++blk) {
-                tma_load_4d(sK + blk * BLOCK_BYTES, &tmap_k, &bars[A_KV], blk * 64, k0, h, b);
-                tma_load_4d(sV + blk * BLOCK_BYTES, &tmap_v, &bars[A_KV], blk * 64, k0, h, b);
-            }
-            for (int it = 0; it < niter; ++it) {
-                const int st = it & 1;
-                const uint32_t ph = (uint32_t)(it >> 1) & 1u;
-                if (!mbar_wait(ws, &bars[A_QDO_EMPTY + st], ph ^ 1u, DEERS_KERR_BWD_F16 | 1)) break;
-                uint64_t* full = &bars[A_QDO_FULL + st];
-                mbar_arrive_expect_tx(full, 2 * TILE_BYTES + 2 * BT * 4);
-                const int q0 = (i0 + it) * BT;
-                bulk_load(lse2_s + st * BT, p.lse2 + (long long)bh * p.Tpad + q0, BT * 4, full);
-                bulk_load(delta_s + st * BT, p.delta + (long long)bh * p.Tpad + q0, BT * 4, full);
+            uint32_t gi = 0;                                    // query-tile iterations so far (all items)
+            bool ok = true;
+            for (int n = 0, w = blockIdx.x; ok && w < n_items; ++n, w += gridDim.x) {
+                int kt, bh;
+                item_tile(p.B, p.H, nq, w, kt, bh);             // low KV tiles carry the most work
+                const int b = bh / p.H, h = bh % p.H;
+                const int i0 = p.causal ? kt : 0;
+                const int niter = nq - i0;
+                // K / V are single-buffered: wait until the previous item's S^T and dP^T products are done.
+                if (!mbar_wait(ws, &bars[A_KV_EMPTY], ((uint32_t)n & 1u) ^ 1u, DEERS_KERR_BWD_F16 | 1)) break;
+                mbar_arrive_expect_tx(&bars[A_KV_FULL], 2 * TILE_BYTES);
 #pragma unroll
                 for (int blk = 0; blk < DBLK; ++blk) {
-                    tma_load_4d(sQ + st * TILE_BYTES + blk * BLOCK_BYTES, &tmap_q, full, blk * 64, q0, h, b);
-                    tma_load_4d(sDO + st * TILE_BYTES + blk * BLOCK_BYTES, &tmap_do, full, blk * 64, q0, h, b);
+                    tma_load_4d(sK + blk * BLOCK_BYTES, &tmap_k, &bars[A_KV_FULL], blk * 64, kt * BT, h, b);
+                    tma_load_4d(sV + blk * BLOCK_BYTES, &tmap_v, &bars[A_KV_FULL], blk * 64, kt * BT, h, b);
+                }
+                for (int it = 0; it < niter; ++it, ++gi) {
+                    const uint32_t qs = gi % 3u, ds = gi & 1u;
+                    const int q0 = (i0 + it) * BT;
+                    if (!mbar_wait(ws, &bars[A_Q_EMPTY + qs], ((gi / 3u) & 1u) ^ 1u, DEERS_KERR_BWD_F16 | 2)) { ok = false; break; }
+                    mbar_arrive_expect_tx(&bars[A_Q_FULL + qs], TILE_BYTES);
+#pragma unroll
+                    for (int blk = 0; blk < DBLK; ++blk)
+                        tma_load_4d(sQ + qs * TILE_BYTES + blk * BLOCK_BYTES, &tmap_q, &bars[A_Q_FULL + qs], blk * 64, q0, h, b);
+                    if (!mbar_wait(ws, &bars[A_ST_EMPTY + ds], ((gi >> 1) & 1u) ^ 1u, DEERS_KERR_BWD_F16 | 3)) { ok = false; break; }
+                    mbar_arrive_expect_tx(&bars[A_ST_FULL + ds], 2 * BT * 4);
+                    bulk_load(lse2_s + ds * BT, p.lse2 + (long long)bh * p.Tpad + q0, BT * 4, &bars[A_ST_FULL + ds]);
+                    bulk_load(delta_s + ds * BT, p.delta + (long long)bh * p.Tpad + q0, BT * 4, &bars[A_ST_FULL + ds]);
+                    if (!mbar_wait(ws, &bars[A_DO_EMPTY + ds], ((gi >> 1) & 1u) ^ 1u, DEERS_KERR_BWD_F16 | 4)) { ok = false; break; }
+                    mbar_arrive_expect_tx(&bars[A_DO_FULL + ds], TILE_BYTES);
+#pragma unroll
+                    for (int blk = 0; blk < DBLK; ++blk)
+                        tma_load_4d(sDO + ds * TILE_BYTES + blk * BLOCK_BYTES, &tmap_do, &bars[A_DO_FULL + ds], blk * 64, q0, h, b);
                 }
             }
         }
@@ -231,13 +249,15 @@ attn_bwd_dkdv_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
             const uint64_t v_km = desc_kmajor(smem_u32(sV), 0, BLOCK_BYTES);
             const uint64_t q_km0 = desc_kmajor(smem_u32(sQ), 0, BLOCK_BYTES), q_mn0 = desc_mnmajor(smem_u32(sQ), 0, BLOCK_BYTES);
             const uint64_t do_km0 = desc_kmajor(smem_u32(sDO), 0, BLOCK_BYTES), do_mn0 = desc_mnmajor(smem_u32(sDO), 0, BLOCK_BYTES);
-            auto issue_st = [&](uint64_t q_km) {
+            auto issue_st = [&](uint32_t qs) {
+                const uint64_t q_km = q_km0 + (uint64_t)qs * STAGE_STEP;
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks)
                     umma_ss(tmem + TM_S, k_km + kmajor_step(ks, BLOCK_BYTES), q_km + kmajor_step(ks, BLOCK_BYTES), IDESC_ST, ks > 0);
                 umma_commit(&bars[A_S]);
             };
-            auto issue_dpt = [&](uint64_t do_km) {
+            auto issue_dpt = [&](uint32_t ds) {
+                const uint64_t do_km = do_km0 + (uint64_t)ds * STAGE_STEP;
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks)
                     umma_ss(tmem + TM_DP, v_km + kmajor_step(ks, BLOCK_BYTES), do_km + kmajor_step(ks, BLOCK_BYTES), IDESC_ST, ks > 0);
@@ -245,45 +265,61 @@ attn_bwd_dkdv_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
             };
             // A operand in TMEM: 32 packed columns per warpgroup half, halves 64 columns apart.
             auto a_tmem = [&](uint32_t base, int ks) { return tmem + base + (uint32_t)(ks >> 2) * 64u + (uint32_t)(ks & 3) * 8u; };
-            bool ok = mbar_wait(ws, &bars[A_KV], 0, DEERS_KERR_BWD_F16 | 2) &&
-                      mbar_wait(ws, &bars[A_QDO_FULL], 0, DEERS_KERR_BWD_F16 | 3);
-            if (ok) {
+            uint32_t gi = 0;
+            bool ok = true;
+            for (int n = 0, w = blockIdx.x; ok && w < n_items; ++n, w += gridDim.x) {
+                int kt, bh;
+                item_tile(p.B, p.H, nq, w, kt, bh);
+                const int niter = nq - (p.causal ? kt : 0);
+                if (!mbar_wait(ws, &bars[A_KV_FULL], (uint32_t)n & 1u, DEERS_KERR_BWD_F16 | 5)) break;
+                if (!mbar_wait(ws, &bars[A_Q_FULL + gi % 3u], (gi / 3u) & 1u, DEERS_KERR_BWD_F16 | 6)) break;
+                if (!mbar_wait(ws, &bars[A_DO_FULL + (gi & 1u)], (gi >> 1) & 1u, DEERS_KERR_BWD_F16 | 7)) break;
                 tc_fence_after_sync();
-                issue_st(q_km0);
-                issue_dpt(do_km0);
-            }
-            for (int it = 0; ok && it < niter; ++it) {
-                const int st = it & 1, sn = st ^ 1;
-                const uint32_t par = (uint32_t)it & 1u;
-                const uint64_t q_mn = q_mn0 + (uint64_t)st * STAGE_STEP, do_mn = do_mn0 + (uint64_t)st * STAGE_STEP;
-                const bool more = it + 1 < niter;
-                // dV += P^T dO, then S^T of the next query tile: the pipe is in order, so the
-                // new S^T lands only after dV has consumed P^T from the same columns.
-                TRACE_A(0, 0);
-                if (!mbar_wait(ws, &bars[A_P], par, DEERS_KERR_BWD_F16 | 4)) break;
-                tc_fence_after_sync();
-                TRACE_A(0, 1);
-#pragma unroll
-                for (int ks = 0; ks < BT / 16; ++ks)
-                    umma_ts(tmem + TM_DV, a_tmem(TM_S, ks), do_mn + mnmajor_step(ks), IDESC_KV, (it > 0 || ks > 0));
-                if (more) {
-                    if (!mbar_wait(ws, &bars[A_QDO_FULL + sn], (uint32_t)((it + 1) >> 1) & 1u, DEERS_KERR_BWD_F16 | 6)) break;
+                issue_st(gi % 3u);
+                issue_dpt(gi & 1u);
+                if (niter == 1) umma_commit(&bars[A_KV_EMPTY]);         // no further product reads K / V
+                for (int it = 0; it < niter; ++it, ++gi) {
+                    const uint32_t qs = gi % 3u, ds = gi & 1u, par = gi & 1u;
+                    const uint64_t q_mn = q_mn0 + (uint64_t)qs * STAGE_STEP, do_mn = do_mn0 + (uint64_t)ds * STAGE_STEP;
+                    const bool more = it + 1 < niter;
+                    // dV += P^T dO, then S^T of the next query tile: the pipe is in order, so the
+                    // new S^T lands only after dV has consumed P^T from the same columns.
+                    TRACE_A(0, 0);
+                    if (!mbar_wait(ws, &bars[A_P], par, DEERS_KERR_BWD_F16 | 8)) { ok = false; break; }
+                    // The previous item's dK / dV must have left TMEM before this item accumulates.
+                    if (it == 0 && !mbar_wait(ws, &bars[A_ACC_FREE], ((uint32_t)n & 1u) ^ 1u, DEERS_KERR_BWD_F16 | 9)) { ok = false; break; }
                     tc_fence_after_sync();
-                    issue_st(q_km0 + (uint64_t)sn * STAGE_STEP);
-                }
-                // dK += dS^T Q, then dP^T of the next query tile over the consumed dS^T columns.
-                TRACE_A(0, 2);
-                if (!mbar_wait(ws, &bars[A_DS], par, DEERS_KERR_BWD_F16 | 5)) break;
-                tc_fence_after_sync();
-                TRACE_A(0, 3);
+                    TRACE_A(0, 1);
 #pragma unroll
-                for (int ks = 0; ks < BT / 16; ++ks)
-                    umma_ts(tmem + TM_DK, a_tmem(TM_DP, ks), q_mn + mnmajor_step(ks), IDESC_KV, (it > 0 || ks > 0));
-                umma_commit(&bars[A_QDO_EMPTY + st]);                  // Q / dO of this stage are consumed
-                if (more) issue_dpt(do_km0 + (uint64_t)sn * STAGE_STEP);
-                TRACE_A(0, 4);
+                    for (int ks = 0; ks < BT / 16; ++ks)
+                        umma_ts(tmem + TM_DV, a_tmem(TM_S, ks), do_mn + mnmajor_step(ks), IDESC_KV, (it > 0 || ks > 0));
+                    if (more) {
+                        if (!mbar_wait(ws, &bars[A_Q_FULL + (gi + 1u) % 3u], ((gi + 1u) / 3u) & 1u, DEERS_KERR_BWD_F16 | 10)) { ok = false; break; }
+                        tc_fence_after_sync();
+                        issue_st((gi + 1u) % 3u);
+                    }
+                    // dK += dS^T Q, then dP^T of the next query tile over the consumed dS^T columns.
+                    TRACE_A(0, 2);
+                    if (!mbar_wait(ws, &bars[A_DS], par, DEERS_KERR_BWD_F16 | 11)) { ok = false; break; }
+                    tc_fence_after_sync();
+                    TRACE_A(0, 3);
+#pragma unroll
+                    for (int ks = 0; ks < BT / 16; ++ks)
+                        umma_ts(tmem + TM_DK, a_tmem(TM_DP, ks), q_mn + mnmajor_step(ks), IDESC_KV, (it > 0 || ks > 0));
+                    umma_commit(&bars[A_Q_EMPTY + qs]);                 // S^T and dK have both read this Q tile
+                    if (more) {
+                        if (!mbar_wait(ws, &bars[A_DO_FULL + (ds ^ 1u)], ((gi + 1u) >> 1) & 1u, DEERS_KERR_BWD_F16 | 12)) { ok = false; break; }
+                        tc_fence_after_sync();
+                        issue_dpt(ds ^ 1u);
+                        if (it + 2 == niter) umma_commit(&bars[A_KV_EMPTY]);   // the last S^T and dP^T are issued
+                    }
+                    // dO of this iteration was last read by dV (and dP^T before it): its stage is free once
+                    // everything issued so far has finished.
+                    umma_commit(&bars[A_DO_EMPTY + ds]);
+                    TRACE_A(0, 4);
+                }
+                umma_commit(&bars[A_DONE]);
             }
-            umma_commit(&bars[A_DONE]);
         }
     } else {
         // ------------------------------ compute threads ------------------------------
@@ -294,92 +330,103 @@ attn_bwd_dkdv_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         const int r = lane_base + lane;
         const uint32_t t_lane = (uint32_t)lane_base << 16;
         const float sl2 = p.scale * LOG2E;
-        const bool kv_valid = (k0 + r) < p.T;               // rows past the sequence end contribute nothing
+        uint32_t gi = 0;
         bool alive = true;
-#ifdef DEERS_TRACE
+#if defined(DEERS_TRACE) && DEERS_TRACE == 1
         const bool tr = lane == 0 && (warp == 2 || warp == 6);
 #endif
 
-        for (int it = 0; it < niter; ++it) {
-            const int i = i0 + it;
-            const int st = it & 1;
-            const uint32_t par = (uint32_t)it & 1u;
-            const float* lse2 = lse2_s + st * BT + 64 * g;
-            const float* dlt = delta_s + st * BT + 64 * g;
-            // The stage's lse / delta rows arrive with Q and dO: observe that barrier directly.
-            if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[A_QDO_FULL + st], (uint32_t)(it >> 1) & 1u, DEERS_KERR_BWD_F16 | 8))) { alive = false; break; }
-#ifdef DEERS_TRACE
-            if (tr) TRACE_A(1 + g, 0);
+        for (int n = 0, w = blockIdx.x; alive && w < n_items; ++n, w += gridDim.x) {
+            int kt, bh;
+            item_tile(p.B, p.H, nq, w, kt, bh);
+            const int b = bh / p.H, h = bh % p.H;
+            const int k0 = kt * BT;
+            const int i0 = p.causal ? kt : 0;
+            const int niter = nq - i0;
+            const bool kv_valid = (k0 + r) < p.T;           // rows past the sequence end contribute nothing
+
+            for (int it = 0; it < niter; ++it, ++gi) {
+                const int i = i0 + it;
+                const uint32_t ss = gi & 1u, par = gi & 1u;
+                const float* lse2 = lse2_s + ss * BT + 64 * g;
+                const float* dlt = delta_s + ss * BT + 64 * g;
+                if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[A_ST_FULL + ss], (gi >> 1) & 1u, DEERS_KERR_BWD_F16 | 13))) { alive = false; break; }
+#if defined(DEERS_TRACE) && DEERS_TRACE == 1
+                if (tr) TRACE_A(1 + g, 0);
 #endif
-            if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[A_S], par, DEERS_KERR_BWD_F16 | 9))) { alive = false; break; }
-            tc_fence_after_sync();
-#ifdef DEERS_TRACE
-            if (tr) TRACE_A(1 + g, 1);
+                if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[A_S], par, DEERS_KERR_BWD_F16 | 14))) { alive = false; break; }
+                tc_fence_after_sync();
+#if defined(DEERS_TRACE) && DEERS_TRACE == 1
+                if (tr) TRACE_A(1 + g, 1);
 #endif
-            const bool diag = p.causal && (i == kt);
-            uint32_t pk[32];                                // P^T row, 64 query columns as f16 pairs
+                const bool diag = p.causal && (i == kt);
+                uint32_t pk[32];                            // P^T row, 64 query columns as f16 pairs
 #pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                uint32_t sr[32];
-                tmem_ld_x32(tmem + TM_S + t_lane + 64 * g + c * 32, sr);
-                tmem_wait_ld();
-                if (diag || !kv_valid) {                    // only the diagonal / tail tile pays for masking
+                for (int c = 0; c < 2; ++c) {
+                    uint32_t sr[32];
+                    tmem_ld_x32(tmem + TM_S + t_lane + 64 * g + c * 32, sr);
+                    tmem_wait_ld();
+                    if (diag || !kv_valid) {                // only the diagonal / tail tile pays for masking
 #pragma unroll
-                    for (int e = 0; e < 16; ++e) {
-                        const int cl = c * 32 + e * 2;      // column inside this warpgroup's half
-                        float p0 = ex2(fmaf(__uint_as_float(sr[e * 2]), sl2, -lse2[cl]));
-                        float p1 = ex2(fmaf(__uint_as_float(sr[e * 2 + 1]), sl2, -lse2[cl + 1]));
-                        if ((diag && (64 * g + cl) < r) || !kv_valid) p0 = 0.f;   // query index < key index: masked
-                        if ((diag && (64 * g + cl + 1) < r) || !kv_valid) p1 = 0.f;
-                        pk[c * 16 + e] = pack_half2(p0, p1);
+                        for (int e = 0; e < 16; ++e) {
+                            const int cl = c * 32 + e * 2;  // column inside this warpgroup's half
+                            float p0 = ex2(fmaf(__uint_as_float(sr[e * 2]), sl2, -lse2[cl]));
+                            float p1 = ex2(fmaf(__uint_as_float(sr[e * 2 + 1]), sl2, -lse2[cl + 1]));
+                            if ((diag && (64 * g + cl) < r) || !kv_valid) p0 = 0.f;   // query index < key index: masked
+                            if ((diag && (64 * g + cl + 1) < r) || !kv_valid) p1 = 0.f;
+                            pk[c * 16 + e] = pack_half2(p0, p1);
+                        }
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 16; ++e) {
+                            const int cl = c * 32 + e * 2;
+                            pk[c * 16 + e] = pack_half2(ex2(fmaf(__uint_as_float(sr[e * 2]), sl2, -lse2[cl])),
+                                                        ex2(fmaf(__uint_as_float(sr[e * 2 + 1]), sl2, -lse2[cl + 1])));
+                        }
                     }
-                } else {
+                }
+                // P^T replaces this warpgroup's half of S^T in TMEM (32 packed columns).
+                tmem_st_x32(tmem + TM_S + t_lane + 64 * g, pk);
+                tmem_wait_st();
+                tc_fence_before_sync();
+                mbar_arrive(&bars[A_P]);
+#if defined(DEERS_TRACE) && DEERS_TRACE == 1
+                if (tr) TRACE_A(1 + g, 2);
+#endif
+
+                if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[A_DP], par, DEERS_KERR_BWD_F16 | 15))) { alive = false; break; }
+                tc_fence_after_sync();
+#if defined(DEERS_TRACE) && DEERS_TRACE == 1
+                if (tr) TRACE_A(1 + g, 3);
+#endif
+                uint32_t dd[32];                            // dS^T row, 64 query columns as f16 pairs
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    uint32_t dr[32];
+                    tmem_ld_x32(tmem + TM_DP + t_lane + 64 * g + c * 32, dr);
+                    tmem_wait_ld();
 #pragma unroll
                     for (int e = 0; e < 16; ++e) {
                         const int cl = c * 32 + e * 2;
-                        pk[c * 16 + e] = pack_half2(ex2(fmaf(__uint_as_float(sr[e * 2]), sl2, -lse2[cl])),
-                                                    ex2(fmaf(__uint_as_float(sr[e * 2 + 1]), sl2, -lse2[cl + 1])));
+                        const float2 pf = __half22float2(*reinterpret_cast<const __half2*>(&pk[c * 16 + e]));
+                        dd[c * 16 + e] = pack_half2(pf.x * (__uint_as_float(dr[e * 2]) - dlt[cl]),
+                                                    pf.y * (__uint_as_float(dr[e * 2 + 1]) - dlt[cl + 1]));
                     }
                 }
+                mbar_arrive(&bars[A_ST_EMPTY + ss]);        // this stage's lse / delta rows have been read
+                tmem_st_x32(tmem + TM_DP + t_lane + 64 * g, dd);
+                tmem_wait_st();
+                tc_fence_before_sync();
+                mbar_arrive(&bars[A_DS]);
+#if defined(DEERS_TRACE) && DEERS_TRACE == 1
+                if (tr) TRACE_A(1 + g, 4);
+#endif
             }
-            // P^T replaces this warpgroup's half of S^T in TMEM (32 packed columns).
-            tmem_st_x32(tmem + TM_S + t_lane + 64 * g, pk);
-            tmem_wait_st();
-            tc_fence_before_sync();
-            mbar_arrive(&bars[A_P]);
-#ifdef DEERS_TRACE
-            if (tr) TRACE_A(1 + g, 2);
-#endif
+            if (!alive) break;
 
-            if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[A_DP], par, DEERS_KERR_BWD_F16 | 10))) { alive = false; break; }
-            tc_fence_after_sync();
-#ifdef DEERS_TRACE
-            if (tr) TRACE_A(1 + g, 3);
-#endif
-            uint32_t dd[32];                                // dS^T row, 64 query columns as f16 pairs
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                uint32_t dr[32];
-                tmem_ld_x32(tmem + TM_DP + t_lane + 64 * g + c * 32, dr);
-                tmem_wait_ld();
-#pragma unroll
-                for (int e = 0; e < 16; ++e) {
-                    const int cl = c * 32 + e * 2;
-                    const float2 pf = __half22float2(*reinterpret_cast<const __half2*>(&pk[c * 16 + e]));
-                    dd[c * 16 + e] = pack_half2(pf.x * (__uint_as_float(dr[e * 2]) - dlt[cl]),
-                                                pf.y * (__uint_as_float(dr[e * 2 + 1]) - dlt[cl + 1]));
-                }
-            }
-            tmem_st_x32(tmem + TM_DP + t_lane + 64 * g, dd);
-            tmem_wait_st();
-            tc_fence_before_sync();
-            mbar_arrive(&bars[A_DS]);
-#ifdef DEERS_TRACE
-            if (tr) TRACE_A(1 + g, 4);
-#endif
-        }
-
-        if (alive && __all_sync(0xffffffffu, mbar_wait(ws, &bars[A_DONE], 0, DEERS_KERR_BWD_F16 | 12))) {
+            // Epilogue: dK and dV of this KV tile leave TMEM; meanwhile the tensor core already
+            // computes S^T and dP^T of the next item.
+            if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[A_DONE], (uint32_t)n & 1u, DEERS_KERR_BWD_F16 | 16))) { alive = false; break; }
             tc_fence_after_sync();
             const int krow = k0 + r;
             __half* dkrow = p.dk + b * p.sdk_b + h * p.sdk_h + (long long)krow * p.sdk_t + g * DH;
@@ -390,6 +437,10 @@ attn_bwd_dkdv_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
                 tmem_ld_x32(tmem + TM_DK + t_lane + g * DH + c * 32, kr);
                 tmem_ld_x32(tmem + TM_DV + t_lane + g * DH + c * 32, vr);
                 tmem_wait_ld();
+                if (c == DH / 32 - 1) {                     // accumulators are in registers: release TMEM early
+                    tc_fence_before_sync();
+                    mbar_arrive(&bars[A_ACC_FREE]);
+                }
                 if (krow < p.T) {
                     store_row32(dkrow + c * 32, kr, p.scale);
                     store_row32(dvrow + c * 32, vr, 1.0f);
@@ -405,20 +456,21 @@ attn_bwd_dkdv_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
 }
 
 // ---------------------------------------------------------------------------------------------
-// dQ kernel
+// dQ kernel (persistent: each CTA walks a strided list of query tiles)
 // ---------------------------------------------------------------------------------------------
 template <int D>
 struct DqSmem {
     static constexpr uint32_t TILE = 128u * D * 2u;
     static constexpr uint32_t Q = 0;
     static constexpr uint32_t DO = Q + TILE;
-    static constexpr uint32_t K = DO + TILE;                 // two stages
-    static constexpr uint32_t V = K + 2 * TILE;              // two stages
+    static constexpr uint32_t K = DO + TILE;                 // three stages: K(j+1) feeds S while K(j) still feeds dQ
+    static constexpr uint32_t V = K + 3 * TILE;              // two stages
     static constexpr uint32_t BARS = V + 2 * TILE;
     static constexpr uint32_t TOTAL = BARS + 256;
 };
 
-enum DqBar { Q_QDO = 0, Q_KV_FULL = 1, Q_KV_EMPTY = 3, Q_S = 5, Q_DP = 6, Q_PDONE = 7, Q_DS = 8, Q_DONE = 9, Q_COUNT = 10 };
+enum DqBar { Q_QDO_FULL = 0, Q_QDO_EMPTY = 1, Q_K_FULL = 2, Q_K_EMPTY = 5, Q_V_FULL = 8, Q_V_EMPTY = 10, Q_S = 12, Q_DP = 13,
+             Q_PDONE = 14, Q_DS = 15, Q_DONE = 16, Q_DQ_FREE = 18, Q_COUNT = 20 };
 
 template <int D>
 __global__ void __launch_bounds__(320, 1)
@@ -430,7 +482,7 @@ attn_bwd_dq_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     constexpr int DBLK = D / 64;
     constexpr int DH = D / 2;
     constexpr uint32_t TMEM_COLS = 512;
-    // S | dP (later dS in place) | dQ
+    // S | dP (later dS in place) | dQ of even items | dQ of odd items
     constexpr uint32_t TM_S = 0, TM_DP = 128, TM_DQ = 256;
 
     extern __shared__ __align__(1024) uint8_t smem[];
@@ -445,12 +497,7 @@ attn_bwd_dq_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
 
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const int nq = (p.T + BT - 1) / BT;
-    int slot, bh;
-    tile_of_block(p.B, p.H, nq, slot, bh);
-    const int qt = nq - 1 - slot;                           // late query tiles carry the most work
-    const int b = bh / p.H, h = bh % p.H;
-    const int q0 = qt * BT;
-    const int ntiles = p.causal ? qt + 1 : nq;
+    const int n_items = p.B * p.H * nq;
 
     if (threadIdx.x == 0) {
         *abort_s = 0;
@@ -460,13 +507,17 @@ attn_bwd_dq_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
             skip = 1;
         }
         *skip_s = skip;
-        mbar_init(&bars[Q_QDO], 1);
-        for (int s = 0; s < 2; ++s) { mbar_init(&bars[Q_KV_FULL + s], 1); mbar_init(&bars[Q_KV_EMPTY + s], 1); }
+        mbar_init(&bars[Q_QDO_FULL], 1);
+        mbar_init(&bars[Q_QDO_EMPTY], 1);
+        for (int s = 0; s < 3; ++s) { mbar_init(&bars[Q_K_FULL + s], 1); mbar_init(&bars[Q_K_EMPTY + s], 1); }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&bars[Q_V_FULL + s], 1); mbar_init(&bars[Q_V_EMPTY + s], 1);
+            mbar_init(&bars[Q_DONE + s], 1); mbar_init(&bars[Q_DQ_FREE + s], 256);
+        }
         mbar_init(&bars[Q_S], 1);
         mbar_init(&bars[Q_DP], 1);
         mbar_init(&bars[Q_PDONE], 256);
         mbar_init(&bars[Q_DS], 256);
-        mbar_init(&bars[Q_DONE], 1);
         fence_barrier_init();
         tma_prefetch_desc(&tmap_q); tma_prefetch_desc(&tmap_k); tma_prefetch_desc(&tmap_v); tma_prefetch_desc(&tmap_do);
     }
@@ -485,22 +536,34 @@ attn_bwd_dq_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
-            mbar_arrive_expect_tx(&bars[Q_QDO], 2 * TILE_BYTES);
-#pragma unroll
-            for (int blk = 0; blk < DBLK; ++blk) {
-                tma_load_4d(sQ + blk * BLOCK_BYTES, &tmap_q, &bars[Q_QDO], blk * 64, q0, h, b);
-                tma_load_4d(sDO + blk * BLOCK_BYTES, &tmap_do, &bars[Q_QDO], blk * 64, q0, h, b);
-            }
-            for (int j = 0; j < ntiles; ++j) {
-                const int st = j & 1;
-                const uint32_t ph = (uint32_t)(j >> 1) & 1u;
-                if (!mbar_wait(ws, &bars[Q_KV_EMPTY + st], ph ^ 1u, DEERS_KERR_BWD_F16 | 0x11)) break;
-                uint64_t* full = &bars[Q_KV_FULL + st];
-                mbar_arrive_expect_tx(full, 2 * TILE_BYTES);
+            uint32_t kvc = 0;                                   // K/V stage uses so far (all items)
+            bool ok = true;
+            for (int n = 0, w = blockIdx.x; ok && w < n_items; ++n, w += gridDim.x) {
+                int slot, bh;
+                item_tile(p.B, p.H, nq, w, slot, bh);
+                const int qt = nq - 1 - slot;                   // late query tiles carry the most work
+                const int b = bh / p.H, h = bh % p.H;
+                const int ntiles = p.causal ? qt + 1 : nq;
+                // Q / dO are single-buffered: wait until the previous item's S and dP products are done.
+                if (!mbar_wait(ws, &bars[Q_QDO_EMPTY], ((uint32_t)n & 1u) ^ 1u, DEERS_KERR_BWD_F16 | 0x10)) break;
+                mbar_arrive_expect_tx(&bars[Q_QDO_FULL], 2 * TILE_BYTES);
 #pragma unroll
                 for (int blk = 0; blk < DBLK; ++blk) {
-                    tma_load_4d(sK + st * TILE_BYTES + blk * BLOCK_BYTES, &tmap_k, full, blk * 64, j * BT, h, b);
-                    tma_load_4d(sV + st * TILE_BYTES + blk * BLOCK_BYTES, &tmap_v, full, blk * 64, j * BT, h, b);
+                    tma_load_4d(sQ + blk * BLOCK_BYTES, &tmap_q, &bars[Q_QDO_FULL], blk * 64, qt * BT, h, b);
+                    tma_load_4d(sDO + blk * BLOCK_BYTES, &tmap_do, &bars[Q_QDO_FULL], blk * 64, qt * BT, h, b);
+                }
+                for (int j = 0; j < ntiles; ++j, ++kvc) {
+                    const uint32_t ks = kvc % 3u, vs = kvc & 1u;
+                    if (!mbar_wait(ws, &bars[Q_K_EMPTY + ks], ((kvc / 3u) & 1u) ^ 1u, DEERS_KERR_BWD_F16 | 0x11)) { ok = false; break; }
+                    mbar_arrive_expect_tx(&bars[Q_K_FULL + ks], TILE_BYTES);
+#pragma unroll
+                    for (int blk = 0; blk < DBLK; ++blk)
+                        tma_load_4d(sK + ks * TILE_BYTES + blk * BLOCK_BYTES, &tmap_k, &bars[Q_K_FULL + ks], blk * 64, j * BT, h, b);
+                    if (!mbar_wait(ws, &bars[Q_V_EMPTY + vs], ((kvc >> 1) & 1u) ^ 1u, DEERS_KERR_BWD_F16 | 0x1b)) { ok = false; break; }
+                    mbar_arrive_expect_tx(&bars[Q_V_FULL + vs], TILE_BYTES);
+#pragma unroll
+                    for (int blk = 0; blk < DBLK; ++blk)
+                        tma_load_4d(sV + vs * TILE_BYTES + blk * BLOCK_BYTES, &tmap_v, &bars[Q_V_FULL + vs], blk * 64, j * BT, h, b);
                 }
             }
         }
@@ -513,58 +576,74 @@ attn_bwd_dq_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
             const uint64_t q_km = desc_kmajor(smem_u32(sQ), 0, BLOCK_BYTES), do_km = desc_kmajor(smem_u32(sDO), 0, BLOCK_BYTES);
             const uint64_t k_km0 = desc_kmajor(smem_u32(sK), 0, BLOCK_BYTES), k_mn0 = desc_mnmajor(smem_u32(sK), 0, BLOCK_BYTES);
             const uint64_t v_km0 = desc_kmajor(smem_u32(sV), 0, BLOCK_BYTES);
-            auto issue_s = [&](int st) {
+            auto issue_s = [&](uint32_t st) {
                 const uint64_t k_km = k_km0 + (uint64_t)st * STAGE_STEP;
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks)
                     umma_ss(tmem + TM_S, q_km + kmajor_step(ks, BLOCK_BYTES), k_km + kmajor_step(ks, BLOCK_BYTES), IDESC_S, ks > 0);
                 umma_commit(&bars[Q_S]);
             };
-            auto issue_dp = [&](int st) {
+            auto issue_dp = [&](uint32_t st) {
                 const uint64_t v_km = v_km0 + (uint64_t)st * STAGE_STEP;
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks)
                     umma_ss(tmem + TM_DP, do_km + kmajor_step(ks, BLOCK_BYTES), v_km + kmajor_step(ks, BLOCK_BYTES), IDESC_S, ks > 0);
                 umma_commit(&bars[Q_DP]);
+                umma_commit(&bars[Q_V_EMPTY + st]);                    // dP is the only reader of a V tile
             };
-            bool ok = mbar_wait(ws, &bars[Q_QDO], 0, DEERS_KERR_BWD_F16 | 0x12) &&
-                      mbar_wait(ws, &bars[Q_KV_FULL], 0, DEERS_KERR_BWD_F16 | 0x13);
-            if (ok) {
+            uint32_t kvc = 0;                                   // K/V stage uses == KV iterations so far
+            bool ok = true;
+            for (int n = 0, w = blockIdx.x; ok && w < n_items; ++n, w += gridDim.x) {
+                int slot, bh;
+                item_tile(p.B, p.H, nq, w, slot, bh);
+                const int qt = nq - 1 - slot;
+                const int ntiles = p.causal ? qt + 1 : nq;
+                const uint32_t tm_dq = tmem + TM_DQ + (uint32_t)(n & 1) * D;
+                if (!mbar_wait(ws, &bars[Q_QDO_FULL], (uint32_t)n & 1u, DEERS_KERR_BWD_F16 | 0x12)) break;
+                if (!mbar_wait(ws, &bars[Q_K_FULL + kvc % 3u], (kvc / 3u) & 1u, DEERS_KERR_BWD_F16 | 0x13)) break;
+                if (!mbar_wait(ws, &bars[Q_V_FULL + (kvc & 1u)], (kvc >> 1) & 1u, DEERS_KERR_BWD_F16 | 0x1c)) break;
                 tc_fence_after_sync();
-                issue_s(0);
-                issue_dp(0);
-            }
-            for (int j = 0; ok && j < ntiles; ++j) {
-#ifdef DEERS_TRACE
-                const int it = j;
+                issue_s(kvc % 3u);
+                issue_dp(kvc & 1u);
+                for (int j = 0; j < ntiles; ++j, ++kvc) {
+#if defined(DEERS_TRACE) && DEERS_TRACE == 2
+                    const int it = (int)kvc;
 #endif
-                const int st = j & 1, sn = st ^ 1;
-                const uint32_t par = (uint32_t)j & 1u;
-                const bool more = j + 1 < ntiles;
-                // S of the next KV tile as soon as the compute threads have read this one.
-                TRACE_B(0, 0);
-                if (!mbar_wait(ws, &bars[Q_PDONE], par, DEERS_KERR_BWD_F16 | 0x14)) break;
-                TRACE_B(0, 1);
-                if (more) {
-                    if (!mbar_wait(ws, &bars[Q_KV_FULL + sn], (uint32_t)((j + 1) >> 1) & 1u, DEERS_KERR_BWD_F16 | 0x15)) break;
+                    const uint32_t ks = kvc % 3u, ksn = (kvc + 1u) % 3u, vsn = (kvc + 1u) & 1u;
+                    const uint32_t par = kvc & 1u;
+                    const bool more = j + 1 < ntiles;
+                    // S of the next KV tile as soon as the compute threads have read this one.
+                    TRACE_B(0, 0);
+                    if (!mbar_wait(ws, &bars[Q_PDONE], par, DEERS_KERR_BWD_F16 | 0x14)) { ok = false; break; }
+                    TRACE_B(0, 1);
+                    if (more) {
+                        if (!mbar_wait(ws, &bars[Q_K_FULL + ksn], ((kvc + 1u) / 3u) & 1u, DEERS_KERR_BWD_F16 | 0x15)) { ok = false; break; }
+                        tc_fence_after_sync();
+                        issue_s(ksn);
+                    } else {
+                        umma_commit(&bars[Q_QDO_EMPTY]);               // every product reading Q / dO has been issued
+                    }
+                    // dQ += dS K, then dP of the next KV tile over the consumed dS columns.
+                    TRACE_B(0, 2);
+                    if (!mbar_wait(ws, &bars[Q_DS], par, DEERS_KERR_BWD_F16 | 0x16)) { ok = false; break; }
+                    if (j == 0 && !mbar_wait(ws, &bars[Q_DQ_FREE + (n & 1)], (((uint32_t)n >> 1) & 1u) ^ 1u, DEERS_KERR_BWD_F16 | 0x1a)) { ok = false; break; }
                     tc_fence_after_sync();
-                    issue_s(sn);
-                }
-                // dQ += dS K, then dP of the next KV tile over the consumed dS columns.
-                TRACE_B(0, 2);
-                if (!mbar_wait(ws, &bars[Q_DS], par, DEERS_KERR_BWD_F16 | 0x16)) break;
-                tc_fence_after_sync();
-                TRACE_B(0, 3);
-                const uint64_t k_mn = k_mn0 + (uint64_t)st * STAGE_STEP;
+                    TRACE_B(0, 3);
+                    const uint64_t k_mn = k_mn0 + (uint64_t)ks * STAGE_STEP;
 #pragma unroll
-                for (int ks = 0; ks < BT / 16; ++ks)
-                    umma_ts(tmem + TM_DQ, tmem + TM_DP + (uint32_t)(ks >> 2) * 64u + (uint32_t)(ks & 3) * 8u,
-                            k_mn + mnmajor_step(ks), IDESC_DQ, (j > 0 || ks > 0));
-                umma_commit(&bars[Q_KV_EMPTY + st]);                   // K / V of this stage are consumed
-                if (more) issue_dp(sn);
-                TRACE_B(0, 4);
+                    for (int ks = 0; ks < BT / 16; ++ks)
+                        umma_ts(tm_dq, tmem + TM_DP + (uint32_t)(ks >> 2) * 64u + (uint32_t)(ks & 3) * 8u,
+                                k_mn + mnmajor_step(ks), IDESC_DQ, (j > 0 || ks > 0));
+                    umma_commit(&bars[Q_K_EMPTY + ks]);                // S and dQ have both read this K tile
+                    if (more) {
+                        if (!mbar_wait(ws, &bars[Q_V_FULL + vsn], ((kvc + 1u) >> 1) & 1u, DEERS_KERR_BWD_F16 | 0x1d)) { ok = false; break; }
+                        tc_fence_after_sync();
+                        issue_dp(vsn);
+                    }
+                    TRACE_B(0, 4);
+                }
+                umma_commit(&bars[Q_DONE + (n & 1)]);
             }
-            umma_commit(&bars[Q_DONE]);
         }
     } else {
         // ------------------------------ compute threads ------------------------------
@@ -575,88 +654,114 @@ attn_bwd_dq_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         const int r = lane_base + lane;
         const uint32_t t_lane = (uint32_t)lane_base << 16;
         const float sl2 = p.scale * LOG2E;
-        const float lse2_r = p.lse2[(long long)bh * p.Tpad + q0 + r];      // padded: 0 beyond T
-        const float delta_r = p.delta[(long long)bh * p.Tpad + q0 + r];
+        uint32_t gi = 0;                                        // KV iterations so far (all items)
         bool alive = true;
-#ifdef DEERS_TRACE
+#if defined(DEERS_TRACE) && DEERS_TRACE == 2
         const bool tr = lane == 0 && (warp == 2 || warp == 6);
 #endif
-
-        for (int j = 0; j < ntiles; ++j) {
-#ifdef DEERS_TRACE
-            const int it = j;
-            if (tr) TRACE_B(1 + g, 0);
-#endif
-            const uint32_t par = (uint32_t)j & 1u;
-            if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[Q_S], par, DEERS_KERR_BWD_F16 | 0x17))) { alive = false; break; }
+        // The epilogue of item n (scale, convert, store its dQ tile, release the accumulator) is
+        // deferred until the first dS of item n+1 has been handed to the tensor core, which then
+        // never waits for it: dQ accumulators alternate between two TMEM regions.
+        int pend_n = -1, pend_row = 0;
+        __half* pend_ptr = nullptr;
+        auto epilogue = [&]() -> bool {
+            if (pend_n < 0) return true;
+            const int n = pend_n;
+            pend_n = -1;
+            if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[Q_DONE + (n & 1)], ((uint32_t)n >> 1) & 1u, DEERS_KERR_BWD_F16 | 0x19))) return false;
             tc_fence_after_sync();
-#ifdef DEERS_TRACE
-            if (tr) TRACE_B(1 + g, 1);
-#endif
-            const int k0 = j * BT;
-            const bool edge = (p.causal && j == qt) || (k0 + BT > p.T);
-            float pv[64];                                   // P row, this warpgroup's 64 key columns
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                uint32_t sr[32];
-                tmem_ld_x32(tmem + TM_S + t_lane + 64 * g + c * 32, sr);
-                tmem_wait_ld();
-                if (edge) {
-#pragma unroll
-                    for (int e = 0; e < 32; ++e) {
-                        const int col = 64 * g + c * 32 + e;                  // key index inside the tile
-                        const bool masked = (p.causal && j == qt && col > r) || (k0 + col >= p.T);
-                        pv[c * 32 + e] = masked ? 0.f : ex2(fmaf(__uint_as_float(sr[e]), sl2, -lse2_r));
-                    }
-                } else {
-#pragma unroll
-                    for (int e = 0; e < 32; ++e) pv[c * 32 + e] = ex2(fmaf(__uint_as_float(sr[e]), sl2, -lse2_r));
-                }
-            }
-            tc_fence_before_sync();
-            mbar_arrive(&bars[Q_PDONE]);                    // S has been read: the next S may land
-#ifdef DEERS_TRACE
-            if (tr) TRACE_B(1 + g, 2);
-#endif
-
-            if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[Q_DP], par, DEERS_KERR_BWD_F16 | 0x18))) { alive = false; break; }
-            tc_fence_after_sync();
-#ifdef DEERS_TRACE
-            if (tr) TRACE_B(1 + g, 3);
-#endif
-            uint32_t dd[32];
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                uint32_t dr[32];
-                tmem_ld_x32(tmem + TM_DP + t_lane + 64 * g + c * 32, dr);
-                tmem_wait_ld();
-#pragma unroll
-                for (int e = 0; e < 16; ++e)
-                    dd[c * 16 + e] = pack_half2(pv[c * 32 + e * 2] * (__uint_as_float(dr[e * 2]) - delta_r),
-                                                pv[c * 32 + e * 2 + 1] * (__uint_as_float(dr[e * 2 + 1]) - delta_r));
-            }
-            // dS replaces this warpgroup's half of dP in TMEM (32 packed columns).
-            tmem_st_x32(tmem + TM_DP + t_lane + 64 * g, dd);
-            tmem_wait_st();
-            tc_fence_before_sync();
-            mbar_arrive(&bars[Q_DS]);
-#ifdef DEERS_TRACE
-            if (tr) TRACE_B(1 + g, 4);
-#endif
-        }
-
-        if (alive && __all_sync(0xffffffffu, mbar_wait(ws, &bars[Q_DONE], 0, DEERS_KERR_BWD_F16 | 0x19))) {
-            tc_fence_after_sync();
-            const int qrow = q0 + r;
-            __half* dqrow = p.dq + b * p.sdq_b + h * p.sdq_h + (long long)qrow * p.sdq_t + g * DH;
 #pragma unroll
             for (int c = 0; c < DH / 32; ++c) {
                 uint32_t qr[32];
-                tmem_ld_x32(tmem + TM_DQ + t_lane + g * DH + c * 32, qr);
+                tmem_ld_x32(tmem + TM_DQ + (uint32_t)(n & 1) * D + t_lane + g * DH + c * 32, qr);
                 tmem_wait_ld();
-                if (qrow < p.T) store_row32(dqrow + c * 32, qr, p.scale);
+                if (pend_row < p.T) store_row32(pend_ptr + c * 32, qr, p.scale);
             }
+            tc_fence_before_sync();
+            mbar_arrive(&bars[Q_DQ_FREE + (n & 1)]);
+            return true;
+        };
+
+        for (int n = 0, w = blockIdx.x; alive && w < n_items; ++n, w += gridDim.x) {
+            int slot, bh;
+            item_tile(p.B, p.H, nq, w, slot, bh);
+            const int qt = nq - 1 - slot;
+            const int b = bh / p.H, h = bh % p.H;
+            const int q0 = qt * BT;
+            const int ntiles = p.causal ? qt + 1 : nq;
+            const float lse2_r = p.lse2[(long long)bh * p.Tpad + q0 + r];      // padded: 0 beyond T
+            const float delta_r = p.delta[(long long)bh * p.Tpad + q0 + r];
+
+            for (int j = 0; j < ntiles; ++j, ++gi) {
+#if defined(DEERS_TRACE) && DEERS_TRACE == 2
+                const int it = (int)gi;
+                if (tr) TRACE_B(1 + g, 0);
+#endif
+                const uint32_t par = gi & 1u;
+                if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[Q_S], par, DEERS_KERR_BWD_F16 | 0x17))) { alive = false; break; }
+                tc_fence_after_sync();
+#if defined(DEERS_TRACE) && DEERS_TRACE == 2
+                if (tr) TRACE_B(1 + g, 1);
+#endif
+                const int k0 = j * BT;
+                const bool edge = (p.causal && j == qt) || (k0 + BT > p.T);
+                float pv[64];                               // P row, this warpgroup's 64 key columns
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    uint32_t sr[32];
+                    tmem_ld_x32(tmem + TM_S + t_lane + 64 * g + c * 32, sr);
+                    tmem_wait_ld();
+                    if (edge) {
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) {
+                            const int col = 64 * g + c * 32 + e;              // key index inside the tile
+                            const bool masked = (p.causal && j == qt && col > r) || (k0 + col >= p.T);
+                            pv[c * 32 + e] = masked ? 0.f : ex2(fmaf(__uint_as_float(sr[e]), sl2, -lse2_r));
+                        }
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) pv[c * 32 + e] = ex2(fmaf(__uint_as_float(sr[e]), sl2, -lse2_r));
+                    }
+                }
+                tc_fence_before_sync();
+                mbar_arrive(&bars[Q_PDONE]);                // S has been read: the next S may land
+#if defined(DEERS_TRACE) && DEERS_TRACE == 2
+                if (tr) TRACE_B(1 + g, 2);
+#endif
+
+                if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[Q_DP], par, DEERS_KERR_BWD_F16 | 0x18))) { alive = false; break; }
+                tc_fence_after_sync();
+#if defined(DEERS_TRACE) && DEERS_TRACE == 2
+                if (tr) TRACE_B(1 + g, 3);
+#endif
+                uint32_t dd[32];
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    uint32_t dr[32];
+                    tmem_ld_x32(tmem + TM_DP + t_lane + 64 * g + c * 32, dr);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int e = 0; e < 16; ++e)
+                        dd[c * 16 + e] = pack_half2(pv[c * 32 + e * 2] * (__uint_as_float(dr[e * 2]) - delta_r),
+                                                    pv[c * 32 + e * 2 + 1] * (__uint_as_float(dr[e * 2 + 1]) - delta_r));
+                }
+                // dS replaces this warpgroup's half of dP in TMEM (32 packed columns).
+                tmem_st_x32(tmem + TM_DP + t_lane + 64 * g, dd);
+                tmem_wait_st();
+                tc_fence_before_sync();
+                mbar_arrive(&bars[Q_DS]);
+#if defined(DEERS_TRACE) && DEERS_TRACE == 2
+                if (tr) TRACE_B(1 + g, 4);
+#endif
+                if (j == 0 && !epilogue()) { alive = false; break; }       // previous item's dQ tile
+            }
+            if (!alive) break;
+
+            pend_n = n;
+            pend_row = q0 + r;
+            pend_ptr = p.dq + b * p.sdq_b + h * p.sdq_h + (long long)(q0 + r) * p.sdq_t + g * DH;
         }
+        if (alive) epilogue();
     }
 
     __syncwarp();
@@ -748,12 +853,14 @@ int bwd_launch(deers_ctx* ctx, const deers_attn_desc* d, const void* q, const vo
     DEERS_CUDA_TRY(ctx, cudaFuncSetAttribute(attn_bwd_dq_f16_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_b));
     {
         KernelTimerScope ts(ctx, DEERS_K_BWD_MAIN);
-        attn_bwd_dkdv_f16_kernel<D><<<(unsigned)grid, 320, smem_a, ctx->stream>>>(tq, tk, tv, tdo, p);
+        const unsigned persistent = (unsigned)(grid < ctx->sm_count ? grid : ctx->sm_count);
+        attn_bwd_dkdv_f16_kernel<D><<<persistent, 320, smem_a, ctx->stream>>>(tq, tk, tv, tdo, p);
     }
     DEERS_CUDA_TRY(ctx, cudaGetLastError());
     {
         KernelTimerScope ts(ctx, DEERS_K_BWD_DQ);
-        attn_bwd_dq_f16_kernel<D><<<(unsigned)grid, 320, smem_b, ctx->stream>>>(tq, tk, tv, tdo, p);
+        const unsigned persistent = (unsigned)(grid < ctx->sm_count ? grid : ctx->sm_count);
+        attn_bwd_dq_f16_kernel<D><<<persistent, 320, smem_b, ctx->stream>>>(tq, tk, tv, tdo, p);
     }
     DEERS_CUDA_TRY(ctx, cudaGetLastError());
     ctx->launches += 3;
