@@ -4,8 +4,8 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg5] [--impl ours|reference]
 
 One "step" is one forward + backward of the whole workload (for N > 1: of this
-rank's (batch x head) shard, plus the all-gather of O overlapped with the
-backward).  The default workload is the one the headline metric is quoted on:
+rank's (batch x head) shard; O and the gradients stay sharded, and the cost of an
+optional NCCL all-gather of O is measured separately and reported beside it).  The default workload is the one the headline metric is quoted on:
 f16, B=64, T=2048, H=32, head_dim=128 (7.7 TFLOP per step counting causal FLOPs
 as 7*B*H*T^2*D).  Rank 0 prints ONE JSON line.
 
@@ -181,8 +181,10 @@ def main():
     ap.add_argument("--shape", default=None, help="B,T,H,D: a custom shape (profiling captures on a small case)")
     ap.add_argument("--dtype", default=None, choices=["f16", "f32"], help="dtype for --shape")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--gather", default="overlap", choices=["overlap", "none"],
-                    help="N>1: all-gather O over NCCL on a side stream (overlap) or keep O sharded (none)")
+    ap.add_argument("--gather", default="none", choices=["overlap", "none"],
+                    help="N>1: include an all-gather of O over NCCL (side stream, overlapping the backward) in the "
+                         "timed step.  Default none: gradients and O stay sharded, as a training step needs them; "
+                         "the gather's cost is measured separately and reported under config.gather_probe")
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -214,6 +216,7 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
+        os.environ["NCCL_DEBUG"] = "WARN"      # keep NCCL's version banner off stdout: one JSON line only
         dist.init_process_group("nccl", device_id=dev)
 
     tdtype = torch.float16 if dtype == "f16" else torch.float32
@@ -230,16 +233,14 @@ def main():
     ctx = ops.Context.current(dev)
     ws_bytes = ops.workspace_bytes(q, scale)
     workspace = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=dev)
-    gatherer = None
-    if world > 1 and args.gather == "overlap":
-        gatherer = shard.OverlappedGather(n_total, T, D, tdtype, dev)
+    gatherer = shard.OverlappedGather(n_total, T, D, tdtype, dev) if world > 1 else None
 
-    def step():
+    def step(gather=(args.gather == "overlap")):
         o, lse = ops.attention_fwd(q, k, v, scale, True)
-        if gatherer is not None:
+        if gather and gatherer is not None:
             gatherer.start(o)
         grads = ops.attention_bwd(q, k, v, o, lse, do, scale, True, workspace=workspace)
-        if gatherer is not None:
+        if gather and gatherer is not None:
             gatherer.finish()
         return o, grads
 
@@ -275,6 +276,29 @@ def main():
     if world > 1:
         dist.all_reduce(ms_t, op=dist.ReduceOp.MAX)
     ms_max = float(ms_t.item())
+
+    # ---- N > 1: what the optional all-gather of O costs (overlapped with the backward, and alone) ----
+    gather_probe = None
+    if world > 1:
+        def timed(fn, reps):
+            a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            barrier()
+            a.record()
+            for _ in range(reps):
+                fn()
+            b_.record()
+            barrier()
+            t = torch.tensor([a.elapsed_time(b_) / reps], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item())
+        o_probe, _ = ops.attention_fwd(q, k, v, scale, True)
+        step(True)
+        overlap_ms = timed(lambda: step(True), 5)
+        shard.gather_output(o_probe, n_total, out=gatherer.out)
+        alone_ms = timed(lambda: shard.gather_output(o_probe, n_total, out=gatherer.out), 5)
+        gather_probe = {"step_with_overlapped_gather_ms": overlap_ms, "allgather_alone_ms": alone_ms,
+                        "bytes_received_per_gpu": (n_total - n_local) * T * D * esize}
+        del o_probe
     total_flops = flops_fwd_bwd(n_total, T, D)
     value = total_flops / (ms_max * 1e-3) / 1e12
 
@@ -351,7 +375,7 @@ def main():
                 "config": {"workload": workload_name(args.workload, dtype, B, T, H, D),
                            "flops_per_step": total_flops, "flop_convention": "7*B*H*T^2*D (causal fwd 2, bwd 5)",
                            "parallelism": f"(b x h) shards over {world} GPU(s), {n_local} slices on rank 0",
-                           "gather": (args.gather if world > 1 else "n/a (1 GPU)"),
+                           "gather": (args.gather if world > 1 else "n/a (1 GPU)"), "gather_probe": gather_probe,
                            "l2": "inputs larger than L2 (no flush needed)" if 4 * q.numel() * esize > 126e6
                                  else "inputs fit in L2 (not flushed)",
                            "frac_of_dense_peak": value / world / peaks["tflops_sustained"],

@@ -1,0 +1,264 @@
+// C++ mirror of the deers operator interface for the fused attention op, on top
+// of the C ABI in include/deers_b200.h.  The deers host code is Rust; this header
+// restates the handful of types the path touches with the same names, argument
+// meaning and error behaviour, so that the boundary can be exercised from a
+// compiled host language:
+//
+//   Tensor / Layout / DType            src/tensor.rs:53-108, src/layout.rs:151-202, src/dtype.rs:14-21
+//   TensorOp {forward, backward, dependencies, name}      src/ops.rs:82-97
+//   GradientStore::accumulate (insert-or-add)             src/backprop.rs:101-112
+//   CudaStorage::attention_fwd / attention_bwd            new BackendStorage methods, added the way
+//                                                         log_softmax_fwd/bwd were (src/storage.rs:284-302)
+//   Error::{LayoutMismatch, DTypeMismatch, DeviceMismatch, Cuda}   src/error.rs:8-42
+//   Device::synchronize                                   src/device.rs:66-72
+//
+// Header-only, C++17; link with libdeers_b200.so.  There is no CPU fallback.
+#pragma once
+#include <cmath>
+#include <cstdint>
+#include <cstring>
+#include <map>
+#include <memory>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "../../include/deers_b200.h"
+
+namespace deers {
+
+enum class DType { F16 = DEERS_F16, F32 = DEERS_F32 };
+inline size_t dtype_size(DType d) { return d == DType::F16 ? 2 : 4; }
+
+struct Error : std::runtime_error {
+    enum class Kind { LayoutMismatch, DTypeMismatch, DeviceMismatch, Cuda };
+    Kind kind;
+    Error(Kind k, const std::string& what) : std::runtime_error(what), kind(k) {}
+};
+
+// One process-wide runtime per device, like CudaRuntime behind its OnceLock (src/storage/cuda.rs:455-521).
+class Runtime {
+public:
+    static Runtime& get(int device = 0) {
+        static std::map<int, std::unique_ptr<Runtime>> all;
+        auto& slot = all[device];
+        if (!slot) slot.reset(new Runtime(device));
+        return *slot;
+    }
+    deers_ctx* ctx() const { return ctx_; }
+    void check(int status) const {
+        if (status == DEERS_OK) return;
+        throw Error(Error::Kind::Cuda, std::string("deers_b200: ") + deers_b200_status_string(status) + " [" +
+                                           deers_b200_last_error(ctx_) + "]");
+    }
+    void synchronize() const { check(deers_b200_sync(ctx_)); }          // Device::synchronize
+    ~Runtime() { deers_b200_destroy(ctx_); }
+
+private:
+    explicit Runtime(int device) : ctx_(nullptr) {
+        const int rc = deers_b200_init(device, nullptr, &ctx_);
+        if (rc != DEERS_OK) throw Error(Error::Kind::Cuda, std::string("deers_b200_init: ") + deers_b200_status_string(rc));
+    }
+    deers_ctx* ctx_;
+};
+
+struct Layout {
+    std::vector<int64_t> shape, strides;                       // strides in elements (src/layout.rs:101-105)
+    static Layout contiguous(const std::vector<int64_t>& shape) {
+        Layout l{shape, std::vector<int64_t>(shape.size(), 1)};
+        for (int i = (int)shape.size() - 2; i >= 0; --i) l.strides[i] = l.strides[i + 1] * shape[i + 1];
+        return l;
+    }
+    int64_t size() const { int64_t n = 1; for (auto s : shape) n *= s; return n; }
+    bool is_compact() const { return strides == contiguous(shape).strides; }
+};
+
+// Device buffer owned by the storage value and freed on drop (src/storage/cuda.rs:637-644).
+class CudaStorage {
+public:
+    CudaStorage(size_t bytes, DType dtype, int device = 0) : rt_(&Runtime::get(device)), bytes_(bytes), dtype_(dtype) {
+        rt_->check(deers_b200_alloc(rt_->ctx(), bytes, &ptr_));
+    }
+    CudaStorage(const CudaStorage&) = delete;
+    CudaStorage& operator=(const CudaStorage&) = delete;
+    ~CudaStorage() { deers_b200_free(rt_->ctx(), ptr_); }
+    void* ptr() const { return ptr_; }
+    size_t bytes() const { return bytes_; }
+    DType dtype() const { return dtype_; }
+    Runtime& runtime() const { return *rt_; }
+    void upload(const void* host) { rt_->check(deers_b200_memcpy_h2d(rt_->ctx(), ptr_, host, bytes_)); rt_->synchronize(); }
+    void download(void* host) const { rt_->check(deers_b200_memcpy_d2h(rt_->ctx(), host, ptr_, bytes_)); }
+
+private:
+    Runtime* rt_;
+    void* ptr_ = nullptr;
+    size_t bytes_;
+    DType dtype_;
+};
+
+class Tensor;
+class GradientStore;
+
+// src/ops.rs:82-97.  forward() consumes the op in Rust; here the op is shared so that the
+// output tensor can keep it alive for the backward walk.
+class TensorOp {
+public:
+    virtual ~TensorOp() = default;
+    virtual Tensor forward() = 0;
+    virtual void backward(GradientStore& grads, const Tensor& out_grad) const = 0;
+    virtual std::vector<const Tensor*> dependencies() const = 0;
+    virtual const char* name() const = 0;
+};
+
+class Tensor {
+public:
+    Tensor() = default;
+    Tensor(std::shared_ptr<CudaStorage> storage, Layout layout, std::shared_ptr<const TensorOp> op = nullptr)
+        : in_(std::make_shared<Internal>(Internal{next_id()++, std::move(storage), std::move(layout), std::move(op)})) {}
+
+    template <typename T>
+    static Tensor from_vec(const std::vector<T>& data, const std::vector<int64_t>& shape, DType dtype, int device = 0) {
+        Layout l = Layout::contiguous(shape);
+        if ((int64_t)data.size() != l.size() || sizeof(T) != dtype_size(dtype))
+            throw Error(Error::Kind::LayoutMismatch, "from_vec: data does not fit the shape / dtype");
+        auto st = std::make_shared<CudaStorage>(data.size() * sizeof(T), dtype, device);
+        st->upload(data.data());
+        return Tensor(st, l);
+    }
+    template <typename T>
+    std::vector<T> to_vec() const {
+        if (!layout().is_compact()) throw Error(Error::Kind::LayoutMismatch, "to_vec: tensor is not compact");
+        std::vector<T> out(storage().bytes() / sizeof(T));
+        storage().download(out.data());
+        return out;
+    }
+    uint64_t id() const { return in_->id; }
+    const Layout& layout() const { return in_->layout; }
+    CudaStorage& storage() const { return *in_->storage; }
+    std::shared_ptr<CudaStorage> storage_ptr() const { return in_->storage; }
+    DType dtype() const { return in_->storage->dtype(); }
+    const TensorOp* op() const { return in_->op.get(); }
+    bool defined() const { return (bool)in_; }
+
+    // Tensor method of the house style (src/tensor.rs:379-381): CausalAttention::new(..).forward().
+    Tensor causal_attention(const Tensor& k, const Tensor& v, float scale) const;
+
+private:
+    struct Internal {
+        uint64_t id;
+        std::shared_ptr<CudaStorage> storage;
+        Layout layout;
+        std::shared_ptr<const TensorOp> op;
+    };
+    static uint64_t& next_id() { static uint64_t n = 1; return n; }
+    std::shared_ptr<Internal> in_;
+};
+
+// src/backprop.rs:74-128: insert-or-add keyed by tensor id.  The fused op produces exactly one
+// gradient per input, so the add branch only triggers when an input is used twice; it then sums
+// on the host (this mirror has no elementwise add kernel of its own).
+class GradientStore {
+public:
+    void accumulate(const Tensor& t, const Tensor& grad) {
+        auto it = grads_.find(t.id());
+        if (it == grads_.end()) { grads_.emplace(t.id(), grad); return; }
+        if (grad.dtype() != DType::F32) throw Error(Error::Kind::DTypeMismatch, "accumulate: repeated f16 gradient");
+        auto a = it->second.to_vec<float>(), b = grad.to_vec<float>();
+        for (size_t i = 0; i < a.size(); ++i) a[i] += b[i];
+        it->second = Tensor::from_vec(a, grad.layout().shape, DType::F32);
+    }
+    const Tensor* get(const Tensor& t) const {
+        auto it = grads_.find(t.id());
+        return it == grads_.end() ? nullptr : &it->second;
+    }
+
+private:
+    std::map<uint64_t, Tensor> grads_;
+};
+
+inline void fill_strides(int64_t (&dst)[4], const Layout& l) { for (int i = 0; i < 4; ++i) dst[i] = l.strides[i]; }
+
+// The fused op for src/models/gpt.rs:139-144 on [B, H, T, D] tensors.
+class CausalAttention : public TensorOp, public std::enable_shared_from_this<CausalAttention> {
+public:
+    // X::new(args) -> Result<Self>: validates, throwing the reference's error kinds (src/ops.rs:1018-1064).
+    static std::shared_ptr<CausalAttention> make(const Tensor& q, const Tensor& k, const Tensor& v, float scale,
+                                                 bool causal = true) {
+        for (const Tensor* t : {&q, &k, &v}) {
+            if (t->layout().shape.size() != 4) throw Error(Error::Kind::LayoutMismatch, "CausalAttention: expected [B, H, T, D]");
+            if (t->layout().shape != q.layout().shape) throw Error(Error::Kind::LayoutMismatch, "CausalAttention: shapes differ");
+            if (t->dtype() != q.dtype()) throw Error(Error::Kind::DTypeMismatch, "CausalAttention: dtypes differ");
+            if (&t->storage().runtime() != &q.storage().runtime()) throw Error(Error::Kind::DeviceMismatch, "CausalAttention: devices differ");
+        }
+        return std::shared_ptr<CausalAttention>(new CausalAttention(q, k, v, scale, causal));
+    }
+
+    Tensor forward() override {
+        Runtime& rt = q_.storage().runtime();
+        const Layout out_layout = Layout::contiguous(q_.layout().shape);
+        auto o = std::make_shared<CudaStorage>((size_t)out_layout.size() * dtype_size(q_.dtype()), q_.dtype());
+        const auto& s = q_.layout().shape;
+        lse_ = std::make_shared<CudaStorage>((size_t)(s[0] * s[1] * s[2]) * sizeof(float), DType::F32);
+        deers_attn_desc d = desc(out_layout);
+        rt.check(deers_b200_attn_fwd(rt.ctx(), &d, q_.storage().ptr(), k_.storage().ptr(), v_.storage().ptr(), o->ptr(),
+                                     (float*)lse_->ptr(), nullptr, 0));
+        o_ = Tensor(o, out_layout);                                     // kept for the backward, like LogSumExp.lse
+        return Tensor(o, out_layout, shared_from_this());
+    }
+
+    void backward(GradientStore& grads, const Tensor& out_grad) const override {
+        if (!o_.defined()) throw std::logic_error("CausalAttention::backward before forward");
+        if (out_grad.layout().shape != q_.layout().shape) throw Error(Error::Kind::LayoutMismatch, "out_grad shape");
+        Runtime& rt = q_.storage().runtime();
+        const Layout gl = Layout::contiguous(q_.layout().shape);
+        const size_t bytes = (size_t)gl.size() * dtype_size(q_.dtype());
+        auto dq = std::make_shared<CudaStorage>(bytes, q_.dtype()), dk = std::make_shared<CudaStorage>(bytes, q_.dtype()),
+             dv = std::make_shared<CudaStorage>(bytes, q_.dtype());
+        deers_attn_desc d = desc(o_.layout());
+        fill_strides(d.do_strides, out_grad.layout());
+        fill_strides(d.dq_strides, gl); fill_strides(d.dk_strides, gl); fill_strides(d.dv_strides, gl);
+        const size_t ws_bytes = deers_b200_attn_workspace_bytes(&d, 1);
+        CudaStorage ws(ws_bytes ? ws_bytes : 256, DType::F32);
+        rt.check(deers_b200_attn_bwd(rt.ctx(), &d, q_.storage().ptr(), k_.storage().ptr(), v_.storage().ptr(),
+                                     o_.storage().ptr(), (const float*)lse_->ptr(), out_grad.storage().ptr(), dq->ptr(),
+                                     dk->ptr(), dv->ptr(), ws.ptr(), ws.bytes()));
+        grads.accumulate(q_, Tensor(dq, gl));
+        grads.accumulate(k_, Tensor(dk, gl));
+        grads.accumulate(v_, Tensor(dv, gl));
+    }
+
+    std::vector<const Tensor*> dependencies() const override { return {&q_, &k_, &v_}; }
+    const char* name() const override { return "CausalAttention"; }
+    const CudaStorage& lse() const { return *lse_; }
+
+private:
+    CausalAttention(const Tensor& q, const Tensor& k, const Tensor& v, float scale, bool causal)
+        : q_(q), k_(k), v_(v), scale_(scale), causal_(causal) {}
+    deers_attn_desc desc(const Layout& o_layout) const {
+        const auto& s = q_.layout().shape;
+        deers_attn_desc d;
+        deers_b200_attn_desc_compact(&d, (int32_t)s[0], (int32_t)s[1], (int32_t)s[2], (int32_t)s[3], (int32_t)q_.dtype(),
+                                     causal_ ? 1 : 0, scale_);
+        fill_strides(d.q_strides, q_.layout()); fill_strides(d.k_strides, k_.layout());
+        fill_strides(d.v_strides, v_.layout()); fill_strides(d.o_strides, o_layout);
+        return d;
+    }
+    Tensor q_, k_, v_, o_;
+    float scale_;
+    bool causal_;
+    std::shared_ptr<CudaStorage> lse_;
+};
+
+inline Tensor Tensor::causal_attention(const Tensor& k, const Tensor& v, float scale) const {
+    return CausalAttention::make(*this, k, v, scale)->forward();
+}
+
+// Tensor::backward for a graph that consists of this one op (src/backprop.rs:52-66 walks the
+// sorted nodes and calls op.backward for each).
+inline GradientStore backward(const Tensor& out, const Tensor& out_grad) {
+    GradientStore grads;
+    if (out.op()) out.op()->backward(grads, out_grad);
+    return grads;
+}
+
+}  // namespace deers

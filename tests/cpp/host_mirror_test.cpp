@@ -1,0 +1,94 @@
+// Test of the C++ host mirror (deers_b200/host/deers_host.hpp) against the CPU oracle: the
+// fused op is driven the way deers drives a TensorOp (new -> forward -> backward into a
+// GradientStore) and its results are compared with oracle/attn_ref.c on the same seeded inputs.
+// Test infrastructure: links the oracle, never shipped.
+#include <cstdio>
+#include <random>
+
+#include "../../deers_b200/host/deers_host.hpp"
+
+extern "C" int ref_attn_fwd_bwd(const float* q, const float* k, const float* v, const float* d_o, int B, int H, int T,
+                                int D, float scale, int causal, float* o, float* lse, float* dq, float* dk, float* dv);
+
+static float max_rel(const std::vector<float>& got, const std::vector<float>& want) {
+    float err = 0.f, mx = 1e-30f;
+    for (size_t i = 0; i < want.size(); ++i) {
+        if (!(got[i] == got[i])) return INFINITY;
+        err = std::fmax(err, std::fabs(got[i] - want[i]));
+        mx = std::fmax(mx, std::fabs(want[i]));
+    }
+    return err / mx;
+}
+
+template <typename T>
+static std::vector<float> as_float(const std::vector<T>& v) {
+    std::vector<float> out(v.size());
+    for (size_t i = 0; i < v.size(); ++i) out[i] = (float)v[i];
+    return out;
+}
+
+static int run_case(deers::DType dtype, int B, int H, int T, int D, float tol) {
+    const size_t n = (size_t)B * H * T * D;
+    std::mt19937 rng(1234 + T + D);
+    std::normal_distribution<float> dist(0.f, 1.f);
+    std::vector<float> host[4];
+    for (auto& h : host) {
+        h.resize(n);
+        for (auto& x : h) { x = dist(rng); if (dtype == deers::DType::F16) x = (float)(_Float16)x; }
+    }
+    const float scale = (float)(1.0 / std::sqrt((double)D));
+    std::vector<float> o(n), lse((size_t)B * H * T), dq(n), dk(n), dv(n);
+    ref_attn_fwd_bwd(host[0].data(), host[1].data(), host[2].data(), host[3].data(), B, H, T, D, scale, 1, o.data(),
+                     lse.data(), dq.data(), dk.data(), dv.data());
+
+    const std::vector<int64_t> shape{B, H, T, D};
+    deers::Tensor t[4];
+    for (int i = 0; i < 4; ++i) {
+        if (dtype == deers::DType::F16) {
+            std::vector<_Float16> h16(n);
+            for (size_t e = 0; e < n; ++e) h16[e] = (_Float16)host[i][e];
+            t[i] = deers::Tensor::from_vec(h16, shape, dtype);
+        } else {
+            t[i] = deers::Tensor::from_vec(host[i], shape, dtype);
+        }
+    }
+    deers::Tensor y = t[0].causal_attention(t[1], t[2], scale);
+    if (std::string(y.op()->name()) != "CausalAttention" || y.op()->dependencies().size() != 3) return 1;
+    deers::GradientStore grads = deers::backward(y, t[3]);
+    deers::Runtime::get().synchronize();
+
+    auto fetch = [&](const deers::Tensor& x) {
+        return dtype == deers::DType::F16 ? as_float(x.to_vec<_Float16>()) : x.to_vec<float>();
+    };
+    const float e[4] = {max_rel(fetch(y), o), max_rel(fetch(*grads.get(t[0])), dq), max_rel(fetch(*grads.get(t[1])), dk),
+                        max_rel(fetch(*grads.get(t[2])), dv)};
+    const bool ok = e[0] <= tol && e[1] <= tol && e[2] <= tol && e[3] <= tol;
+    std::printf("%s %s B%d H%d T%d D%d  o %.2e dq %.2e dk %.2e dv %.2e (tol %.0e)\n", ok ? "PASS" : "FAIL",
+                dtype == deers::DType::F16 ? "f16" : "f32", B, H, T, D, e[0], e[1], e[2], e[3], tol);
+    return ok ? 0 : 1;
+}
+
+int main() {
+    int fails = 0;
+    try {
+        fails += run_case(deers::DType::F32, 2, 3, 96, 32, 1e-4f);
+        fails += run_case(deers::DType::F16, 2, 2, 300, 128, 2e-2f);
+        fails += run_case(deers::DType::F16, 1, 3, 200, 64, 2e-2f);
+        // Error behaviour: mismatched shapes are a LayoutMismatch, like the Rust constructor.
+        auto a = deers::Tensor::from_vec(std::vector<float>(64, 0.f), {1, 1, 8, 8}, deers::DType::F32);
+        auto b = deers::Tensor::from_vec(std::vector<float>(32, 0.f), {1, 1, 4, 8}, deers::DType::F32);
+        try {
+            deers::CausalAttention::make(a, b, a, 1.0f);
+            std::printf("FAIL no LayoutMismatch\n");
+            ++fails;
+        } catch (const deers::Error& err) {
+            const bool ok = err.kind == deers::Error::Kind::LayoutMismatch;
+            std::printf("%s LayoutMismatch raised\n", ok ? "PASS" : "FAIL");
+            fails += !ok;
+        }
+    } catch (const std::exception& ex) {
+        std::printf("FAIL exception: %s\n", ex.what());
+        return 2;
+    }
+    return fails ? 1 : 0;
+}
