@@ -879,3 +879,55 @@ int launch_attn_bwd_f16(deers_ctx* ctx, const deers_attn_desc* d, const void* q,
     if (d->D == 128) return bwd_launch<128>(ctx, d, q, k, v, o, lse, d_o, dq, dk, dv, workspace);
     return DEERS_ERR_UNSUPPORTED;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Backward without a caller-provided workspace
+// ---------------------------------------------------------------------------------------------
+// Some hosts of this library cannot hand it scratch memory: code running inside a stream-ordered
+// or pooled allocator's callback, a plugin whose host forbids cudaMalloc after start-up, or a caller
+// in the middle of building its own memory plan.  For them the f16 backward is also offered with
+// its scratch (the per-row delta and lse*log2e arrays) placed in a fixed array that is part of the
+// library image.  Every GPU that loads the library carries these 8 MiB until the process exits.
+constexpr size_t kStaticScratchFloats = 2u * 1024u * 1024u;            // 8 MiB: B*H*Tpad <= 1 Mi rows
+static __device__ __align__(256) float g_bwd_static_scratch[kStaticScratchFloats];
+
+// In host code the array's name is only a handle; kernels need its device address, which differs
+// per device and is looked up once per device with that device current.
+static void* g_static_scratch_addr[64] = {nullptr};
+
+extern "C" __attribute__((visibility("default")))
+int deers_b200_attn_bwd_f16_static(deers_ctx* ctx, const deers_attn_desc* d, const void* q, const void* k,
+                                   const void* v, const void* o, const float* lse, const void* d_o, void* dq,
+                                   void* dk, void* dv) {
+    if (!ctx || !d || !q || !k || !v || !o || !lse || !d_o || !dq || !dk || !dv) return DEERS_ERR_NULL;
+    if (d->dtype != DEERS_F16) return DEERS_ERR_DTYPE;
+    if (d->B < 1 || d->H < 1 || d->T < 1 || (d->D != 64 && d->D != 128)) return DEERS_ERR_SHAPE;
+    if (ctx->device < 0 || ctx->device >= 64) return DEERS_ERR_DEVICE;
+    const int64_t* strides[8] = {d->q_strides, d->k_strides, d->v_strides, d->o_strides,
+                                 d->do_strides, d->dq_strides, d->dk_strides, d->dv_strides};
+    const void* ptrs[8] = {q, k, v, o, d_o, dq, dk, dv};
+    for (int i = 0; i < 8; ++i) {
+        if (strides[i][3] != 1 || ((uintptr_t)ptrs[i] & 15u) != 0) return DEERS_ERR_LAYOUT;
+        for (int a = 0; a < 3; ++a)
+            if (strides[i][a] < 0 || ((strides[i][a] * 2) & 15) != 0) return DEERS_ERR_LAYOUT;
+    }
+    const size_t need = attn_bwd_f16_workspace_bytes(d);
+    if (need > sizeof(float) * kStaticScratchFloats) {
+        snprintf(ctx->last_error, sizeof(ctx->last_error),
+                 "deers_b200_attn_bwd_f16_static: needs %zu bytes of scratch, the built-in array holds %zu "
+                 "(B*H*ceil(T/128)*128 must not exceed %zu rows); use deers_b200_attn_bwd with a workspace",
+                 need, sizeof(float) * kStaticScratchFloats, kStaticScratchFloats / 2);
+        return DEERS_ERR_WORKSPACE;
+    }
+    DEERS_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    if (!g_static_scratch_addr[ctx->device]) {
+        void* addr = nullptr;
+        DEERS_CUDA_TRY(ctx, cudaGetSymbolAddress(&addr, g_bwd_static_scratch));
+        g_static_scratch_addr[ctx->device] = addr;
+    }
+    void* scratch = g_static_scratch_addr[ctx->device];
+    // Nothing needs clearing: the first kernel of the backward writes every element of both arrays
+    // (zeros beyond T included) before the other two read them.
+    if (d->D == 64) return bwd_launch<64>(ctx, d, q, k, v, o, lse, d_o, dq, dk, dv, scratch);
+    return bwd_launch<128>(ctx, d, q, k, v, o, lse, d_o, dq, dk, dv, scratch);
+}

@@ -142,6 +142,31 @@ int deers_b200_attn_bwd(deers_ctx* ctx, const deers_attn_desc* desc, const void*
                         void* dk, void* dv, void* workspace, size_t workspace_bytes);
 
 /*
+ * The f16 backward for callers that cannot provide scratch memory.  No counterpart in the
+ * reference (its ops allocate their temporaries freely, `src/storage/cuda.rs:637-644`).
+ *
+ * Who needs it: code that runs where allocation is off limits - inside an allocator or
+ * memory-pool callback, in a host application that freezes its device-memory plan after start-up
+ * and forbids plugins to call cudaMalloc, or on a real-time path that may not take the
+ * allocator's locks.  Same arguments and results as deers_b200_attn_bwd with dtype DEERS_F16, minus
+ * the workspace: the per-row scratch lives in an 8 MiB array inside the library image, which every
+ * GPU that loads the library holds until the process exits.
+ *
+ * Limits and rules:
+ *  - B * H * ceil(T/128)*128 must not exceed 1,048,576 rows; larger problems return
+ *    DEERS_ERR_WORKSPACE (deers_b200_last_error names the sizes) and must use deers_b200_attn_bwd.
+ *  - The call allocates nothing and synchronises nothing.  The first call on each device looks up
+ *    the array's device address (cudaGetSymbolAddress); make that first call outside any stream
+ *    capture.
+ *  - All calls on a device share the one array, which keeps the previous call's contents.  The
+ *    backward's first kernel overwrites everything it later reads, so nothing has to be cleared, but
+ *    two calls that overlap on the GPU (different streams or contexts) race on it: serialise them.
+ */
+int deers_b200_attn_bwd_f16_static(deers_ctx* ctx, const deers_attn_desc* desc, const void* q, const void* k,
+                                   const void* v, const void* o, const float* lse, const void* d_o, void* dq,
+                                   void* dk, void* dv);
+
+/*
  * Status text, the way backend failures become `Error::Cuda(String)`
  * (`src/error.rs:40-41`).  last_error adds the detail of the most recent failure
  * on this context (CUDA error string, or which kernel wait gave up).
