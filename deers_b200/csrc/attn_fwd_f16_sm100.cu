@@ -1,26 +1,44 @@
 // f16 causal attention forward for sm_100a.
 //
-// One CTA owns 128 query rows of one (batch, head) slice and walks the key/value
-// tiles (128 rows each) at or left of its diagonal:
-//   warp 0      TMA producer: Q once, then K and V tiles through a 2-stage ring
-//   warp 1      issues tcgen05.mma: S = Q K^T into a double-buffered TMEM tile,
-//               then O += P V with the accumulator resident in TMEM
-//   warps 2-5   softmax: one thread per query row reads its S row from TMEM,
-//               keeps the running max / sum, writes P (f16) into shared memory in
-//               the swizzled K-major layout the second MMA reads, rescales O in
-//               TMEM only when the row max grew by more than 2^8, and at the end
-//               normalises O and stores O and the row lse.
-// Scale, causal mask, softmax and both products happen in this one pass; the
-// T x T scores never reach global memory.
+// Persistent kernel: one CTA per SM walks a strided, heaviest-first list of work items, an item
+// being 128 query rows of one (batch, head) slice together with the key/value tiles (128 rows
+// each) at or left of its diagonal.  The whole list is treated as ONE stream of (item, KV tile)
+// steps, so loads and the S product run two steps ahead across item boundaries.
+//   warp 0      TMA producer: Q per item (2 buffers), K and V tiles through 2-stage rings
+//   warp 1      issues tcgen05.mma: S = Q K^T into a double-buffered TMEM tile, then
+//               O += P V with P read from TMEM and the accumulator resident in TMEM
+//               (two O accumulators alternate between items)
+//   warps 2-9   two softmax warpgroups that split the 128 key columns of a step; thread r of a
+//               warpgroup owns query row r (= TMEM lane r).  Per step a thread reads its 64
+//               scores, exchanges its partial row max with the twin thread of the other
+//               warpgroup, keeps the running max / partial sum, stores P (f16 pairs) back into
+//               TMEM over the scores it has just read, and rescales its half of O only when the
+//               row max grew by more than 2^8.  At the end of an item the two partial sums are
+//               combined, O is normalised and O and the row lse are stored.
+// Scale, causal mask, softmax and both products happen in this one pass; the T x T scores
+// never reach global memory.
 #include "sm100_ptx.cuh"
 #include "tma_host.cuh"
+
+#if defined(DEERS_TRACE) && DEERS_TRACE == 3
+// Development aid: clock64() stamps of the last CTA's first steps, read back by a debug entry point.
+__device__ unsigned long long g_fwd_trace[16 * 3 * 8];
+#define FWD_TRACE(role, step, ev)                                                                        \
+    do {                                                                                                 \
+        if (blockIdx.x == gridDim.x - 1 && (step) < 16) g_fwd_trace[((step) * 3 + (role)) * 8 + (ev)] = clock64(); \
+    } while (0)
+extern "C" __attribute__((visibility("default"))) int deers_b200_debug_fwd_trace(unsigned long long* out) {
+    return (int)cudaMemcpyFromSymbol(out, g_fwd_trace, sizeof(g_fwd_trace));
+}
+#else
+#define FWD_TRACE(role, step, ev) do {} while (0)
+#endif
 
 namespace {
 using namespace sm100;
 
 constexpr int BM = 128;
 constexpr int BN = 128;
-constexpr int KV_STAGES = 2;
 constexpr uint32_t BLOCK_BYTES = 128 * 128;   // one 64-column block of a 128-row tile
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
@@ -42,252 +60,363 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
+// Dynamic shared memory only; the base must be 1024-byte aligned for the 128-byte swizzle (checked).
 template <int D>
-__global__ void __launch_bounds__(192, 1)
+struct FwdSmem {
+    static constexpr uint32_t TILE = 128u * D * 2u;
+    static constexpr uint32_t Q = 0;                         // two buffers (alternate between items)
+    static constexpr uint32_t K = Q + 2 * TILE;              // two stages
+    static constexpr uint32_t V = K + 2 * TILE;              // two stages
+    static constexpr uint32_t XCH = V + 2 * TILE;            // [2 parities][2 warpgroups][128] partial row max
+    static constexpr uint32_t LX = XCH + 2 * 2 * BM * 4;     // [2 parities][2 warpgroups][128] partial row sum
+    static constexpr uint32_t BARS = LX + 2 * 2 * BM * 4;
+    static constexpr uint32_t TOTAL = BARS + 256;
+};
+
+enum FwdBar { F_Q_FULL = 0, F_Q_EMPTY = 2, F_K_FULL = 4, F_K_EMPTY = 6, F_V_FULL = 8, F_V_EMPTY = 10, F_S_FULL = 12,
+              F_P_FULL = 14, F_PV_DONE = 15, F_XCH = 16, F_LX = 17, F_O_DONE = 18, F_O_FREE = 20, F_COUNT = 22 };
+
+// Work order: groups of 16 slices; inside a group the heaviest (latest) query tiles of all its
+// slices come first (balance) and the group's K and V (a few MB) stay in L2.
+struct WorkCursor {
+    int n;          // index of the item inside this CTA's list
+    int w;          // global item index
+    int j;          // KV tile inside the item
+    int ntiles, qt, bh;
+    __device__ __forceinline__ void load(const FwdParams& p, int nq) {
+        const int BH = p.B * p.H;
+        const int group = w / (16 * nq);
+        const int gsize = min(16, BH - group * 16);
+        const int within = w - group * 16 * nq;
+        qt = nq - 1 - within / gsize;
+        bh = group * 16 + within % gsize;
+        ntiles = p.causal ? qt + 1 : nq;
+    }
+    __device__ __forceinline__ void init(const FwdParams& p, int nq, int n_items) {
+        n = 0; w = blockIdx.x; j = 0;
+        if (w < n_items) load(p, nq);
+    }
+    __device__ __forceinline__ bool valid(int n_items) const { return w < n_items; }
+    __device__ __forceinline__ void advance(const FwdParams& p, int nq, int n_items) {
+        if (++j == ntiles) {
+            j = 0; ++n; w += gridDim.x;
+            if (w < n_items) load(p, nq);
+        }
+    }
+};
+
+template <int D>
+__global__ void __launch_bounds__(320, 1)
 attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                     const __grid_constant__ CUtensorMap tmap_v, const FwdParams p) {
-    constexpr uint32_t TILE_BYTES = 128u * D * 2u;
+    using L = FwdSmem<D>;
+    constexpr uint32_t TILE_BYTES = L::TILE;
     constexpr int DBLK = D / 64;
+    constexpr int DH = D / 2;                                // O columns per softmax warpgroup
     constexpr uint32_t TMEM_COLS = 512;
-    constexpr uint32_t TM_S0 = 0, TM_O = 256;
+    // S of even steps (P in place) | S of odd steps | O of even items | O of odd items
+    constexpr uint32_t TM_S = 0, TM_O = 256;
 
-    extern __shared__ __align__(1024) uint8_t smem_raw[];
-    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint8_t* sQ = smem;
-    uint8_t* sK = sQ + TILE_BYTES;
-    uint8_t* sV = sK + KV_STAGES * TILE_BYTES;
-    uint8_t* sP = sV + KV_STAGES * TILE_BYTES;          // 128 x 128 f16
-
-    __shared__ uint64_t q_full, k_full[KV_STAGES], v_full[KV_STAGES], k_empty[KV_STAGES], v_empty[KV_STAGES];
-    __shared__ uint64_t s_full[2], p_full, pv_done;
-    __shared__ uint32_t tmem_base_s, abort_s, skip_s;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    uint8_t* sQ = smem + L::Q;
+    uint8_t* sK = smem + L::K;
+    uint8_t* sV = smem + L::V;
+    float* xch = reinterpret_cast<float*>(smem + L::XCH);
+    float* lx = reinterpret_cast<float*>(smem + L::LX);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BARS);
+    uint32_t* tmem_base_s = reinterpret_cast<uint32_t*>(bars + F_COUNT);
+    volatile uint32_t* abort_s = tmem_base_s + 1;
+    uint32_t* skip_s = tmem_base_s + 2;
 
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const int nq = (p.T + BM - 1) / BM;
-    // Launch order: groups of 16 slices; inside a group the heaviest tiles of all its slices
-    // come first (balance), and the group's K and V (a few MB) fit in L2 together.
-    const int BH = p.B * p.H;
-    const int group = (int)(blockIdx.x / (16u * nq));
-    const int gsize = min(16, BH - group * 16);
-    const int within = (int)(blockIdx.x - (unsigned)group * 16u * nq);
-    const int qt = nq - 1 - within / gsize;
-    const int bh = group * 16 + within % gsize;
-    const int b = bh / p.H, h = bh % p.H;
-    const int q0 = qt * BM;
-    const int ntiles = p.causal ? qt + 1 : (p.T + BN - 1) / BN;
+    const int n_items = p.B * p.H * nq;
 
     if (threadIdx.x == 0) {
-        abort_s = 0;
-        skip_s = (*(volatile unsigned int*)p.err != 0) ? 1u : 0u;   // an earlier CTA gave up: exit at once
-        mbar_init(&q_full, 1);
-        for (int s = 0; s < KV_STAGES; ++s) {
-            mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1);
-            mbar_init(&k_empty[s], 1); mbar_init(&v_empty[s], 1);
+        *abort_s = 0;
+        uint32_t skip = (*(volatile unsigned int*)p.err != 0) ? 1u : 0u;   // an earlier CTA gave up: exit at once
+        if ((smem_u32(smem) & 1023u) != 0) {
+            atomicCAS(p.err, 0u, DEERS_KERR_FWD_F16 | 0x20);
+            skip = 1;
         }
-        mbar_init(&s_full[0], 1); mbar_init(&s_full[1], 1);
-        mbar_init(&p_full, 128);
-        mbar_init(&pv_done, 1);
+        *skip_s = skip;
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&bars[F_Q_FULL + s], 1); mbar_init(&bars[F_Q_EMPTY + s], 1);
+            mbar_init(&bars[F_K_FULL + s], 1); mbar_init(&bars[F_K_EMPTY + s], 1);
+            mbar_init(&bars[F_V_FULL + s], 1); mbar_init(&bars[F_V_EMPTY + s], 1);
+            mbar_init(&bars[F_S_FULL + s], 1);
+            mbar_init(&bars[F_O_DONE + s], 1); mbar_init(&bars[F_O_FREE + s], 256);
+        }
+        mbar_init(&bars[F_P_FULL], 256);
+        mbar_init(&bars[F_PV_DONE], 1);
+        mbar_init(&bars[F_XCH], 256);
+        mbar_init(&bars[F_LX], 256);
         fence_barrier_init();
         tma_prefetch_desc(&tmap_q); tma_prefetch_desc(&tmap_k); tma_prefetch_desc(&tmap_v);
     }
     __syncthreads();
-    if (skip_s) return;
+    if (*skip_s) return;
     if (warp == 1) {
-        tmem_alloc(&tmem_base_s, TMEM_COLS);
+        tmem_alloc(tmem_base_s, TMEM_COLS);
         tmem_relinquish();
     }
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
-    const uint32_t tmem = tmem_base_s;
-    WaitState ws{&abort_s, p.err};
+    const uint32_t tmem = *tmem_base_s;
+    WaitState ws{abort_s, p.err};
 
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
-            mbar_arrive_expect_tx(&q_full, TILE_BYTES);
+            WorkCursor c;
+            c.init(p, nq, n_items);
+            for (uint32_t g = 0; c.valid(n_items); ++g) {      // g: global step = K / V stage use
+                const int b = c.bh / p.H, h = c.bh % p.H;
+                if (c.j == 0) {
+                    const int qb = c.n & 1;
+                    if (!mbar_wait(ws, &bars[F_Q_EMPTY + qb], (((uint32_t)c.n >> 1) & 1u) ^ 1u, DEERS_KERR_FWD_F16 | 1)) break;
+                    mbar_arrive_expect_tx(&bars[F_Q_FULL + qb], TILE_BYTES);
 #pragma unroll
-            for (int blk = 0; blk < DBLK; ++blk) tma_load_4d(sQ + blk * BLOCK_BYTES, &tmap_q, &q_full, blk * 64, q0, h, b);
-            for (int j = 0; j < ntiles; ++j) {
-                const int st = j % KV_STAGES;
-                const uint32_t ph = (uint32_t)(j / KV_STAGES) & 1u;
-                if (!mbar_wait(ws, &k_empty[st], ph ^ 1u, DEERS_KERR_FWD_F16 | 1)) break;
-                mbar_arrive_expect_tx(&k_full[st], TILE_BYTES);
+                    for (int blk = 0; blk < DBLK; ++blk)
+                        tma_load_4d(sQ + qb * TILE_BYTES + blk * BLOCK_BYTES, &tmap_q, &bars[F_Q_FULL + qb], blk * 64, c.qt * BM, h, b);
+                }
+                const uint32_t st = g & 1u, ph = ((g >> 1) & 1u) ^ 1u;
+                if (!mbar_wait(ws, &bars[F_K_EMPTY + st], ph, DEERS_KERR_FWD_F16 | 2)) break;
+                mbar_arrive_expect_tx(&bars[F_K_FULL + st], TILE_BYTES);
 #pragma unroll
                 for (int blk = 0; blk < DBLK; ++blk)
-                    tma_load_4d(sK + st * TILE_BYTES + blk * BLOCK_BYTES, &tmap_k, &k_full[st], blk * 64, j * BN, h, b);
-                if (!mbar_wait(ws, &v_empty[st], ph ^ 1u, DEERS_KERR_FWD_F16 | 2)) break;
-                mbar_arrive_expect_tx(&v_full[st], TILE_BYTES);
+                    tma_load_4d(sK + st * TILE_BYTES + blk * BLOCK_BYTES, &tmap_k, &bars[F_K_FULL + st], blk * 64, c.j * BN, h, b);
+                if (!mbar_wait(ws, &bars[F_V_EMPTY + st], ph, DEERS_KERR_FWD_F16 | 3)) break;
+                mbar_arrive_expect_tx(&bars[F_V_FULL + st], TILE_BYTES);
 #pragma unroll
                 for (int blk = 0; blk < DBLK; ++blk)
-                    tma_load_4d(sV + st * TILE_BYTES + blk * BLOCK_BYTES, &tmap_v, &v_full[st], blk * 64, j * BN, h, b);
+                    tma_load_4d(sV + st * TILE_BYTES + blk * BLOCK_BYTES, &tmap_v, &bars[F_V_FULL + st], blk * 64, c.j * BN, h, b);
+                c.advance(p, nq, n_items);
             }
         }
     } else if (warp == 1) {
         // ------------------------------ MMA issuer ------------------------------
         if (lane == 0) {
-            constexpr uint32_t IDESC_S = idesc_f16(BM, BN, 0, 0);
-            constexpr uint32_t IDESC_O = idesc_f16(BM, D, 0, 1);
+            constexpr uint32_t IDESC_S = idesc_f16(BM, BN, 0, 0);      // S: K-major A (Q) and B (K)
+            constexpr uint32_t IDESC_O = idesc_f16(BM, D, 0, 1);       // O: A = P from TMEM, B = V MN-major
             // Step-0 descriptors built once; each MMA adds a constant (single-thread issue must
             // stay faster than MMA execution).
             constexpr uint64_t STAGE_STEP = TILE_BYTES >> 4;
-            const uint64_t q_km = desc_kmajor(smem_u32(sQ), 0, BLOCK_BYTES), p_km = desc_kmajor(smem_u32(sP), 0, BLOCK_BYTES);
+            const uint64_t q_km0 = desc_kmajor(smem_u32(sQ), 0, BLOCK_BYTES);
             const uint64_t k_km0 = desc_kmajor(smem_u32(sK), 0, BLOCK_BYTES), v_mn0 = desc_mnmajor(smem_u32(sV), 0, BLOCK_BYTES);
-            auto issue_s = [&](int j) {
-                const uint64_t k_km = k_km0 + (uint64_t)(j % KV_STAGES) * STAGE_STEP;
-                const uint32_t d_tmem = tmem + TM_S0 + (uint32_t)(j & 1) * 128u;
+            WorkCursor sc, pc;                                       // S runs two steps ahead of P V
+            sc.init(p, nq, n_items);
+            pc.init(p, nq, n_items);
+            uint32_t gs = 0, gp = 0;
+            bool ok = true;
+            auto issue_s = [&]() -> bool {
+                const int qb = sc.n & 1;
+                if (sc.j == 0 && !mbar_wait(ws, &bars[F_Q_FULL + qb], ((uint32_t)sc.n >> 1) & 1u, DEERS_KERR_FWD_F16 | 4)) return false;
+                if (!mbar_wait(ws, &bars[F_K_FULL + (gs & 1u)], (gs >> 1) & 1u, DEERS_KERR_FWD_F16 | 5)) return false;
+                tc_fence_after_sync();
+                const uint64_t q_km = q_km0 + (uint64_t)qb * STAGE_STEP, k_km = k_km0 + (uint64_t)(gs & 1u) * STAGE_STEP;
+                const uint32_t d_tmem = tmem + TM_S + (gs & 1u) * 128u;
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks)
                     umma_ss(d_tmem, q_km + kmajor_step(ks, BLOCK_BYTES), k_km + kmajor_step(ks, BLOCK_BYTES), IDESC_S, ks > 0);
-                umma_commit(&s_full[j & 1]);
-                umma_commit(&k_empty[j % KV_STAGES]);
+                umma_commit(&bars[F_S_FULL + (gs & 1u)]);
+                umma_commit(&bars[F_K_EMPTY + (gs & 1u)]);
+                if (sc.j == sc.ntiles - 1) umma_commit(&bars[F_Q_EMPTY + qb]);     // last product reading this Q
+                ++gs;
+                sc.advance(p, nq, n_items);
+                return true;
             };
-            bool ok = mbar_wait(ws, &q_full, 0, DEERS_KERR_FWD_F16 | 3) &&
-                      mbar_wait(ws, &k_full[0], 0, DEERS_KERR_FWD_F16 | 4);
-            if (ok) {
+            for (int pre = 0; ok && pre < 2 && sc.valid(n_items); ++pre) ok = issue_s();
+            while (ok && pc.valid(n_items)) {
+                const uint32_t st = gp & 1u;
+                FWD_TRACE(0, gp, 0);
+                if (!mbar_wait(ws, &bars[F_P_FULL], gp & 1u, DEERS_KERR_FWD_F16 | 6)) break;
+                FWD_TRACE(0, gp, 1);
+                if (!mbar_wait(ws, &bars[F_V_FULL + st], (gp >> 1) & 1u, DEERS_KERR_FWD_F16 | 7)) break;
+                // The accumulator of item n was last used by item n-2: its epilogue must be over.
+                if (pc.j == 0 && !mbar_wait(ws, &bars[F_O_FREE + (pc.n & 1)], (((uint32_t)pc.n >> 1) & 1u) ^ 1u, DEERS_KERR_FWD_F16 | 8)) break;
                 tc_fence_after_sync();
-                issue_s(0);
-            }
-            for (int j = 0; ok && j < ntiles; ++j) {
-                if (j + 1 < ntiles) {
-                    const int jn = j + 1;
-                    if (!mbar_wait(ws, &k_full[jn % KV_STAGES], (uint32_t)(jn / KV_STAGES) & 1u, DEERS_KERR_FWD_F16 | 5)) break;
-                    tc_fence_after_sync();
-                    issue_s(jn);
-                }
-                if (!mbar_wait(ws, &p_full, (uint32_t)j & 1u, DEERS_KERR_FWD_F16 | 6)) break;
-                if (!mbar_wait(ws, &v_full[j % KV_STAGES], (uint32_t)(j / KV_STAGES) & 1u, DEERS_KERR_FWD_F16 | 7)) break;
-                tc_fence_after_sync();
-                const uint64_t v_mn = v_mn0 + (uint64_t)(j % KV_STAGES) * STAGE_STEP;
+                const uint64_t v_mn = v_mn0 + (uint64_t)st * STAGE_STEP;
+                const uint32_t o_tmem = tmem + TM_O + (uint32_t)(pc.n & 1) * D;
+                const uint32_t p_tmem = tmem + TM_S + st * 128u;       // P sits where this step's S was
 #pragma unroll
                 for (int ks = 0; ks < BN / 16; ++ks)
-                    umma_ss(tmem + TM_O, p_km + kmajor_step(ks, BLOCK_BYTES), v_mn + mnmajor_step(ks), IDESC_O, (j > 0 || ks > 0));
-                umma_commit(&pv_done);
-                umma_commit(&v_empty[j % KV_STAGES]);
+                    umma_ts(o_tmem, p_tmem + (uint32_t)(ks >> 2) * 64u + (uint32_t)(ks & 3) * 8u, v_mn + mnmajor_step(ks),
+                            IDESC_O, (pc.j > 0 || ks > 0));
+                umma_commit(&bars[F_PV_DONE]);
+                umma_commit(&bars[F_V_EMPTY + st]);
+                FWD_TRACE(0, gp, 2);
+                if (pc.j == pc.ntiles - 1) umma_commit(&bars[F_O_DONE + (pc.n & 1)]);
+                ++gp;
+                pc.advance(p, nq, n_items);
+                // S of step gp+1 reuses the TMEM tile whose P the product above has just consumed.
+                if (sc.valid(n_items)) ok = issue_s();
+                FWD_TRACE(0, gp - 1, 3);
             }
         }
     } else {
         // ------------------------------ softmax + epilogue ------------------------------
+        const int g = (warp - 2) >> 2;                          // warpgroup: key columns [64g, 64g+64)
         const int lane_base = (warp & 3) * 32;
         const int row = lane_base + lane;                       // row inside the query tile == TMEM lane
         const uint32_t t_lane = (uint32_t)lane_base << 16;
         const float sl2 = p.scale * LOG2E;
-        float m_used = -INFINITY, l = 0.f;
+        uint32_t gstep = 0;                                     // global step counter
         bool alive = true;
 
-        for (int j = 0; j < ntiles; ++j) {
-            if (!__all_sync(0xffffffffu, mbar_wait(ws, &s_full[j & 1], (uint32_t)(j >> 1) & 1u, DEERS_KERR_FWD_F16 | 8))) { alive = false; break; }
+        // Deferred epilogue of the previous item (runs after this item's first P has been handed over).
+        int pend_n = -1, pend_grow = 0, pend_bh = 0;
+        float pend_m = 0.f, pend_l = 0.f;
+        auto epilogue = [&]() -> bool {
+            if (pend_n < 0) return true;
+            const int n = pend_n;
+            pend_n = -1;
+            // Combine the two partial row sums.
+            float* lxp = lx + (n & 1) * 2 * BM;
+            lxp[g * BM + row] = pend_l;
+            mbar_arrive(&bars[F_LX]);
+            if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[F_LX], (uint32_t)n & 1u, DEERS_KERR_FWD_F16 | 9))) return false;
+            const float l = pend_l + lxp[(g ^ 1) * BM + row];
+            if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[F_O_DONE + (n & 1)], ((uint32_t)n >> 1) & 1u, DEERS_KERR_FWD_F16 | 10))) return false;
             tc_fence_after_sync();
-            float s[128];
-            {
-                const uint32_t ts = tmem + TM_S0 + (uint32_t)(j & 1) * 128u + t_lane;
+            const float inv = 1.f / l;
+            const int b = pend_bh / p.H, h = pend_bh % p.H;
+            __half* orow = p.o + b * p.so_b + h * p.so_h + (long long)pend_grow * p.so_t + g * DH;
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t r[32];
-                    tmem_ld_x32(ts + c * 32, r);
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) s[c * 32 + i] = __uint_as_float(r[i]);
-                }
+            for (int c = 0; c < DH / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld_x32(tmem + TM_O + (uint32_t)(n & 1) * D + t_lane + g * DH + c * 32, r);
                 tmem_wait_ld();
-            }
-            // Tiles that touch the diagonal or the end of the sequence are scaled
-            // here and masked with -inf; all others keep raw scores and fold the
-            // scale into the exponent's FFMA.
-            const int k0 = j * BN;
-            const bool edge = (p.causal && j == qt) || (k0 + BN > p.T);
-            float c1 = sl2;
-            if (edge) {
-#pragma unroll
-                for (int i = 0; i < 128; ++i) {
-                    const int col = k0 + i;
-                    const bool masked = (col >= p.T) || (p.causal && col > q0 + row);
-                    s[i] = masked ? -INFINITY : s[i] * sl2;
+                if (c == DH / 32 - 1) {                         // accumulator is in registers: release it
+                    tc_fence_before_sync();
+                    mbar_arrive(&bars[F_O_FREE + (n & 1)]);
                 }
-                c1 = 1.0f;
-            }
-            float mx;
-            if (c1 >= 0.f) {
-                mx = s[0];
+                if (pend_grow < p.T) {
 #pragma unroll
-                for (int i = 1; i < 128; ++i) mx = fmaxf(mx, s[i]);
-            } else {
-                mx = s[0];
-#pragma unroll
-                for (int i = 1; i < 128; ++i) mx = fminf(mx, s[i]);
+                    for (int q8 = 0; q8 < 4; ++q8) {
+                        uint4 v;
+                        v.x = pack_half2(__uint_as_float(r[q8 * 8 + 0]) * inv, __uint_as_float(r[q8 * 8 + 1]) * inv);
+                        v.y = pack_half2(__uint_as_float(r[q8 * 8 + 2]) * inv, __uint_as_float(r[q8 * 8 + 3]) * inv);
+                        v.z = pack_half2(__uint_as_float(r[q8 * 8 + 4]) * inv, __uint_as_float(r[q8 * 8 + 5]) * inv);
+                        v.w = pack_half2(__uint_as_float(r[q8 * 8 + 6]) * inv, __uint_as_float(r[q8 * 8 + 7]) * inv);
+                        *reinterpret_cast<uint4*>(orow + c * 32 + q8 * 8) = v;
+                    }
+                }
             }
-            mx *= c1;
-            const float m_new = fmaxf(m_used, mx);
-            // Lazy rescale: keep the old reference max unless this row grew by more than 2^8.
-            const bool grow = (j > 0) && (m_new - m_used > RESCALE_THRESHOLD);
-            const float m_cur = (j == 0 || grow) ? m_new : m_used;
-            const float m_safe = (m_cur == -INFINITY) ? 0.f : m_cur;
-            const float alpha = (j == 0) ? 0.f : ex2(m_used - m_safe);
-            const bool warp_grow = __any_sync(0xffffffffu, grow);
+            if (g == 0 && pend_grow < p.T) p.lse[(long long)pend_bh * p.T + pend_grow] = (pend_m + log2f(l)) * LN2;
+            return true;
+        };
 
-            uint32_t pk[64];
-            float rs = 0.f;
-#pragma unroll
-            for (int i = 0; i < 64; ++i) {
-                const float e0 = ex2(fmaf(s[2 * i], c1, -m_safe));
-                const float e1 = ex2(fmaf(s[2 * i + 1], c1, -m_safe));
-                rs += e0 + e1;
-                pk[i] = pack_half2(e0, e1);
-            }
-            l = l * alpha + rs;
-            m_used = m_cur;
-
-            if (j > 0) {
-                // P's buffer and the O accumulator are free once PV(j-1) has finished.
-                if (!__all_sync(0xffffffffu, mbar_wait(ws, &pv_done, (uint32_t)(j - 1) & 1u, DEERS_KERR_FWD_F16 | 9))) { alive = false; break; }
+        WorkCursor c;
+        c.init(p, nq, n_items);
+        while (alive && c.valid(n_items)) {
+            const int n = c.n, qt = c.qt, ntiles = c.ntiles, bh = c.bh;
+            const int q0 = qt * BM;
+            float m_used = -INFINITY, l = 0.f;                  // l: partial sum over this warpgroup's columns
+            for (int j = 0; j < ntiles; ++j, ++gstep) {
+                const uint32_t sb = gstep & 1u;
+                const bool tr = lane == 0 && (warp == 2 || warp == 6);
+                if (tr) FWD_TRACE(1 + g, gstep, 0);
+                if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[F_S_FULL + sb], (gstep >> 1) & 1u, DEERS_KERR_FWD_F16 | 11))) { alive = false; break; }
                 tc_fence_after_sync();
-                if (warp_grow) {
+                float s[64];
+                {
+                    const uint32_t ts = tmem + TM_S + sb * 128u + t_lane + 64 * g;
 #pragma unroll
-                    for (int c = 0; c < D / 32; ++c) {
+                    for (int cc = 0; cc < 2; ++cc) {
                         uint32_t r[32];
-                        tmem_ld_x32(tmem + TM_O + t_lane + c * 32, r);
+                        tmem_ld_x32(ts + cc * 32, r);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) s[cc * 32 + i] = __uint_as_float(r[i]);
+                    }
+                    tmem_wait_ld();
+                }
+                if (tr) FWD_TRACE(1 + g, gstep, 1);
+                // Steps that touch the diagonal or the end of the sequence are scaled here and
+                // masked with -inf; all others keep raw scores and fold the scale into the
+                // exponent's FFMA.
+                const int k0 = j * BN;
+                const bool edge = (p.causal && j == qt) || (k0 + BN > p.T);
+                float c1 = sl2;
+                if (edge) {
+#pragma unroll
+                    for (int i = 0; i < 64; ++i) {
+                        const int col = k0 + 64 * g + i;
+                        const bool masked = (col >= p.T) || (p.causal && col > q0 + row);
+                        s[i] = masked ? -INFINITY : s[i] * sl2;
+                    }
+                    c1 = 1.0f;
+                }
+                float mx = s[0];
+                if (c1 >= 0.f) {
+#pragma unroll
+                    for (int i = 1; i < 64; ++i) mx = fmaxf(mx, s[i]);
+                } else {
+#pragma unroll
+                    for (int i = 1; i < 64; ++i) mx = fminf(mx, s[i]);
+                }
+                mx *= c1;
+                // Exchange the partial row max with the twin thread of the other warpgroup.
+                if (tr) FWD_TRACE(1 + g, gstep, 2);
+                float* xp = xch + sb * 2 * BM;
+                xp[g * BM + row] = mx;
+                mbar_arrive(&bars[F_XCH]);
+                if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[F_XCH], gstep & 1u, DEERS_KERR_FWD_F16 | 12))) { alive = false; break; }
+                mx = fmaxf(mx, xp[(g ^ 1) * BM + row]);
+                if (tr) FWD_TRACE(1 + g, gstep, 3);
+
+                const float m_new = fmaxf(m_used, mx);
+                // Lazy rescale: keep the old reference max unless this row grew by more than 2^8.
+                const bool grow = (j > 0) && (m_new - m_used > RESCALE_THRESHOLD);
+                const float m_cur = (j == 0 || grow) ? m_new : m_used;
+                const float m_safe = (m_cur == -INFINITY) ? 0.f : m_cur;
+                const float alpha = (j == 0) ? 0.f : ex2(m_used - m_safe);
+                const bool warp_grow = __any_sync(0xffffffffu, grow);
+
+                uint32_t pk[32];
+                float rs = 0.f;
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const float e0 = ex2(fmaf(s[2 * i], c1, -m_safe));
+                    const float e1 = ex2(fmaf(s[2 * i + 1], c1, -m_safe));
+                    rs += e0 + e1;
+                    pk[i] = pack_half2(e0, e1);
+                }
+                l = l * alpha + rs;
+                m_used = m_cur;
+                if (tr) FWD_TRACE(1 + g, gstep, 4);
+
+                if (j > 0 && warp_grow) {
+                    // O += P V of the previous step must have landed before O is rescaled.
+                    if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[F_PV_DONE], (gstep - 1u) & 1u, DEERS_KERR_FWD_F16 | 13))) { alive = false; break; }
+                    tc_fence_after_sync();
+                    const uint32_t to = tmem + TM_O + (uint32_t)(n & 1) * D + t_lane + g * DH;
+#pragma unroll
+                    for (int cc = 0; cc < DH / 32; ++cc) {
+                        uint32_t r[32];
+                        tmem_ld_x32(to + cc * 32, r);
                         tmem_wait_ld();
 #pragma unroll
                         for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-                        tmem_st_x32(tmem + TM_O + t_lane + c * 32, r);
-                    }
-                    tmem_wait_st();
-                }
-            }
-            // P row -> shared memory, K-major with the 128-byte swizzle: 16 chunks of 8 f16.
-#pragma unroll
-            for (int ch = 0; ch < 16; ++ch) {
-                uint4 v = make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
-                *reinterpret_cast<uint4*>(sP + (ch >> 3) * BLOCK_BYTES + sw128_chunk_offset(row, ch & 7)) = v;
-            }
-            fence_proxy_async_smem();
-            tc_fence_before_sync();
-            mbar_arrive(&p_full);
-        }
-
-        if (alive && __all_sync(0xffffffffu, mbar_wait(ws, &pv_done, (uint32_t)(ntiles - 1) & 1u, DEERS_KERR_FWD_F16 | 10))) {
-            tc_fence_after_sync();
-            const float inv = 1.f / l;
-            const int grow_ = q0 + row;
-            __half* orow = p.o + b * p.so_b + h * p.so_h + (long long)grow_ * p.so_t;
-#pragma unroll
-            for (int c = 0; c < D / 32; ++c) {
-                uint32_t r[32];
-                tmem_ld_x32(tmem + TM_O + t_lane + c * 32, r);
-                tmem_wait_ld();
-                if (grow_ < p.T) {
-#pragma unroll
-                    for (int g = 0; g < 4; ++g) {
-                        uint4 v;
-                        v.x = pack_half2(__uint_as_float(r[g * 8 + 0]) * inv, __uint_as_float(r[g * 8 + 1]) * inv);
-                        v.y = pack_half2(__uint_as_float(r[g * 8 + 2]) * inv, __uint_as_float(r[g * 8 + 3]) * inv);
-                        v.z = pack_half2(__uint_as_float(r[g * 8 + 4]) * inv, __uint_as_float(r[g * 8 + 5]) * inv);
-                        v.w = pack_half2(__uint_as_float(r[g * 8 + 6]) * inv, __uint_as_float(r[g * 8 + 7]) * inv);
-                        *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = v;
+                        tmem_st_x32(to + cc * 32, r);
                     }
                 }
+                // P replaces this warpgroup's half of S in TMEM (32 packed columns).
+                tmem_st_x32(tmem + TM_S + sb * 128u + t_lane + 64 * g, pk);
+                tmem_wait_st();
+                tc_fence_before_sync();
+                mbar_arrive(&bars[F_P_FULL]);
+                if (tr) FWD_TRACE(1 + g, gstep, 5);
+                if (j == 0 && !epilogue()) { alive = false; break; }          // previous item's O tile
             }
-            if (grow_ < p.T) p.lse[(long long)bh * p.T + grow_] = (m_used + log2f(l)) * LN2;
+            if (!alive) break;
+            pend_n = n; pend_grow = q0 + row; pend_bh = bh; pend_m = m_used; pend_l = l;
+            // advance the cursor by a whole item
+            c.j = ntiles - 1;
+            c.advance(p, nq, n_items);
         }
+        if (alive) epilogue();
     }
 
     __syncwarp();
@@ -308,14 +437,15 @@ int fwd_launch(deers_ctx* ctx, const deers_attn_desc* d, const void* q, const vo
     p.o = (__half*)o; p.lse = lse;
     p.so_b = d->o_strides[0]; p.so_h = d->o_strides[1]; p.so_t = d->o_strides[2];
     p.B = d->B; p.H = d->H; p.T = d->T; p.causal = d->causal; p.scale = d->scale; p.err = ctx->dev_err;
-    const size_t smem = (size_t)(1 + 2 * KV_STAGES) * 128 * D * 2 + 128 * 128 * 2 + 1024;
+    const size_t smem = FwdSmem<D>::TOTAL;
     DEERS_CUDA_TRY(ctx, cudaFuncSetAttribute(attn_fwd_f16_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const long long nq = (d->T + BM - 1) / BM;
-    const long long grid = nq * d->B * d->H;
-    if (grid > 0x7fffffffLL) return DEERS_ERR_SHAPE;
+    const long long items = nq * d->B * d->H;
+    if (items > 0x7fffffffLL) return DEERS_ERR_SHAPE;
+    const unsigned grid = (unsigned)(items < ctx->sm_count ? items : ctx->sm_count);
     {
         KernelTimerScope ts(ctx, DEERS_K_FWD);
-        attn_fwd_f16_kernel<D><<<(unsigned)grid, 192, smem, ctx->stream>>>(tq, tk, tv, p);
+        attn_fwd_f16_kernel<D><<<grid, 320, smem, ctx->stream>>>(tq, tk, tv, p);
     }
     ctx->launches += 1;
     DEERS_CUDA_TRY(ctx, cudaGetLastError());
