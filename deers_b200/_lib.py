@@ -19,7 +19,8 @@ SYMBOLS = [
     "deers_b200_memcpy_d2h", "deers_b200_memcpy_d2d", "deers_b200_sync", "deers_b200_attn_workspace_bytes",
     "deers_b200_attn_fwd", "deers_b200_attn_bwd", "deers_b200_status_string", "deers_b200_last_error",
     "deers_b200_launch_count", "deers_b200_selftest_umma", "deers_b200_kernel_timing",
-    "deers_b200_kernel_time", "deers_b200_attn_bwd_f16_static",
+    "deers_b200_kernel_time", "deers_b200_attn_bwd_f16_static", "deers_b200_attn_host_scratch_bytes",
+    "deers_b200_attn_fwd_bwd_host",
 ]
 K_FWD, K_BWD_PREP, K_BWD_MAIN, K_BWD_DQ = range(4)
 
@@ -66,6 +67,9 @@ def lib() -> ctypes.CDLL:
     L.deers_b200_attn_fwd.argtypes = [vp, dp, vp, vp, vp, vp, vp, vp, sz]
     L.deers_b200_attn_bwd.argtypes = [vp, dp] + [vp] * 10 + [sz]
     L.deers_b200_attn_bwd_f16_static.argtypes = [vp, dp] + [vp] * 9
+    L.deers_b200_attn_host_scratch_bytes.argtypes = [dp, i32]
+    L.deers_b200_attn_host_scratch_bytes.restype = sz
+    L.deers_b200_attn_fwd_bwd_host.argtypes = [vp, dp] + [vp] * 9 + [i32, vp, sz]
     L.deers_b200_status_string.argtypes = [i32]
     L.deers_b200_status_string.restype = ctypes.c_char_p
     L.deers_b200_last_error.argtypes = [vp]

@@ -35,6 +35,10 @@ struct deers_ctx {
     void* encode_tiled;
     bool timing;
     deers_ktimer kt[DEERS_K_COUNT];
+    // Side streams and events of the host-tensor pipeline (created on first use).
+    cudaStream_t h2d_stream, d2h_stream;
+    cudaEvent_t pipe_ev[3][3];      // [buffer set][h2d done, compute done, d2h done]
+    bool pipe_ready;
 };
 
 // Brackets one kernel launch with events when timing is on.  A full ring drops the sample.

@@ -94,6 +94,12 @@ extern "C" void deers_b200_destroy(deers_ctx* ctx) {
     if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
     if (ctx->host_err) cudaFreeHost(ctx->host_err);
     if (ctx->dev_err) cudaFree(ctx->dev_err);
+    if (ctx->pipe_ready) {
+        cudaStreamDestroy(ctx->h2d_stream);
+        cudaStreamDestroy(ctx->d2h_stream);
+        for (int s2 = 0; s2 < 3; ++s2)
+            for (int e = 0; e < 3; ++e) cudaEventDestroy(ctx->pipe_ev[s2][e]);
+    }
     for (int k = 0; k < DEERS_K_COUNT; ++k) {
         deers_ktimer* t = &ctx->kt[k];
         if (t->start && t->stop)
@@ -302,6 +308,107 @@ extern "C" int deers_b200_kernel_time(deers_ctx* ctx, int kind, int reset, doubl
     *launches = t->launches;
     if (reset) { t->total_ms = 0.0; t->launches = 0; }
     return DEERS_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Host-tensor pipeline
+// ---------------------------------------------------------------------------
+namespace {
+constexpr int kPipeSets = 3;
+
+struct ChunkLayout {
+    size_t tensor_bytes;    // one [chunk, T, D] tensor
+    size_t lse_bytes;
+    size_t ws_bytes;
+    size_t set_bytes;       // 8 tensors + lse + workspace, each 256-byte aligned
+};
+
+ChunkLayout chunk_layout(const deers_attn_desc* d, int chunk) {
+    ChunkLayout l;
+    const size_t es = d->dtype == DEERS_F16 ? 2 : 4;
+    l.tensor_bytes = align_up((size_t)chunk * d->T * d->D * es, 256);
+    l.lse_bytes = align_up((size_t)chunk * d->T * sizeof(float), 256);
+    deers_attn_desc c;
+    deers_b200_attn_desc_compact(&c, chunk, 1, d->T, d->D, d->dtype, d->causal, d->scale);
+    l.ws_bytes = align_up(deers_b200_attn_workspace_bytes(&c, 1), 256);
+    l.set_bytes = 8 * l.tensor_bytes + l.lse_bytes + l.ws_bytes;
+    return l;
+}
+}  // namespace
+
+extern "C" size_t deers_b200_attn_host_scratch_bytes(const deers_attn_desc* d, int chunk_slices) {
+    if (check_desc(d) != DEERS_OK || chunk_slices < 1) return 0;
+    return kPipeSets * chunk_layout(d, chunk_slices).set_bytes;
+}
+
+extern "C" int deers_b200_attn_fwd_bwd_host(deers_ctx* ctx, const deers_attn_desc* d, const void* q_host,
+                                            const void* k_host, const void* v_host, const void* do_host, void* o_host,
+                                            float* lse_host, void* dq_host, void* dk_host, void* dv_host,
+                                            int chunk_slices, void* device_scratch, size_t scratch_bytes) {
+    if (!ctx || !q_host || !k_host || !v_host || !do_host || !o_host || !dq_host || !dk_host || !dv_host) return DEERS_ERR_NULL;
+    int rc = check_desc(d);
+    if (rc) return rc;
+    if (chunk_slices < 1) return DEERS_ERR_SHAPE;
+    const size_t need = deers_b200_attn_host_scratch_bytes(d, chunk_slices);
+    if (!device_scratch || scratch_bytes < need || ((uintptr_t)device_scratch & 255u) != 0) return DEERS_ERR_WORKSPACE;
+    DEERS_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    if (!ctx->pipe_ready) {
+        DEERS_CUDA_TRY(ctx, cudaStreamCreateWithFlags(&ctx->h2d_stream, cudaStreamNonBlocking));
+        DEERS_CUDA_TRY(ctx, cudaStreamCreateWithFlags(&ctx->d2h_stream, cudaStreamNonBlocking));
+        for (int s = 0; s < kPipeSets; ++s)
+            for (int e = 0; e < 3; ++e) DEERS_CUDA_TRY(ctx, cudaEventCreateWithFlags(&ctx->pipe_ev[s][e], cudaEventDisableTiming));
+        ctx->pipe_ready = true;
+    }
+    const ChunkLayout l = chunk_layout(d, chunk_slices);
+    const size_t es = d->dtype == DEERS_F16 ? 2 : 4;
+    const long long n_slices = (long long)d->B * d->H;
+    const size_t slice_bytes = (size_t)d->T * d->D * es;
+    const void* in_host[4] = {q_host, k_host, v_host, do_host};
+    void* out_host[4] = {o_host, dq_host, dk_host, dv_host};
+
+    // Inputs already on the context's stream (e.g. earlier work of the caller) come first.
+    cudaEvent_t start = ctx->pipe_ev[0][2];
+    DEERS_CUDA_TRY(ctx, cudaEventRecord(start, ctx->stream));
+    DEERS_CUDA_TRY(ctx, cudaStreamWaitEvent(ctx->h2d_stream, start, 0));
+
+    int chunk_idx = 0;
+    for (long long s0 = 0; s0 < n_slices; s0 += chunk_slices, ++chunk_idx) {
+        const int n = (int)((n_slices - s0) < chunk_slices ? (n_slices - s0) : chunk_slices);
+        const int set = chunk_idx % kPipeSets;
+        char* base = (char*)device_scratch + (size_t)set * l.set_bytes;
+        void* dev[8];
+        for (int t = 0; t < 8; ++t) dev[t] = base + (size_t)t * l.tensor_bytes;        // q k v do | o dq dk dv
+        float* lse_dev = (float*)(base + 8 * l.tensor_bytes);
+        void* ws = base + 8 * l.tensor_bytes + l.lse_bytes;
+        cudaEvent_t h2d_done = ctx->pipe_ev[set][0], comp_done = ctx->pipe_ev[set][1], d2h_done = ctx->pipe_ev[set][2];
+
+        // This buffer set was last used kPipeSets chunks ago: its results must have left the device.
+        if (chunk_idx >= kPipeSets) DEERS_CUDA_TRY(ctx, cudaStreamWaitEvent(ctx->h2d_stream, d2h_done, 0));
+        for (int t = 0; t < 4; ++t)
+            DEERS_CUDA_TRY(ctx, cudaMemcpyAsync(dev[t], (const char*)in_host[t] + (size_t)s0 * slice_bytes,
+                                                (size_t)n * slice_bytes, cudaMemcpyHostToDevice, ctx->h2d_stream));
+        DEERS_CUDA_TRY(ctx, cudaEventRecord(h2d_done, ctx->h2d_stream));
+
+        DEERS_CUDA_TRY(ctx, cudaStreamWaitEvent(ctx->stream, h2d_done, 0));
+        deers_attn_desc c;
+        deers_b200_attn_desc_compact(&c, n, 1, d->T, d->D, d->dtype, d->causal, d->scale);
+        if ((rc = deers_b200_attn_fwd(ctx, &c, dev[0], dev[1], dev[2], dev[4], lse_dev, nullptr, 0))) return rc;
+        if ((rc = deers_b200_attn_bwd(ctx, &c, dev[0], dev[1], dev[2], dev[4], lse_dev, dev[3], dev[5], dev[6], dev[7], ws,
+                                      l.ws_bytes)))
+            return rc;
+        DEERS_CUDA_TRY(ctx, cudaEventRecord(comp_done, ctx->stream));
+
+        DEERS_CUDA_TRY(ctx, cudaStreamWaitEvent(ctx->d2h_stream, comp_done, 0));
+        for (int t = 0; t < 4; ++t)
+            DEERS_CUDA_TRY(ctx, cudaMemcpyAsync((char*)out_host[t] + (size_t)s0 * slice_bytes, dev[4 + t],
+                                                (size_t)n * slice_bytes, cudaMemcpyDeviceToHost, ctx->d2h_stream));
+        if (lse_host)
+            DEERS_CUDA_TRY(ctx, cudaMemcpyAsync(lse_host + (size_t)s0 * d->T, lse_dev, (size_t)n * d->T * sizeof(float),
+                                                cudaMemcpyDeviceToHost, ctx->d2h_stream));
+        DEERS_CUDA_TRY(ctx, cudaEventRecord(d2h_done, ctx->d2h_stream));
+    }
+    DEERS_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->d2h_stream));
+    return deers_b200_sync(ctx);
 }
 
 extern "C" int deers_b200_selftest_umma(deers_ctx* ctx, float* max_abs_err) {

@@ -223,3 +223,33 @@ class CausalAttention:
 def causal_attention(q, k, v, scale: Optional[float] = None) -> torch.Tensor:
     """Tensor-method form (house style of src/tensor.rs:379-381): new(..).forward()."""
     return CausalAttention.new(q, k, v, scale).forward()
+
+
+def attention_fwd_bwd_host(q, k, v, d_o, scale: float, causal: bool = True, chunk_slices: int = 64,
+                           device: Optional[torch.device] = None, scratch: Optional[torch.Tensor] = None,
+                           out=None):
+    """Forward + backward on HOST tensors (compact [B,H,T,D], ideally pinned) through the pipelined
+    C-ABI call: returns (o, dq, dk, dv, lse) as host tensors.  `scratch` is device memory the caller
+    may keep between calls; `out` optional preallocated (o, dq, dk, dv, lse) host tensors."""
+    _check_inputs("attention_fwd_bwd_host", (q, k, v, d_o))
+    for t in (q, k, v, d_o):
+        if t.device.type != "cpu" or not t.is_contiguous():
+            raise LayoutMismatch("attention_fwd_bwd_host: expected compact host tensors")
+    device = device or torch.device("cuda", torch.cuda.current_device())
+    ctx = Context.current(device)
+    B, H, T, D = q.shape
+    d = _lib.AttnDesc()
+    _lib.lib().deers_b200_attn_desc_compact(ctypes.byref(d), B, H, T, D, _DTYPES[q.dtype], int(causal), scale)
+    need = int(_lib.lib().deers_b200_attn_host_scratch_bytes(ctypes.byref(d), chunk_slices))
+    if scratch is None or scratch.numel() * scratch.element_size() < need:
+        scratch = torch.empty(need, dtype=torch.uint8, device=device)
+    if out is None:
+        pin = q.is_pinned()
+        out = tuple(torch.empty(q.shape, dtype=q.dtype, pin_memory=pin) for _ in range(4)) + \
+              (torch.empty((B, H, T), dtype=torch.float32, pin_memory=pin),)
+    o, dq, dk, dv, lse = out
+    _lib.check(_lib.lib().deers_b200_attn_fwd_bwd_host(
+        ctx.handle, ctypes.byref(d), q.data_ptr(), k.data_ptr(), v.data_ptr(), d_o.data_ptr(), o.data_ptr(),
+        lse.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), chunk_slices, scratch.data_ptr(),
+        scratch.numel() * scratch.element_size()), ctx.handle)
+    return o, dq, dk, dv, lse

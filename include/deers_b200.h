@@ -142,6 +142,24 @@ int deers_b200_attn_bwd(deers_ctx* ctx, const deers_attn_desc* desc, const void*
                         void* dk, void* dv, void* workspace, size_t workspace_bytes);
 
 /*
+ * Forward + backward on HOST tensors, for callers whose tensors live in host memory (the
+ * reference moves data between host and device with `clone_htod` / `clone_dtoh`,
+ * `src/storage/cuda.rs:692-706,1541-1555`, one whole tensor at a time).  q, k, v, d_o (inputs) and
+ * o, dq, dk, dv (outputs; lse_host may be NULL) are compact [B,H,T,D] host arrays, ideally pinned.
+ * The (batch x head) slices are processed in chunks of `chunk_slices`; host->device copies of the
+ * next chunk, the kernels of the current one and the device->host copies of the previous one run
+ * on three streams, so the PCIe link is used in both directions while the GPU computes.
+ * `device_scratch` is caller-owned device memory of at least
+ * deers_b200_attn_host_scratch_bytes(desc, chunk_slices) bytes (256-byte aligned); nothing is
+ * allocated inside.  The call returns after the last copy has finished.
+ */
+size_t deers_b200_attn_host_scratch_bytes(const deers_attn_desc* desc, int chunk_slices);
+int deers_b200_attn_fwd_bwd_host(deers_ctx* ctx, const deers_attn_desc* desc, const void* q_host, const void* k_host,
+                                 const void* v_host, const void* do_host, void* o_host, float* lse_host, void* dq_host,
+                                 void* dk_host, void* dv_host, int chunk_slices, void* device_scratch,
+                                 size_t scratch_bytes);
+
+/*
  * The f16 backward for callers that cannot provide scratch memory.  No counterpart in the
  * reference (its ops allocate their temporaries freely, `src/storage/cuda.rs:637-644`).
  *
