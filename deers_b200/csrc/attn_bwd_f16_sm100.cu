@@ -771,39 +771,47 @@ attn_bwd_dq_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
 }
 
 // delta[row] = sum_d dO[row][d] * O[row][d] and lse2[row] = lse[row] * log2(e) on the padded
-// [B*H][Tpad] grid (0 beyond T).  One warp per row.
+// [B*H][Tpad] grid (0 beyond T).  D/8 lanes share a row (16-byte loads), so a warp covers
+// 256 / D rows per step; grid-stride over row groups.
 template <int D>
 __global__ void __launch_bounds__(256)
 attn_bwd_prep_f16_kernel(const __half* __restrict__ o, const __half* __restrict__ d_o, const float* __restrict__ lse,
                          float* __restrict__ delta, float* __restrict__ lse2, int B, int H, int T, int Tpad,
                          long long so_b, long long so_h, long long so_t, long long sdo_b, long long sdo_h,
                          long long sdo_t) {
-    const long long row = (long long)blockIdx.x * 8 + threadIdx.x / 32;
+    constexpr int LPR = D / 8;                               // lanes per row
+    constexpr int RPW = 32 / LPR;                            // rows per warp step
     const int lane = threadIdx.x % 32;
-    if (row >= (long long)B * H * Tpad) return;
-    const int t = (int)(row % Tpad);
-    const int bh = (int)(row / Tpad);
-    constexpr int PER = D / 32;                              // 2 or 4 elements per lane
-    if (t >= T) {
-        if (lane == 0) { delta[row] = 0.f; lse2[row] = 0.f; }
-        return;
-    }
-    const int b = bh / H, h = bh % H;
-    const __half* orow = o + b * so_b + h * so_h + (long long)t * so_t + lane * PER;
-    const __half* grow = d_o + b * sdo_b + h * sdo_h + (long long)t * sdo_t + lane * PER;
-    float s = 0.f;
+    const int sub = lane % LPR, rw = lane / LPR;
+    const long long rows = (long long)B * H * Tpad;
+    const long long warp_global = (long long)blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
+    const long long warp_count = (long long)gridDim.x * (blockDim.x / 32);
+    for (long long base = warp_global * RPW; base < rows; base += warp_count * RPW) {
+        const long long row = base + rw;
+        float s = 0.f;
+        const bool in_grid = row < rows;
+        const int t = in_grid ? (int)(row % Tpad) : 0;
+        const int bh = in_grid ? (int)(row / Tpad) : 0;
+        const bool valid = in_grid && t < T;
+        if (valid) {
+            const int b = bh / H, h = bh % H;
+            const uint4 a = *reinterpret_cast<const uint4*>(o + b * so_b + h * so_h + (long long)t * so_t + sub * 8);
+            const uint4 g = *reinterpret_cast<const uint4*>(d_o + b * sdo_b + h * sdo_h + (long long)t * sdo_t + sub * 8);
+            const uint32_t av[4] = {a.x, a.y, a.z, a.w}, gv[4] = {g.x, g.y, g.z, g.w};
 #pragma unroll
-    for (int e = 0; e < PER; e += 2) {
-        const float2 a = __half22float2(*reinterpret_cast<const __half2*>(orow + e));
-        const float2 g = __half22float2(*reinterpret_cast<const __half2*>(grow + e));
-        s = fmaf(a.x, g.x, s);
-        s = fmaf(a.y, g.y, s);
-    }
+            for (int e = 0; e < 4; ++e) {
+                const float2 af = __half22float2(*reinterpret_cast<const __half2*>(&av[e]));
+                const float2 gf = __half22float2(*reinterpret_cast<const __half2*>(&gv[e]));
+                s = fmaf(af.x, gf.x, s);
+                s = fmaf(af.y, gf.y, s);
+            }
+        }
 #pragma unroll
-    for (int off = 16; off >= 1; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-    if (lane == 0) {
-        delta[row] = s;
-        lse2[row] = lse[(long long)bh * T + t] * LOG2E;
+        for (int off = LPR / 2; off >= 1; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+        if (in_grid && sub == 0) {
+            delta[row] = valid ? s : 0.f;
+            lse2[row] = valid ? lse[(long long)bh * T + t] * LOG2E : 0.f;
+        }
     }
 }
 
@@ -831,7 +839,9 @@ int bwd_launch(deers_ctx* ctx, const deers_attn_desc* d, const void* q, const vo
     const long long prep_rows = BH * Tpad;
     {
         KernelTimerScope ts(ctx, DEERS_K_BWD_PREP);
-        attn_bwd_prep_f16_kernel<D><<<(unsigned)((prep_rows + 7) / 8), 256, 0, ctx->stream>>>(
+        const long long want = (prep_rows + 8 * (256 / D) - 1) / (8 * (256 / D));
+        const unsigned prep_grid = (unsigned)(want < 8LL * ctx->sm_count ? want : 8LL * ctx->sm_count);
+        attn_bwd_prep_f16_kernel<D><<<prep_grid, 256, 0, ctx->stream>>>(
             (const __half*)o, (const __half*)d_o, lse, delta, lse2, d->B, d->H, d->T, Tpad, d->o_strides[0],
             d->o_strides[1], d->o_strides[2], d->do_strides[0], d->do_strides[1], d->do_strides[2]);
     }
