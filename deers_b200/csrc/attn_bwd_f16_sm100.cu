@@ -72,6 +72,8 @@ struct BwdParams {
     int causal;
     float scale;
     unsigned int* err;
+    const int* sched;           // balanced schedule table[n * grid + cta] (or nullptr: strided)
+    int sched_rows;
 };
 
 __device__ __forceinline__ float ex2(float x) {
@@ -97,6 +99,14 @@ __device__ __forceinline__ void item_tile(int B, int H, int ntile, int w, int& s
     const int within = w - group * 16 * ntile;
     slot = within / gsize;
     bh = group * 16 + within % gsize;
+}
+
+// n-th work item of this CTA, or -1 when its list is exhausted.
+__device__ __forceinline__ int next_item(const BwdParams& p, int n, int n_items) {
+    int w;
+    if (p.sched) w = n < p.sched_rows ? p.sched[n * (int)gridDim.x + (int)blockIdx.x] : -1;
+    else w = (int)blockIdx.x + n * (int)gridDim.x;
+    return w < n_items ? w : -1;
 }
 
 // Stores 32 f32 TMEM columns of one row as 32 f16 values (64 bytes), scaled by s.
@@ -203,7 +213,7 @@ attn_bwd_dkdv_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         if (lane == 0) {
             uint32_t gi = 0;                                    // query-tile iterations so far (all items)
             bool ok = true;
-            for (int n = 0, w = blockIdx.x; ok && w < n_items; ++n, w += gridDim.x) {
+            for (int n = 0, w = next_item(p, 0, n_items); ok && w >= 0; ++n, w = next_item(p, n, n_items)) {
                 int kt, bh;
                 item_tile(p.B, p.H, nq, w, kt, bh);             // low KV tiles carry the most work
                 const int b = bh / p.H, h = bh % p.H;
@@ -267,7 +277,7 @@ attn_bwd_dkdv_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
             auto a_tmem = [&](uint32_t base, int ks) { return tmem + base + (uint32_t)(ks >> 2) * 64u + (uint32_t)(ks & 3) * 8u; };
             uint32_t gi = 0;
             bool ok = true;
-            for (int n = 0, w = blockIdx.x; ok && w < n_items; ++n, w += gridDim.x) {
+            for (int n = 0, w = next_item(p, 0, n_items); ok && w >= 0; ++n, w = next_item(p, n, n_items)) {
                 int kt, bh;
                 item_tile(p.B, p.H, nq, w, kt, bh);
                 const int niter = nq - (p.causal ? kt : 0);
@@ -336,7 +346,7 @@ attn_bwd_dkdv_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         const bool tr = lane == 0 && (warp == 2 || warp == 6);
 #endif
 
-        for (int n = 0, w = blockIdx.x; alive && w < n_items; ++n, w += gridDim.x) {
+        for (int n = 0, w = next_item(p, 0, n_items); alive && w >= 0; ++n, w = next_item(p, n, n_items)) {
             int kt, bh;
             item_tile(p.B, p.H, nq, w, kt, bh);
             const int b = bh / p.H, h = bh % p.H;
@@ -538,7 +548,7 @@ attn_bwd_dq_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         if (lane == 0) {
             uint32_t kvc = 0;                                   // K/V stage uses so far (all items)
             bool ok = true;
-            for (int n = 0, w = blockIdx.x; ok && w < n_items; ++n, w += gridDim.x) {
+            for (int n = 0, w = next_item(p, 0, n_items); ok && w >= 0; ++n, w = next_item(p, n, n_items)) {
                 int slot, bh;
                 item_tile(p.B, p.H, nq, w, slot, bh);
                 const int qt = nq - 1 - slot;                   // late query tiles carry the most work
@@ -593,7 +603,7 @@ attn_bwd_dq_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
             };
             uint32_t kvc = 0;                                   // K/V stage uses == KV iterations so far
             bool ok = true;
-            for (int n = 0, w = blockIdx.x; ok && w < n_items; ++n, w += gridDim.x) {
+            for (int n = 0, w = next_item(p, 0, n_items); ok && w >= 0; ++n, w = next_item(p, n, n_items)) {
                 int slot, bh;
                 item_tile(p.B, p.H, nq, w, slot, bh);
                 const int qt = nq - 1 - slot;
@@ -682,7 +692,7 @@ attn_bwd_dq_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
             return true;
         };
 
-        for (int n = 0, w = blockIdx.x; alive && w < n_items; ++n, w += gridDim.x) {
+        for (int n = 0, w = next_item(p, 0, n_items); alive && w >= 0; ++n, w = next_item(p, n, n_items)) {
             int slot, bh;
             item_tile(p.B, p.H, nq, w, slot, bh);
             const int qt = nq - 1 - slot;
@@ -858,18 +868,18 @@ int bwd_launch(deers_ctx* ctx, const deers_attn_desc* d, const void* q, const vo
     const long long grid = BH * nq;
     if (grid > 0x7fffffffLL) return DEERS_ERR_SHAPE;
 
+    const unsigned persistent = (unsigned)(grid < ctx->sm_count ? grid : ctx->sm_count);
+    p.sched = deers_get_schedule(ctx, d->B, d->H, nq, d->causal, (int)persistent, &p.sched_rows);
     const size_t smem_a = DkvSmem<D>::TOTAL, smem_b = DqSmem<D>::TOTAL;
     DEERS_CUDA_TRY(ctx, cudaFuncSetAttribute(attn_bwd_dkdv_f16_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_a));
     DEERS_CUDA_TRY(ctx, cudaFuncSetAttribute(attn_bwd_dq_f16_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_b));
     {
         KernelTimerScope ts(ctx, DEERS_K_BWD_MAIN);
-        const unsigned persistent = (unsigned)(grid < ctx->sm_count ? grid : ctx->sm_count);
         attn_bwd_dkdv_f16_kernel<D><<<persistent, 320, smem_a, ctx->stream>>>(tq, tk, tv, tdo, p);
     }
     DEERS_CUDA_TRY(ctx, cudaGetLastError());
     {
         KernelTimerScope ts(ctx, DEERS_K_BWD_DQ);
-        const unsigned persistent = (unsigned)(grid < ctx->sm_count ? grid : ctx->sm_count);
         attn_bwd_dq_f16_kernel<D><<<persistent, 320, smem_b, ctx->stream>>>(tq, tk, tv, tdo, p);
     }
     DEERS_CUDA_TRY(ctx, cudaGetLastError());

@@ -34,6 +34,17 @@ extern "C" __attribute__((visibility("default"))) int deers_b200_debug_fwd_trace
 #define FWD_TRACE(role, step, ev) do {} while (0)
 #endif
 
+#if defined(DEERS_TRACE) && DEERS_TRACE == 4
+// Development aid: last known position of every role of every CTA, to locate a stalled wait.
+__device__ int g_fwd_state[160 * 16 * 4];
+#define FWD_STATE(slot, a, b, c) do { int* s_ = g_fwd_state + ((int)blockIdx.x * 16 + (slot)) * 4; s_[0] = (a); s_[1] = (b); s_[2] = (c); s_[3] = 1; } while (0)
+extern "C" __attribute__((visibility("default"))) int deers_b200_debug_fwd_state(int* out) {
+    return (int)cudaMemcpyFromSymbol(out, g_fwd_state, sizeof(g_fwd_state));
+}
+#else
+#define FWD_STATE(slot, a, b, c) do {} while (0)
+#endif
+
 namespace {
 using namespace sm100;
 
@@ -52,6 +63,8 @@ struct FwdParams {
     int causal;
     float scale;
     unsigned int* err;
+    const int* sched;           // balanced schedule table[n * grid + cta] (or nullptr: strided)
+    int sched_rows;
 };
 
 __device__ __forceinline__ float ex2(float x) {
@@ -73,8 +86,11 @@ struct FwdSmem {
     static constexpr uint32_t TOTAL = BARS + 256;
 };
 
+// P_FULL is split by step parity: S runs two steps ahead of P V, so the softmax threads can hand over
+// P of steps g and g+1 before the MMA thread has looked at step g; one barrier per parity keeps each
+// barrier at most one phase ahead of its waiter.
 enum FwdBar { F_Q_FULL = 0, F_Q_EMPTY = 2, F_K_FULL = 4, F_K_EMPTY = 6, F_V_FULL = 8, F_V_EMPTY = 10, F_S_FULL = 12,
-              F_P_FULL = 14, F_PV_DONE = 15, F_XCH = 16, F_LX = 17, F_O_DONE = 18, F_O_FREE = 20, F_COUNT = 22 };
+              F_P_FULL = 14, F_PV_DONE = 16, F_XCH = 17, F_LX = 18, F_O_DONE = 19, F_O_FREE = 21, F_COUNT = 23 };
 
 // Work order: groups of 16 slices; inside a group the heaviest (latest) query tiles of all its
 // slices come first (balance) and the group's K and V (a few MB) stay in L2.
@@ -92,15 +108,21 @@ struct WorkCursor {
         bh = group * 16 + within % gsize;
         ntiles = p.causal ? qt + 1 : nq;
     }
-    __device__ __forceinline__ void init(const FwdParams& p, int nq, int n_items) {
-        n = 0; w = blockIdx.x; j = 0;
-        if (w < n_items) load(p, nq);
+    __device__ __forceinline__ void fetch(const FwdParams& p, int nq, int n_items) {
+        if (p.sched) w = n < p.sched_rows ? p.sched[n * (int)gridDim.x + (int)blockIdx.x] : -1;
+        else w = (int)blockIdx.x + n * (int)gridDim.x;
+        if (w >= n_items) w = -1;
+        if (w >= 0) load(p, nq);
     }
-    __device__ __forceinline__ bool valid(int n_items) const { return w < n_items; }
+    __device__ __forceinline__ void init(const FwdParams& p, int nq, int n_items) {
+        n = 0; j = 0;
+        fetch(p, nq, n_items);
+    }
+    __device__ __forceinline__ bool valid(int) const { return w >= 0; }
     __device__ __forceinline__ void advance(const FwdParams& p, int nq, int n_items) {
         if (++j == ntiles) {
-            j = 0; ++n; w += gridDim.x;
-            if (w < n_items) load(p, nq);
+            j = 0; ++n;
+            fetch(p, nq, n_items);
         }
     }
 };
@@ -145,9 +167,9 @@ attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             mbar_init(&bars[F_K_FULL + s], 1); mbar_init(&bars[F_K_EMPTY + s], 1);
             mbar_init(&bars[F_V_FULL + s], 1); mbar_init(&bars[F_V_EMPTY + s], 1);
             mbar_init(&bars[F_S_FULL + s], 1);
+            mbar_init(&bars[F_P_FULL + s], 256);
             mbar_init(&bars[F_O_DONE + s], 1); mbar_init(&bars[F_O_FREE + s], 256);
         }
-        mbar_init(&bars[F_P_FULL], 256);
         mbar_init(&bars[F_PV_DONE], 1);
         mbar_init(&bars[F_XCH], 256);
         mbar_init(&bars[F_LX], 256);
@@ -175,6 +197,7 @@ attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 const int b = c.bh / p.H, h = c.bh % p.H;
                 if (c.j == 0) {
                     const int qb = c.n & 1;
+                    FWD_STATE(0, (int)g, c.n, c.j * 10 + 1);
                     if (!mbar_wait(ws, &bars[F_Q_EMPTY + qb], (((uint32_t)c.n >> 1) & 1u) ^ 1u, DEERS_KERR_FWD_F16 | 1)) break;
                     mbar_arrive_expect_tx(&bars[F_Q_FULL + qb], TILE_BYTES);
 #pragma unroll
@@ -182,11 +205,13 @@ attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                         tma_load_4d(sQ + qb * TILE_BYTES + blk * BLOCK_BYTES, &tmap_q, &bars[F_Q_FULL + qb], blk * 64, c.qt * BM, h, b);
                 }
                 const uint32_t st = g & 1u, ph = ((g >> 1) & 1u) ^ 1u;
+                FWD_STATE(0, (int)g, c.n, c.j * 10 + 2);
                 if (!mbar_wait(ws, &bars[F_K_EMPTY + st], ph, DEERS_KERR_FWD_F16 | 2)) break;
                 mbar_arrive_expect_tx(&bars[F_K_FULL + st], TILE_BYTES);
 #pragma unroll
                 for (int blk = 0; blk < DBLK; ++blk)
                     tma_load_4d(sK + st * TILE_BYTES + blk * BLOCK_BYTES, &tmap_k, &bars[F_K_FULL + st], blk * 64, c.j * BN, h, b);
+                FWD_STATE(0, (int)g, c.n, c.j * 10 + 3);
                 if (!mbar_wait(ws, &bars[F_V_EMPTY + st], ph, DEERS_KERR_FWD_F16 | 3)) break;
                 mbar_arrive_expect_tx(&bars[F_V_FULL + st], TILE_BYTES);
 #pragma unroll
@@ -212,7 +237,9 @@ attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             bool ok = true;
             auto issue_s = [&]() -> bool {
                 const int qb = sc.n & 1;
+                FWD_STATE(1, (int)gs, sc.n, sc.j * 10 + 4);
                 if (sc.j == 0 && !mbar_wait(ws, &bars[F_Q_FULL + qb], ((uint32_t)sc.n >> 1) & 1u, DEERS_KERR_FWD_F16 | 4)) return false;
+                FWD_STATE(1, (int)gs, sc.n, sc.j * 10 + 5);
                 if (!mbar_wait(ws, &bars[F_K_FULL + (gs & 1u)], (gs >> 1) & 1u, DEERS_KERR_FWD_F16 | 5)) return false;
                 tc_fence_after_sync();
                 const uint64_t q_km = q_km0 + (uint64_t)qb * STAGE_STEP, k_km = k_km0 + (uint64_t)(gs & 1u) * STAGE_STEP;
@@ -231,9 +258,12 @@ attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             while (ok && pc.valid(n_items)) {
                 const uint32_t st = gp & 1u;
                 FWD_TRACE(0, gp, 0);
-                if (!mbar_wait(ws, &bars[F_P_FULL], gp & 1u, DEERS_KERR_FWD_F16 | 6)) break;
+                FWD_STATE(1, (int)gp, pc.n, pc.j * 10 + 6);
+                if (!mbar_wait(ws, &bars[F_P_FULL + st], (gp >> 1) & 1u, DEERS_KERR_FWD_F16 | 6)) break;
                 FWD_TRACE(0, gp, 1);
+                FWD_STATE(1, (int)gp, pc.n, pc.j * 10 + 7);
                 if (!mbar_wait(ws, &bars[F_V_FULL + st], (gp >> 1) & 1u, DEERS_KERR_FWD_F16 | 7)) break;
+                FWD_STATE(1, (int)gp, pc.n, pc.j * 10 + 8);
                 // The accumulator of item n was last used by item n-2: its epilogue must be over.
                 if (pc.j == 0 && !mbar_wait(ws, &bars[F_O_FREE + (pc.n & 1)], (((uint32_t)pc.n >> 1) & 1u) ^ 1u, DEERS_KERR_FWD_F16 | 8)) break;
                 tc_fence_after_sync();
@@ -276,8 +306,10 @@ attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             float* lxp = lx + (n & 1) * 2 * BM;
             lxp[g * BM + row] = pend_l;
             mbar_arrive(&bars[F_LX]);
+            if (lane == 0) FWD_STATE(warp, -1, n, 9);
             if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[F_LX], (uint32_t)n & 1u, DEERS_KERR_FWD_F16 | 9))) return false;
             const float l = pend_l + lxp[(g ^ 1) * BM + row];
+            if (lane == 0) FWD_STATE(warp, -1, n, 10);
             if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[F_O_DONE + (n & 1)], ((uint32_t)n >> 1) & 1u, DEERS_KERR_FWD_F16 | 10))) return false;
             tc_fence_after_sync();
             const float inv = 1.f / l;
@@ -318,6 +350,7 @@ attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 const uint32_t sb = gstep & 1u;
                 const bool tr = lane == 0 && (warp == 2 || warp == 6);
                 if (tr) FWD_TRACE(1 + g, gstep, 0);
+                if (lane == 0) FWD_STATE(warp, (int)gstep, n, j * 100 + 11);
                 if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[F_S_FULL + sb], (gstep >> 1) & 1u, DEERS_KERR_FWD_F16 | 11))) { alive = false; break; }
                 tc_fence_after_sync();
                 float s[64];
@@ -362,6 +395,7 @@ attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 float* xp = xch + sb * 2 * BM;
                 xp[g * BM + row] = mx;
                 mbar_arrive(&bars[F_XCH]);
+                if (lane == 0) FWD_STATE(warp, (int)gstep, n, j * 100 + 12);
                 if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[F_XCH], gstep & 1u, DEERS_KERR_FWD_F16 | 12))) { alive = false; break; }
                 mx = fmaxf(mx, xp[(g ^ 1) * BM + row]);
                 if (tr) FWD_TRACE(1 + g, gstep, 3);
@@ -389,6 +423,7 @@ attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
 
                 if (j > 0 && warp_grow) {
                     // O += P V of the previous step must have landed before O is rescaled.
+                    if (lane == 0) FWD_STATE(warp, (int)gstep, n, j * 100 + 13);
                     if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[F_PV_DONE], (gstep - 1u) & 1u, DEERS_KERR_FWD_F16 | 13))) { alive = false; break; }
                     tc_fence_after_sync();
                     const uint32_t to = tmem + TM_O + (uint32_t)(n & 1) * D + t_lane + g * DH;
@@ -406,7 +441,8 @@ attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 tmem_st_x32(tmem + TM_S + sb * 128u + t_lane + 64 * g, pk);
                 tmem_wait_st();
                 tc_fence_before_sync();
-                mbar_arrive(&bars[F_P_FULL]);
+                mbar_arrive(&bars[F_P_FULL + sb]);
+                if (lane == 0) FWD_STATE(warp, (int)gstep, n, j * 100 + 14);
                 if (tr) FWD_TRACE(1 + g, gstep, 5);
                 if (j == 0 && !epilogue()) { alive = false; break; }          // previous item's O tile
             }
@@ -443,6 +479,7 @@ int fwd_launch(deers_ctx* ctx, const deers_attn_desc* d, const void* q, const vo
     const long long items = nq * d->B * d->H;
     if (items > 0x7fffffffLL) return DEERS_ERR_SHAPE;
     const unsigned grid = (unsigned)(items < ctx->sm_count ? items : ctx->sm_count);
+    p.sched = deers_get_schedule(ctx, d->B, d->H, (int)nq, d->causal, (int)grid, &p.sched_rows);
     {
         KernelTimerScope ts(ctx, DEERS_K_FWD);
         attn_fwd_f16_kernel<D><<<grid, 320, smem, ctx->stream>>>(tq, tk, tv, p);

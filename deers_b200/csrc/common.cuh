@@ -35,6 +35,11 @@ struct deers_ctx {
     void* encode_tiled;
     bool timing;
     deers_ktimer kt[DEERS_K_COUNT];
+    // Balanced work schedule of the persistent f16 kernels: table[n * grid + cta] = n-th work item
+    // of that CTA (or -1), built on the host for the last (B, H, T, causal, grid) seen.
+    int* sched_dev;
+    int sched_key[5];
+    int sched_rows;
     // Side streams and events of the host-tensor pipeline (created on first use).
     cudaStream_t h2d_stream, d2h_stream;
     cudaEvent_t pipe_ev[3][3];      // [buffer set][h2d done, compute done, d2h done]
@@ -75,6 +80,14 @@ enum {
     DEERS_KERR_BWD_F16 = 0x200,
     DEERS_KERR_SELFTEST = 0x300,
 };
+
+// Work schedule shared by the persistent f16 kernels (ctx.cu).  Work items are ordered in groups
+// of 16 slices, heaviest tiles first inside a group (item -> (slot, slice), slot 0 heaviest, weight
+// ntile - slot when causal).  The table hands the items, in that order, to whichever CTA is least
+// loaded so far, which balances the causal triangle for any slice count.  Returns nullptr (plain
+// strided assignment) when the table would not fit.
+constexpr int DEERS_SCHED_CAP = 1 << 20;                 // table entries
+const int* deers_get_schedule(deers_ctx* ctx, int B, int H, int ntile, int causal, int grid, int* rows);
 
 // f32 FFMA path (attn_f32.cu)
 int launch_attn_fwd_f32(deers_ctx* ctx, const deers_attn_desc* d, const float* q, const float* k,

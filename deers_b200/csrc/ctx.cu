@@ -4,6 +4,8 @@
 #include "common.cuh"
 
 #include <new>
+#include <queue>
+#include <vector>
 
 static const char* kStatus[] = {
     "ok",
@@ -77,6 +79,8 @@ extern "C" int deers_b200_init(int device_ordinal, void* stream, deers_ctx** out
         return DEERS_ERR_CUDA;
     }
     *ctx->host_err = 0;
+    if (cudaMalloc((void**)&ctx->sched_dev, sizeof(int) * DEERS_SCHED_CAP) != cudaSuccess) ctx->sched_dev = nullptr;
+    ctx->sched_key[0] = -1;
     cudaDriverEntryPointQueryResult qres;
     void* fn = nullptr;
     if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess ||
@@ -94,6 +98,7 @@ extern "C" void deers_b200_destroy(deers_ctx* ctx) {
     if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
     if (ctx->host_err) cudaFreeHost(ctx->host_err);
     if (ctx->dev_err) cudaFree(ctx->dev_err);
+    if (ctx->sched_dev) cudaFree(ctx->sched_dev);
     if (ctx->pipe_ready) {
         cudaStreamDestroy(ctx->h2d_stream);
         cudaStreamDestroy(ctx->d2h_stream);
@@ -171,6 +176,53 @@ extern "C" int deers_b200_sync(deers_ctx* ctx) {
         return DEERS_ERR_KERNEL;
     }
     return DEERS_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Work schedule of the persistent kernels
+// ---------------------------------------------------------------------------
+const int* deers_get_schedule(deers_ctx* ctx, int B, int H, int ntile, int causal, int grid, int* rows) {
+    *rows = 0;
+    const long long n_items = (long long)B * H * ntile;
+    if (!ctx->sched_dev || grid < 1 || n_items < 1) return nullptr;
+    const int key[5] = {B, H, ntile, causal, grid};
+    if (memcmp(key, ctx->sched_key, sizeof(key)) == 0) {
+        *rows = ctx->sched_rows;
+        return ctx->sched_rows > 0 ? ctx->sched_dev : nullptr;
+    }
+    memcpy(ctx->sched_key, key, sizeof(key));
+    ctx->sched_rows = 0;
+    // Greedy list scheduling in item order: each item goes to the CTA with the least work so far.
+    std::vector<std::vector<int>> lists(grid);
+    typedef std::pair<long long, int> Load;                            // (work so far, cta)
+    std::priority_queue<Load, std::vector<Load>, std::greater<Load>> heap;
+    for (int c = 0; c < grid; ++c) heap.push(Load(0, c));
+    const int BH = B * H;
+    for (long long w = 0; w < n_items; ++w) {
+        const int group = (int)(w / (16LL * ntile));
+        const int gsize = BH - group * 16 < 16 ? BH - group * 16 : 16;
+        const int slot = (int)((w - (long long)group * 16 * ntile) / gsize);
+        const long long weight = (causal ? ntile - slot : ntile) + 1;  // +1: per-item start-up and epilogue
+        Load l = heap.top();
+        heap.pop();
+        lists[l.second].push_back((int)w);
+        heap.push(Load(l.first + weight, l.second));
+    }
+    size_t nrows = 0;
+    for (auto& v : lists) nrows = v.size() > nrows ? v.size() : nrows;
+    if (nrows * (size_t)grid > (size_t)DEERS_SCHED_CAP) return nullptr;
+    std::vector<int> table(nrows * grid, -1);
+    for (int c = 0; c < grid; ++c)
+        for (size_t n = 0; n < lists[c].size(); ++n) table[n * grid + c] = lists[c][n];
+    if (cudaMemcpyAsync(ctx->sched_dev, table.data(), table.size() * sizeof(int), cudaMemcpyHostToDevice, ctx->stream) !=
+            cudaSuccess ||
+        cudaStreamSynchronize(ctx->stream) != cudaSuccess) {           // the host vector goes away on return
+        ctx->sched_key[0] = -1;
+        return nullptr;
+    }
+    ctx->sched_rows = (int)nrows;
+    *rows = ctx->sched_rows;
+    return ctx->sched_dev;
 }
 
 // ---------------------------------------------------------------------------

@@ -16,7 +16,9 @@
  *    that the caller can compact() and retry.  Outputs are written with the
  *    strides given in the descriptor.
  *  - Work is enqueued on the context's stream and the call returns at once; no
- *    allocation and no synchronisation happens inside attn_fwd / attn_bwd.
+ *    allocation happens inside attn_fwd / attn_bwd, and no synchronisation except
+ *    once per new (B, H, T, causal) on the f16 path, when a small work-schedule
+ *    table is rebuilt on the host and uploaded.
  *  - Nothing aborts or traps.  Every function returns a status (0 = OK) and
  *    device-side waits are bounded: a kernel that gives up records a code that
  *    deers_b200_sync() reports as DEERS_ERR_KERNEL.
