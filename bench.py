@@ -215,8 +215,12 @@ def main():
         raise SystemExit("bench.py needs a B200: there is no CPU fallback for the attention path")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    # Libraries (NCCL's version banner) may write to stdout: point fd 1 at stderr for the run and keep
+    # the real stdout for the one JSON line.
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
     if world > 1:
-        os.environ["NCCL_DEBUG"] = "WARN"      # keep NCCL's version banner off stdout: one JSON line only
         dist.init_process_group("nccl", device_id=dev)
 
     tdtype = torch.float16 if dtype == "f16" else torch.float32
@@ -340,13 +344,19 @@ def main():
         peaks = load_peaks()
         bwd_ms, bwd_n = ktimes["bwd_main"]
         bwd_avg = bwd_ms / max(bwd_n, 1)
-        bwd_flops = 5.0 * n_local * T * T * D               # the 5 GEMMs of the backward, causal-counted
+        # The dominant kernel is the dK/dV kernel: 4 causal products (S^T, dP^T, dV, dK) of n*T^2*D FLOPs each.
+        dkdv_flops = 4.0 * n_local * T * T * D
         peak = peaks["tflops_sustained"] if dtype == "f16" else None
         roofline = None
         if dtype == "f16":
-            achieved = bwd_flops / (bwd_avg * 1e-3) / 1e12
-            roofline = {"bound": "tensor", "kernel": "attn_bwd_f16_kernel", "achieved": achieved, "peak": peak,
-                        "unit": UNIT, "frac": achieved / peak, "traffic": None,
+            achieved = dkdv_flops / (bwd_avg * 1e-3) / 1e12
+            # DRAM traffic of this kernel from the ncu capture summarised in
+            # profiles/attn_f16_kernels_B8_T2048_H16_D128.md (374.8 MB for 128 slices of T=2048, D=128),
+            # scaled by the slices one launch processes; traffic is proportional to the slice count.
+            traffic = 374.8e6 / 128 * n_local if (T == 2048 and D == 128) else None
+            roofline = {"bound": "tensor", "kernel": "attn_bwd_dkdv_f16_kernel", "achieved": achieved, "peak": peak,
+                        "unit": UNIT, "frac": achieved / peak, "traffic": traffic,
+                        "flops_per_launch": dkdv_flops,
                         "peak_source": f"{peaks['source']} sustained bf16 (kernel timed inside a long step)",
                         "avg_launch_ms": bwd_avg}
         else:
@@ -359,8 +369,11 @@ def main():
                         "peak_source": f"{peaks['source']} copy bandwidth"}
         fwd_ms, fwd_n = ktimes["fwd"]
         kernels = {name: {"launches": n_, "avg_ms": (ms_ / n_ if n_ else None)} for name, (ms_, n_) in ktimes.items()}
-        if dtype == "f16" and fwd_n:
-            kernels["fwd"]["tflops"] = 2.0 * n_local * T * T * D / (fwd_ms / fwd_n * 1e-3) / 1e12
+        if dtype == "f16":
+            for name, nprod in (("fwd", 2.0), ("bwd_main", 4.0), ("bwd_dq", 3.0)):     # causal products per kernel
+                ms_, n_ = ktimes[name]
+                if n_:
+                    kernels[name]["tflops_executed"] = nprod * n_local * T * T * D / (ms_ / n_ * 1e-3) / 1e12
         cb = None
         if not args.no_cpu_baseline:
             from oracle import ref
@@ -382,7 +395,8 @@ def main():
                            "peak_tflops": peaks["tflops_sustained"], "peak_source": peaks["source"]},
                 "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "roofline": roofline,
                 "kernels": kernels, "cpu_baseline": cb}
-        print(json.dumps(line), flush=True)
+        sys.stdout.flush()
+        os.write(real_stdout, (json.dumps(line) + "\n").encode())
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
