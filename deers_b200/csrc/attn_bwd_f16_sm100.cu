@@ -438,9 +438,10 @@ attn_bwd_dkdv_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
             // computes S^T and dP^T of the next item.
             if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[A_DONE], (uint32_t)n & 1u, DEERS_KERR_BWD_F16 | 16))) { alive = false; break; }
             tc_fence_after_sync();
-            const int krow = k0 + r;
-            __half* dkrow = p.dk + b * p.sdk_b + h * p.sdk_h + (long long)krow * p.sdk_t + g * DH;
-            __half* dvrow = p.dv + b * p.sdv_b + h * p.sdv_h + (long long)krow * p.sdv_t + g * DH;
+            // The thread's half rows of dK and dV, as 16-byte pieces, are transposed within lane
+            // groups so that every store instruction writes whole contiguous row segments.
+            constexpr int NP = DH / 8;
+            uint4 kc[NP], vc[NP];
 #pragma unroll
             for (int c = 0; c < DH / 32; ++c) {
                 uint32_t kr[32], vr[32];
@@ -451,9 +452,24 @@ attn_bwd_dkdv_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
                     tc_fence_before_sync();
                     mbar_arrive(&bars[A_ACC_FREE]);
                 }
-                if (krow < p.T) {
-                    store_row32(dkrow + c * 32, kr, p.scale);
-                    store_row32(dvrow + c * 32, vr, 1.0f);
+#pragma unroll
+                for (int q8 = 0; q8 < 4; ++q8) {
+                    kc[c * 4 + q8] = pack8_f16(kr + q8 * 8, p.scale);
+                    vc[c * 4 + q8] = pack8_f16(vr + q8 * 8, 1.0f);
+                }
+            }
+            transpose_pieces<NP>(kc, (uint32_t)lane);
+            transpose_pieces<NP>(vc, (uint32_t)lane);
+            const int row0 = k0 + lane_base + (lane & ~(NP - 1));
+            const int col = g * DH + (lane & (NP - 1)) * 8;
+            __half* dkb = p.dk + b * p.sdk_b + h * p.sdk_h + col;
+            __half* dvb = p.dv + b * p.sdv_b + h * p.sdv_h + col;
+#pragma unroll
+            for (int c = 0; c < NP; ++c) {
+                const int row = row0 + c;
+                if (row < p.T) {
+                    *reinterpret_cast<uint4*>(dkb + (long long)row * p.sdk_t) = kc[c];
+                    *reinterpret_cast<uint4*>(dvb + (long long)row * p.sdv_t) = vc[c];
                 }
             }
         }

@@ -257,4 +257,39 @@ __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&h);
 }
 
+// Packs 8 f32 values (scaled by s) into eight f16 values: one 16-byte piece of an output row.
+__device__ __forceinline__ uint4 pack8_f16(const uint32_t* r, float s) {
+    uint4 a;
+    a.x = pack_half2(__uint_as_float(r[0]) * s, __uint_as_float(r[1]) * s);
+    a.y = pack_half2(__uint_as_float(r[2]) * s, __uint_as_float(r[3]) * s);
+    a.z = pack_half2(__uint_as_float(r[4]) * s, __uint_as_float(r[5]) * s);
+    a.w = pack_half2(__uint_as_float(r[6]) * s, __uint_as_float(r[7]) * s);
+    return a;
+}
+
+// N x N transpose (N = 4 or 8) of 16-byte pieces among the N lanes of each aligned lane group:
+// on return v[c] of the group's lane j holds what v[j] of the group's lane c held.  A thread that
+// owns one row of a tile (the TMEM lane layout) enters with pieces 0..N-1 of its row and leaves
+// with piece j of rows 0..N-1 of its group, so that the group's N lanes together store N*16
+// contiguous bytes of one row per instruction instead of 16 bytes in each of N rows.
+template <int N>
+__device__ __forceinline__ void transpose_pieces(uint4 (&v)[N], uint32_t lane) {
+#pragma unroll
+    for (int s = 1; s < N; s <<= 1) {
+        const bool upper = (lane & (uint32_t)s) != 0;
+#pragma unroll
+        for (int c = 0; c < N; ++c) {
+            if (c & s) continue;
+            // lanes l (bit s clear) and l|s exchange element (l, c|s) with element (l|s, c)
+            const uint4 send = upper ? v[c] : v[c | s];
+            uint4 recv;
+            recv.x = __shfl_xor_sync(0xffffffffu, send.x, s);
+            recv.y = __shfl_xor_sync(0xffffffffu, send.y, s);
+            recv.z = __shfl_xor_sync(0xffffffffu, send.z, s);
+            recv.w = __shfl_xor_sync(0xffffffffu, send.w, s);
+            if (upper) v[c] = recv; else v[c | s] = recv;
+        }
+    }
+}
+
 }  // namespace sm100
