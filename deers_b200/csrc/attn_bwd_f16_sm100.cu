@@ -109,19 +109,6 @@ __device__ __forceinline__ int next_item(const BwdParams& p, int n, int n_items)
     return w < n_items ? w : -1;
 }
 
-// Stores 32 f32 TMEM columns of one row as 32 f16 values (64 bytes), scaled by s.
-__device__ __forceinline__ void store_row32(__half* dst, const uint32_t (&r)[32], float s) {
-#pragma unroll
-    for (int q8 = 0; q8 < 4; ++q8) {
-        uint4 a;
-        a.x = pack_half2(__uint_as_float(r[q8 * 8 + 0]) * s, __uint_as_float(r[q8 * 8 + 1]) * s);
-        a.y = pack_half2(__uint_as_float(r[q8 * 8 + 2]) * s, __uint_as_float(r[q8 * 8 + 3]) * s);
-        a.z = pack_half2(__uint_as_float(r[q8 * 8 + 4]) * s, __uint_as_float(r[q8 * 8 + 5]) * s);
-        a.w = pack_half2(__uint_as_float(r[q8 * 8 + 6]) * s, __uint_as_float(r[q8 * 8 + 7]) * s);
-        *reinterpret_cast<uint4*>(dst + q8 * 8) = a;
-    }
-}
-
 // ---------------------------------------------------------------------------------------------
 // dK / dV kernel (persistent: each CTA walks a strided list of KV tiles)
 // ---------------------------------------------------------------------------------------------
@@ -696,15 +683,27 @@ attn_bwd_dq_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
             pend_n = -1;
             if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[Q_DONE + (n & 1)], ((uint32_t)n >> 1) & 1u, DEERS_KERR_BWD_F16 | 0x19))) return false;
             tc_fence_after_sync();
+            constexpr int NP = DH / 8;
+            uint4 qc[NP];
 #pragma unroll
             for (int c = 0; c < DH / 32; ++c) {
                 uint32_t qr[32];
                 tmem_ld_x32(tmem + TM_DQ + (uint32_t)(n & 1) * D + t_lane + g * DH + c * 32, qr);
                 tmem_wait_ld();
-                if (pend_row < p.T) store_row32(pend_ptr + c * 32, qr, p.scale);
+#pragma unroll
+                for (int q8 = 0; q8 < 4; ++q8) qc[c * 4 + q8] = pack8_f16(qr + q8 * 8, p.scale);
             }
             tc_fence_before_sync();
             mbar_arrive(&bars[Q_DQ_FREE + (n & 1)]);
+            // Pieces transposed within lane groups: every store writes contiguous row segments.
+            transpose_pieces<NP>(qc, (uint32_t)lane);
+            const int row0 = pend_row - lane + (lane & ~(NP - 1));
+            __half* qb = pend_ptr + (lane & (NP - 1)) * 8;     // row 0 of the slice, this lane's piece
+#pragma unroll
+            for (int c = 0; c < NP; ++c) {
+                const int row = row0 + c;
+                if (row < p.T) *reinterpret_cast<uint4*>(qb + (long long)row * p.sdq_t) = qc[c];
+            }
             return true;
         };
 
@@ -785,7 +784,7 @@ attn_bwd_dq_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
 
             pend_n = n;
             pend_row = q0 + r;
-            pend_ptr = p.dq + b * p.sdq_b + h * p.sdq_h + (long long)(q0 + r) * p.sdq_t + g * DH;
+            pend_ptr = p.dq + b * p.sdq_b + h * p.sdq_h + g * DH;     // row 0 of the slice
         }
         if (alive) epilogue();
     }

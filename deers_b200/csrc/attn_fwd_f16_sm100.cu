@@ -314,7 +314,10 @@ attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             tc_fence_after_sync();
             const float inv = 1.f / l;
             const int b = pend_bh / p.H, h = pend_bh % p.H;
-            __half* orow = p.o + b * p.so_b + h * p.so_h + (long long)pend_grow * p.so_t + g * DH;
+            // The thread's half row of O, as 16-byte pieces, is transposed within lane groups so
+            // that every store instruction writes whole contiguous row segments.
+            constexpr int NP = DH / 8;
+            uint4 oc[NP];
 #pragma unroll
             for (int c = 0; c < DH / 32; ++c) {
                 uint32_t r[32];
@@ -324,17 +327,16 @@ attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                     tc_fence_before_sync();
                     mbar_arrive(&bars[F_O_FREE + (n & 1)]);
                 }
-                if (pend_grow < p.T) {
 #pragma unroll
-                    for (int q8 = 0; q8 < 4; ++q8) {
-                        uint4 v;
-                        v.x = pack_half2(__uint_as_float(r[q8 * 8 + 0]) * inv, __uint_as_float(r[q8 * 8 + 1]) * inv);
-                        v.y = pack_half2(__uint_as_float(r[q8 * 8 + 2]) * inv, __uint_as_float(r[q8 * 8 + 3]) * inv);
-                        v.z = pack_half2(__uint_as_float(r[q8 * 8 + 4]) * inv, __uint_as_float(r[q8 * 8 + 5]) * inv);
-                        v.w = pack_half2(__uint_as_float(r[q8 * 8 + 6]) * inv, __uint_as_float(r[q8 * 8 + 7]) * inv);
-                        *reinterpret_cast<uint4*>(orow + c * 32 + q8 * 8) = v;
-                    }
-                }
+                for (int q8 = 0; q8 < 4; ++q8) oc[c * 4 + q8] = pack8_f16(r + q8 * 8, inv);
+            }
+            transpose_pieces<NP>(oc, (uint32_t)lane);
+            const int grow0 = pend_grow - lane + (lane & ~(NP - 1));
+            __half* ob = p.o + b * p.so_b + h * p.so_h + g * DH + (lane & (NP - 1)) * 8;
+#pragma unroll
+            for (int c = 0; c < NP; ++c) {
+                const int grow = grow0 + c;
+                if (grow < p.T) *reinterpret_cast<uint4*>(ob + (long long)grow * p.so_t) = oc[c];
             }
             if (g == 0 && pend_grow < p.T) p.lse[(long long)pend_bh * p.T + pend_grow] = (pend_m + log2f(l)) * LN2;
             return true;
