@@ -482,8 +482,9 @@ struct DqSmem {
     static constexpr uint32_t TOTAL = BARS + 256;
 };
 
+// Q_DP and Q_DS are pairs indexed by the parity of the KV step: dP runs one step ahead of its reader.
 enum DqBar { Q_QDO_FULL = 0, Q_QDO_EMPTY = 1, Q_K_FULL = 2, Q_K_EMPTY = 5, Q_V_FULL = 8, Q_V_EMPTY = 10, Q_S = 12, Q_DP = 13,
-             Q_PDONE = 14, Q_DS = 15, Q_DONE = 16, Q_DQ_FREE = 18, Q_COUNT = 20 };
+             Q_PDONE = 15, Q_DS = 16, Q_DONE = 18, Q_DQ_FREE = 19, Q_COUNT = 20 };
 
 template <int D>
 __global__ void __launch_bounds__(320, 1)
@@ -495,8 +496,8 @@ attn_bwd_dq_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     constexpr int DBLK = D / 64;
     constexpr int DH = D / 2;
     constexpr uint32_t TMEM_COLS = 512;
-    // S | dP (later dS in place) | dQ of even items | dQ of odd items
-    constexpr uint32_t TM_S = 0, TM_DP = 128, TM_DQ = 256;
+    // S | dP of even KV steps (later dS in place) | dP of odd KV steps | dQ
+    constexpr uint32_t TM_S = 0, TM_DP = 128, TM_DQ = 384;
 
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* sQ = smem + L::Q;
@@ -525,12 +526,12 @@ attn_bwd_dq_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         for (int s = 0; s < 3; ++s) { mbar_init(&bars[Q_K_FULL + s], 1); mbar_init(&bars[Q_K_EMPTY + s], 1); }
         for (int s = 0; s < 2; ++s) {
             mbar_init(&bars[Q_V_FULL + s], 1); mbar_init(&bars[Q_V_EMPTY + s], 1);
-            mbar_init(&bars[Q_DONE + s], 1); mbar_init(&bars[Q_DQ_FREE + s], 256);
+            mbar_init(&bars[Q_DP + s], 1); mbar_init(&bars[Q_DS + s], 256);
         }
         mbar_init(&bars[Q_S], 1);
-        mbar_init(&bars[Q_DP], 1);
         mbar_init(&bars[Q_PDONE], 256);
-        mbar_init(&bars[Q_DS], 256);
+        mbar_init(&bars[Q_DONE], 1);
+        mbar_init(&bars[Q_DQ_FREE], 256);
         fence_barrier_init();
         tma_prefetch_desc(&tmap_q); tma_prefetch_desc(&tmap_k); tma_prefetch_desc(&tmap_v); tma_prefetch_desc(&tmap_do);
     }
@@ -596,12 +597,14 @@ attn_bwd_dq_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
                     umma_ss(tmem + TM_S, q_km + kmajor_step(ks, BLOCK_BYTES), k_km + kmajor_step(ks, BLOCK_BYTES), IDESC_S, ks > 0);
                 umma_commit(&bars[Q_S]);
             };
+            // The V stage and the dP buffer both alternate with the parity of the KV step.
             auto issue_dp = [&](uint32_t st) {
                 const uint64_t v_km = v_km0 + (uint64_t)st * STAGE_STEP;
+                const uint32_t tm_dp = tmem + TM_DP + st * 128u;
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks)
-                    umma_ss(tmem + TM_DP, do_km + kmajor_step(ks, BLOCK_BYTES), v_km + kmajor_step(ks, BLOCK_BYTES), IDESC_S, ks > 0);
-                umma_commit(&bars[Q_DP]);
+                    umma_ss(tm_dp, do_km + kmajor_step(ks, BLOCK_BYTES), v_km + kmajor_step(ks, BLOCK_BYTES), IDESC_S, ks > 0);
+                umma_commit(&bars[Q_DP + st]);
                 umma_commit(&bars[Q_V_EMPTY + st]);                    // dP is the only reader of a V tile
             };
             uint32_t kvc = 0;                                   // K/V stage uses == KV iterations so far
@@ -611,7 +614,7 @@ attn_bwd_dq_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
                 item_tile(p.B, p.H, nq, w, slot, bh);
                 const int qt = nq - 1 - slot;
                 const int ntiles = p.causal ? qt + 1 : nq;
-                const uint32_t tm_dq = tmem + TM_DQ + (uint32_t)(n & 1) * D;
+                const uint32_t tm_dq = tmem + TM_DQ;
                 if (!mbar_wait(ws, &bars[Q_QDO_FULL], (uint32_t)n & 1u, DEERS_KERR_BWD_F16 | 0x12)) break;
                 if (!mbar_wait(ws, &bars[Q_K_FULL + kvc % 3u], (kvc / 3u) & 1u, DEERS_KERR_BWD_F16 | 0x13)) break;
                 if (!mbar_wait(ws, &bars[Q_V_FULL + (kvc & 1u)], (kvc >> 1) & 1u, DEERS_KERR_BWD_F16 | 0x1c)) break;
@@ -625,7 +628,9 @@ attn_bwd_dq_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
                     const uint32_t ks = kvc % 3u, ksn = (kvc + 1u) % 3u, vsn = (kvc + 1u) & 1u;
                     const uint32_t par = kvc & 1u;
                     const bool more = j + 1 < ntiles;
-                    // S of the next KV tile as soon as the compute threads have read this one.
+                    // S and dP of the next KV tile as soon as the compute threads have read this S:
+                    // dP lands in the buffer whose dS the product issued one step ago has consumed
+                    // (the pipe is in order), so the tensor core never waits for this step's dS.
                     TRACE_B(0, 0);
                     if (!mbar_wait(ws, &bars[Q_PDONE], par, DEERS_KERR_BWD_F16 | 0x14)) { ok = false; break; }
                     TRACE_B(0, 1);
@@ -633,29 +638,29 @@ attn_bwd_dq_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
                         if (!mbar_wait(ws, &bars[Q_K_FULL + ksn], ((kvc + 1u) / 3u) & 1u, DEERS_KERR_BWD_F16 | 0x15)) { ok = false; break; }
                         tc_fence_after_sync();
                         issue_s(ksn);
-                    } else {
-                        umma_commit(&bars[Q_QDO_EMPTY]);               // every product reading Q / dO has been issued
-                    }
-                    // dQ += dS K, then dP of the next KV tile over the consumed dS columns.
-                    TRACE_B(0, 2);
-                    if (!mbar_wait(ws, &bars[Q_DS], par, DEERS_KERR_BWD_F16 | 0x16)) { ok = false; break; }
-                    if (j == 0 && !mbar_wait(ws, &bars[Q_DQ_FREE + (n & 1)], (((uint32_t)n >> 1) & 1u) ^ 1u, DEERS_KERR_BWD_F16 | 0x1a)) { ok = false; break; }
-                    tc_fence_after_sync();
-                    TRACE_B(0, 3);
-                    const uint64_t k_mn = k_mn0 + (uint64_t)ks * STAGE_STEP;
-#pragma unroll
-                    for (int ks = 0; ks < BT / 16; ++ks)
-                        umma_ts(tm_dq, tmem + TM_DP + (uint32_t)(ks >> 2) * 64u + (uint32_t)(ks & 3) * 8u,
-                                k_mn + mnmajor_step(ks), IDESC_DQ, (j > 0 || ks > 0));
-                    umma_commit(&bars[Q_K_EMPTY + ks]);                // S and dQ have both read this K tile
-                    if (more) {
                         if (!mbar_wait(ws, &bars[Q_V_FULL + vsn], ((kvc + 1u) >> 1) & 1u, DEERS_KERR_BWD_F16 | 0x1d)) { ok = false; break; }
                         tc_fence_after_sync();
                         issue_dp(vsn);
+                    } else {
+                        umma_commit(&bars[Q_QDO_EMPTY]);               // every product reading Q / dO has been issued
                     }
+                    // dQ += dS K
+                    TRACE_B(0, 2);
+                    if (!mbar_wait(ws, &bars[Q_DS + par], (kvc >> 1) & 1u, DEERS_KERR_BWD_F16 | 0x16)) { ok = false; break; }
+                    // The previous item's dQ must have left TMEM before this item accumulates.
+                    if (j == 0 && n > 0 && !mbar_wait(ws, &bars[Q_DQ_FREE], ((uint32_t)n - 1u) & 1u, DEERS_KERR_BWD_F16 | 0x1a)) { ok = false; break; }
+                    tc_fence_after_sync();
+                    TRACE_B(0, 3);
+                    const uint64_t k_mn = k_mn0 + (uint64_t)ks * STAGE_STEP;
+                    const uint32_t tm_ds = tmem + TM_DP + par * 128u;
+#pragma unroll
+                    for (int ks = 0; ks < BT / 16; ++ks)
+                        umma_ts(tm_dq, tm_ds + (uint32_t)(ks >> 2) * 64u + (uint32_t)(ks & 3) * 8u,
+                                k_mn + mnmajor_step(ks), IDESC_DQ, (j > 0 || ks > 0));
+                    umma_commit(&bars[Q_K_EMPTY + ks]);                // S and dQ have both read this K tile
                     TRACE_B(0, 4);
                 }
-                umma_commit(&bars[Q_DONE + (n & 1)]);
+                umma_commit(&bars[Q_DONE]);
             }
         }
     } else {
@@ -673,28 +678,28 @@ attn_bwd_dq_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         const bool tr = lane == 0 && (warp == 2 || warp == 6);
 #endif
         // The epilogue of item n (scale, convert, store its dQ tile, release the accumulator) is
-        // deferred until the first dS of item n+1 has been handed to the tensor core, which then
-        // never waits for it: dQ accumulators alternate between two TMEM regions.
+        // deferred until the first dS of item n+1 has been handed over: the tensor core then still
+        // has S and dP of the second KV tile to compute before it needs the accumulator.
         int pend_n = -1, pend_row = 0;
         __half* pend_ptr = nullptr;
         auto epilogue = [&]() -> bool {
             if (pend_n < 0) return true;
             const int n = pend_n;
             pend_n = -1;
-            if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[Q_DONE + (n & 1)], ((uint32_t)n >> 1) & 1u, DEERS_KERR_BWD_F16 | 0x19))) return false;
+            if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[Q_DONE], (uint32_t)n & 1u, DEERS_KERR_BWD_F16 | 0x19))) return false;
             tc_fence_after_sync();
             constexpr int NP = DH / 8;
             uint4 qc[NP];
 #pragma unroll
             for (int c = 0; c < DH / 32; ++c) {
                 uint32_t qr[32];
-                tmem_ld_x32(tmem + TM_DQ + (uint32_t)(n & 1) * D + t_lane + g * DH + c * 32, qr);
+                tmem_ld_x32(tmem + TM_DQ + t_lane + g * DH + c * 32, qr);
                 tmem_wait_ld();
 #pragma unroll
                 for (int q8 = 0; q8 < 4; ++q8) qc[c * 4 + q8] = pack8_f16(qr + q8 * 8, p.scale);
             }
             tc_fence_before_sync();
-            mbar_arrive(&bars[Q_DQ_FREE + (n & 1)]);
+            mbar_arrive(&bars[Q_DQ_FREE]);
             // Pieces transposed within lane groups: every store writes contiguous row segments.
             transpose_pieces<NP>(qc, (uint32_t)lane);
             const int row0 = pend_row - lane + (lane & ~(NP - 1));
@@ -731,30 +736,30 @@ attn_bwd_dq_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
                 const int k0 = j * BT;
                 const bool edge = (p.causal && j == qt) || (k0 + BT > p.T);
                 float pv[64];                               // P row, this warpgroup's 64 key columns
-#pragma unroll
-                for (int c = 0; c < 2; ++c) {
-                    uint32_t sr[32];
-                    tmem_ld_x32(tmem + TM_S + t_lane + 64 * g + c * 32, sr);
+                {
+                    uint32_t sr[64];
+                    tmem_ld_x32(tmem + TM_S + t_lane + 64 * g, *reinterpret_cast<uint32_t(*)[32]>(&sr[0]));
+                    tmem_ld_x32(tmem + TM_S + t_lane + 64 * g + 32, *reinterpret_cast<uint32_t(*)[32]>(&sr[32]));
                     tmem_wait_ld();
+                    tc_fence_before_sync();
+                    mbar_arrive(&bars[Q_PDONE]);            // S is in registers: the next S may land
                     if (edge) {
 #pragma unroll
-                        for (int e = 0; e < 32; ++e) {
-                            const int col = 64 * g + c * 32 + e;              // key index inside the tile
+                        for (int e = 0; e < 64; ++e) {
+                            const int col = 64 * g + e;                       // key index inside the tile
                             const bool masked = (p.causal && j == qt && col > r) || (k0 + col >= p.T);
-                            pv[c * 32 + e] = masked ? 0.f : ex2(fmaf(__uint_as_float(sr[e]), sl2, -lse2_r));
+                            pv[e] = masked ? 0.f : ex2(fmaf(__uint_as_float(sr[e]), sl2, -lse2_r));
                         }
                     } else {
 #pragma unroll
-                        for (int e = 0; e < 32; ++e) pv[c * 32 + e] = ex2(fmaf(__uint_as_float(sr[e]), sl2, -lse2_r));
+                        for (int e = 0; e < 64; ++e) pv[e] = ex2(fmaf(__uint_as_float(sr[e]), sl2, -lse2_r));
                     }
                 }
-                tc_fence_before_sync();
-                mbar_arrive(&bars[Q_PDONE]);                // S has been read: the next S may land
 #if defined(DEERS_TRACE) && DEERS_TRACE == 2
                 if (tr) TRACE_B(1 + g, 2);
 #endif
 
-                if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[Q_DP], par, DEERS_KERR_BWD_F16 | 0x18))) { alive = false; break; }
+                if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[Q_DP + par], (gi >> 1) & 1u, DEERS_KERR_BWD_F16 | 0x18))) { alive = false; break; }
                 tc_fence_after_sync();
 #if defined(DEERS_TRACE) && DEERS_TRACE == 2
                 if (tr) TRACE_B(1 + g, 3);
@@ -763,7 +768,7 @@ attn_bwd_dq_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
 #pragma unroll
                 for (int c = 0; c < 2; ++c) {
                     uint32_t dr[32];
-                    tmem_ld_x32(tmem + TM_DP + t_lane + 64 * g + c * 32, dr);
+                    tmem_ld_x32(tmem + TM_DP + par * 128u + t_lane + 64 * g + c * 32, dr);
                     tmem_wait_ld();
 #pragma unroll
                     for (int e = 0; e < 16; ++e)
@@ -771,10 +776,10 @@ attn_bwd_dq_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
                                                     pv[c * 32 + e * 2 + 1] * (__uint_as_float(dr[e * 2 + 1]) - delta_r));
                 }
                 // dS replaces this warpgroup's half of dP in TMEM (32 packed columns).
-                tmem_st_x32(tmem + TM_DP + t_lane + 64 * g, dd);
+                tmem_st_x32(tmem + TM_DP + par * 128u + t_lane + 64 * g, dd);
                 tmem_wait_st();
                 tc_fence_before_sync();
-                mbar_arrive(&bars[Q_DS]);
+                mbar_arrive(&bars[Q_DS + par]);
 #if defined(DEERS_TRACE) && DEERS_TRACE == 2
                 if (tr) TRACE_B(1 + g, 4);
 #endif
