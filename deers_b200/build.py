@@ -46,6 +46,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
             trace = os.environ.get("DEERS_TRACE")      # development aid: per-iteration clock stamps
             cmd = [_nvcc()] + [f for f in NVCC_FLAGS if not f.startswith("--use_fast_math")] + \
                   ([f"-DDEERS_TRACE={trace}"] if trace else []) + \
+                  os.environ.get("DEERS_NVCC_EXTRA", "").split() + \
                   (["-Xptxas", "-v"] if verbose else []) + ["-c", s, "-o", o]
             procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
     failed = False

@@ -34,10 +34,10 @@
 
 #ifdef DEERS_TRACE
 // Development aid: clock64() stamps of CTA 0's first iterations, read back by a debug entry point.
-__device__ unsigned long long g_bwd_trace[16 * 3 * 8];
+__device__ unsigned long long g_bwd_trace[48 * 3 * 8];
 #define BWD_TRACE(role, ev)                                                                              \
     do {                                                                                                 \
-        if (blockIdx.x == gridDim.x - 1 && it < 16) g_bwd_trace[(it * 3 + (role)) * 8 + (ev)] = clock64();           \
+        if (blockIdx.x == gridDim.x - 1 && it < 48) g_bwd_trace[(it * 3 + (role)) * 8 + (ev)] = clock64();           \
     } while (0)
 extern "C" __attribute__((visibility("default"))) int deers_b200_debug_bwd_trace(unsigned long long* out) {
     return (int)cudaMemcpyFromSymbol(out, g_bwd_trace, sizeof(g_bwd_trace));

@@ -5,9 +5,13 @@
 // each) at or left of its diagonal.  The whole list is treated as ONE stream of (item, KV tile)
 // steps, so loads and the S product run two steps ahead across item boundaries.
 //   warp 0      TMA producer: Q per item (2 buffers), K and V tiles through 2-stage rings
-//   warp 1      issues tcgen05.mma: S = Q K^T into a double-buffered TMEM tile, then
-//               O += P V with P read from TMEM and the accumulator resident in TMEM
-//               (two O accumulators alternate between items)
+//   warp 10     issues the S = Q K^T products into a double-buffered TMEM tile, two steps ahead
+//   warp 1      issues the O += P V products, with P read from TMEM and the accumulator resident
+//               in TMEM (two O accumulators alternate between items).  One thread cannot issue
+//               both streams fast enough: its barrier waits and commits between the batches of
+//               eight instructions left the tensor core idle a third of the time.  The two
+//               streams are ordered by barriers only (S of step g+2 overwrites P of step g once
+//               the product that read it has completed).
 //   warps 2-9   two softmax warpgroups that split the 128 key columns of a step; thread r of a
 //               warpgroup owns query row r (= TMEM lane r).  Per step a thread reads its 64
 //               scores, exchanges its partial row max with the twin thread of the other
@@ -89,8 +93,11 @@ struct FwdSmem {
 // P_FULL is split by step parity: S runs two steps ahead of P V, so the softmax threads can hand over
 // P of steps g and g+1 before the MMA thread has looked at step g; one barrier per parity keeps each
 // barrier at most one phase ahead of its waiter.
-enum FwdBar { F_Q_FULL = 0, F_Q_EMPTY = 2, F_K_FULL = 4, F_K_EMPTY = 6, F_V_FULL = 8, F_V_EMPTY = 10, F_S_FULL = 12,
-              F_P_FULL = 14, F_PV_DONE = 16, F_XCH = 17, F_LX = 18, F_O_DONE = 19, F_O_FREE = 21, F_COUNT = 23 };
+// S_FULL (all S products of a step have finished) also tells the producer that the step's K stage is
+// free; PV_DONE (all P V products of a step have finished) also frees the V stage, tells the S
+// issuer that the step's P has been consumed and orders a rescale of O behind the product.
+enum FwdBar { F_Q_FULL = 0, F_Q_EMPTY = 2, F_K_FULL = 4, F_V_FULL = 6, F_PV_DONE = 8, F_S_FULL = 10,
+              F_P_FULL = 12, F_XCH = 14, F_LX = 15, F_O_DONE = 16, F_O_FREE = 18, F_COUNT = 20 };
 
 // Work order: groups of 16 slices; inside a group the heaviest (latest) query tiles of all its
 // slices come first (balance) and the group's K and V (a few MB) stay in L2.
@@ -128,7 +135,7 @@ struct WorkCursor {
 };
 
 template <int D>
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(352, 1)
 attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                     const __grid_constant__ CUtensorMap tmap_v, const FwdParams p) {
     using L = FwdSmem<D>;
@@ -164,13 +171,12 @@ attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         *skip_s = skip;
         for (int s = 0; s < 2; ++s) {
             mbar_init(&bars[F_Q_FULL + s], 1); mbar_init(&bars[F_Q_EMPTY + s], 1);
-            mbar_init(&bars[F_K_FULL + s], 1); mbar_init(&bars[F_K_EMPTY + s], 1);
-            mbar_init(&bars[F_V_FULL + s], 1); mbar_init(&bars[F_V_EMPTY + s], 1);
+            mbar_init(&bars[F_K_FULL + s], 1);
+            mbar_init(&bars[F_V_FULL + s], 1); mbar_init(&bars[F_PV_DONE + s], 1);
             mbar_init(&bars[F_S_FULL + s], 1);
             mbar_init(&bars[F_P_FULL + s], 256);
             mbar_init(&bars[F_O_DONE + s], 1); mbar_init(&bars[F_O_FREE + s], 256);
         }
-        mbar_init(&bars[F_PV_DONE], 1);
         mbar_init(&bars[F_XCH], 256);
         mbar_init(&bars[F_LX], 256);
         fence_barrier_init();
@@ -206,13 +212,13 @@ attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 }
                 const uint32_t st = g & 1u, ph = ((g >> 1) & 1u) ^ 1u;
                 FWD_STATE(0, (int)g, c.n, c.j * 10 + 2);
-                if (!mbar_wait(ws, &bars[F_K_EMPTY + st], ph, DEERS_KERR_FWD_F16 | 2)) break;
+                if (!mbar_wait(ws, &bars[F_S_FULL + st], ph, DEERS_KERR_FWD_F16 | 2)) break;      // S of step g-2 done
                 mbar_arrive_expect_tx(&bars[F_K_FULL + st], TILE_BYTES);
 #pragma unroll
                 for (int blk = 0; blk < DBLK; ++blk)
                     tma_load_4d(sK + st * TILE_BYTES + blk * BLOCK_BYTES, &tmap_k, &bars[F_K_FULL + st], blk * 64, c.j * BN, h, b);
                 FWD_STATE(0, (int)g, c.n, c.j * 10 + 3);
-                if (!mbar_wait(ws, &bars[F_V_EMPTY + st], ph, DEERS_KERR_FWD_F16 | 3)) break;
+                if (!mbar_wait(ws, &bars[F_PV_DONE + st], ph, DEERS_KERR_FWD_F16 | 3)) break;     // P V of step g-2 done
                 mbar_arrive_expect_tx(&bars[F_V_FULL + st], TILE_BYTES);
 #pragma unroll
                 for (int blk = 0; blk < DBLK; ++blk)
@@ -221,49 +227,19 @@ attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             }
         }
     } else if (warp == 1) {
-        // ------------------------------ MMA issuer ------------------------------
+        // ------------------------------ P V issuer ------------------------------
         if (lane == 0) {
-            constexpr uint32_t IDESC_S = idesc_f16(BM, BN, 0, 0);      // S: K-major A (Q) and B (K)
             constexpr uint32_t IDESC_O = idesc_f16(BM, D, 0, 1);       // O: A = P from TMEM, B = V MN-major
-            // Step-0 descriptors built once; each MMA adds a constant (single-thread issue must
-            // stay faster than MMA execution).
             constexpr uint64_t STAGE_STEP = TILE_BYTES >> 4;
-            const uint64_t q_km0 = desc_kmajor(smem_u32(sQ), 0, BLOCK_BYTES);
-            const uint64_t k_km0 = desc_kmajor(smem_u32(sK), 0, BLOCK_BYTES), v_mn0 = desc_mnmajor(smem_u32(sV), 0, BLOCK_BYTES);
-            WorkCursor sc, pc;                                       // S runs two steps ahead of P V
-            sc.init(p, nq, n_items);
+            const uint64_t v_mn0 = desc_mnmajor(smem_u32(sV), 0, BLOCK_BYTES);
+            WorkCursor pc;
             pc.init(p, nq, n_items);
-            uint32_t gs = 0, gp = 0;
-            bool ok = true;
-            auto issue_s = [&]() -> bool {
-                const int qb = sc.n & 1;
-                FWD_STATE(1, (int)gs, sc.n, sc.j * 10 + 4);
-                if (sc.j == 0 && !mbar_wait(ws, &bars[F_Q_FULL + qb], ((uint32_t)sc.n >> 1) & 1u, DEERS_KERR_FWD_F16 | 4)) return false;
-                FWD_STATE(1, (int)gs, sc.n, sc.j * 10 + 5);
-                if (!mbar_wait(ws, &bars[F_K_FULL + (gs & 1u)], (gs >> 1) & 1u, DEERS_KERR_FWD_F16 | 5)) return false;
-                tc_fence_after_sync();
-                const uint64_t q_km = q_km0 + (uint64_t)qb * STAGE_STEP, k_km = k_km0 + (uint64_t)(gs & 1u) * STAGE_STEP;
-                const uint32_t d_tmem = tmem + TM_S + (gs & 1u) * 128u;
-#pragma unroll
-                for (int ks = 0; ks < D / 16; ++ks)
-                    umma_ss(d_tmem, q_km + kmajor_step(ks, BLOCK_BYTES), k_km + kmajor_step(ks, BLOCK_BYTES), IDESC_S, ks > 0);
-                umma_commit(&bars[F_S_FULL + (gs & 1u)]);
-                umma_commit(&bars[F_K_EMPTY + (gs & 1u)]);
-                if (sc.j == sc.ntiles - 1) umma_commit(&bars[F_Q_EMPTY + qb]);     // last product reading this Q
-                ++gs;
-                sc.advance(p, nq, n_items);
-                return true;
-            };
-            for (int pre = 0; ok && pre < 2 && sc.valid(n_items); ++pre) ok = issue_s();
-            while (ok && pc.valid(n_items)) {
+            for (uint32_t gp = 0; pc.valid(n_items); ++gp) {
                 const uint32_t st = gp & 1u;
                 FWD_TRACE(0, gp, 0);
-                FWD_STATE(1, (int)gp, pc.n, pc.j * 10 + 6);
                 if (!mbar_wait(ws, &bars[F_P_FULL + st], (gp >> 1) & 1u, DEERS_KERR_FWD_F16 | 6)) break;
                 FWD_TRACE(0, gp, 1);
-                FWD_STATE(1, (int)gp, pc.n, pc.j * 10 + 7);
                 if (!mbar_wait(ws, &bars[F_V_FULL + st], (gp >> 1) & 1u, DEERS_KERR_FWD_F16 | 7)) break;
-                FWD_STATE(1, (int)gp, pc.n, pc.j * 10 + 8);
                 // The accumulator of item n was last used by item n-2: its epilogue must be over.
                 if (pc.j == 0 && !mbar_wait(ws, &bars[F_O_FREE + (pc.n & 1)], (((uint32_t)pc.n >> 1) & 1u) ^ 1u, DEERS_KERR_FWD_F16 | 8)) break;
                 tc_fence_after_sync();
@@ -274,18 +250,44 @@ attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 for (int ks = 0; ks < BN / 16; ++ks)
                     umma_ts(o_tmem, p_tmem + (uint32_t)(ks >> 2) * 64u + (uint32_t)(ks & 3) * 8u, v_mn + mnmajor_step(ks),
                             IDESC_O, (pc.j > 0 || ks > 0));
-                umma_commit(&bars[F_PV_DONE]);
-                umma_commit(&bars[F_V_EMPTY + st]);
+                umma_commit(&bars[F_PV_DONE + st]);
                 FWD_TRACE(0, gp, 2);
                 if (pc.j == pc.ntiles - 1) umma_commit(&bars[F_O_DONE + (pc.n & 1)]);
-                ++gp;
                 pc.advance(p, nq, n_items);
-                // S of step gp+1 reuses the TMEM tile whose P the product above has just consumed.
-                if (sc.valid(n_items)) ok = issue_s();
-                FWD_TRACE(0, gp - 1, 3);
+                FWD_TRACE(0, gp, 3);
             }
         }
-    } else {
+    } else if (warp == 10) {
+        // ------------------------------ S issuer ------------------------------
+        if (lane == 0) {
+            constexpr uint32_t IDESC_S = idesc_f16(BM, BN, 0, 0);      // S: K-major A (Q) and B (K)
+            constexpr uint64_t STAGE_STEP = TILE_BYTES >> 4;
+            const uint64_t q_km0 = desc_kmajor(smem_u32(sQ), 0, BLOCK_BYTES);
+            const uint64_t k_km0 = desc_kmajor(smem_u32(sK), 0, BLOCK_BYTES);
+            WorkCursor sc;
+            sc.init(p, nq, n_items);
+            for (uint32_t gs = 0; sc.valid(n_items); ++gs) {
+                const uint32_t st = gs & 1u;
+                const int qb = sc.n & 1;
+                FWD_TRACE(0, gs, 4);
+                if (sc.j == 0 && !mbar_wait(ws, &bars[F_Q_FULL + qb], ((uint32_t)sc.n >> 1) & 1u, DEERS_KERR_FWD_F16 | 4)) break;
+                if (!mbar_wait(ws, &bars[F_K_FULL + st], (gs >> 1) & 1u, DEERS_KERR_FWD_F16 | 5)) break;
+                // This S tile still holds P of step gs-2 until the product reading it has finished.
+                if (!mbar_wait(ws, &bars[F_PV_DONE + st], ((gs >> 1) & 1u) ^ 1u, DEERS_KERR_FWD_F16 | 0x15)) break;
+                tc_fence_after_sync();
+                FWD_TRACE(0, gs, 5);
+                const uint64_t q_km = q_km0 + (uint64_t)qb * STAGE_STEP, k_km = k_km0 + (uint64_t)st * STAGE_STEP;
+                const uint32_t d_tmem = tmem + TM_S + st * 128u;
+#pragma unroll
+                for (int ks = 0; ks < D / 16; ++ks)
+                    umma_ss(d_tmem, q_km + kmajor_step(ks, BLOCK_BYTES), k_km + kmajor_step(ks, BLOCK_BYTES), IDESC_S, ks > 0);
+                umma_commit(&bars[F_S_FULL + st]);
+                FWD_TRACE(0, gs, 6);
+                if (sc.j == sc.ntiles - 1) umma_commit(&bars[F_Q_EMPTY + qb]);     // last product reading this Q
+                sc.advance(p, nq, n_items);
+            }
+        }
+    } else if (warp < 10) {
         // ------------------------------ softmax + epilogue ------------------------------
         const int g = (warp - 2) >> 2;                          // warpgroup: key columns [64g, 64g+64)
         const int lane_base = (warp & 3) * 32;
@@ -426,7 +428,7 @@ attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 if (j > 0 && warp_grow) {
                     // O += P V of the previous step must have landed before O is rescaled.
                     if (lane == 0) FWD_STATE(warp, (int)gstep, n, j * 100 + 13);
-                    if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[F_PV_DONE], (gstep - 1u) & 1u, DEERS_KERR_FWD_F16 | 13))) { alive = false; break; }
+                    if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[F_PV_DONE + ((gstep - 1u) & 1u)], ((gstep - 1u) >> 1) & 1u, DEERS_KERR_FWD_F16 | 13))) { alive = false; break; }
                     tc_fence_after_sync();
                     const uint32_t to = tmem + TM_O + (uint32_t)(n & 1) * D + t_lane + g * DH;
 #pragma unroll
@@ -484,7 +486,7 @@ int fwd_launch(deers_ctx* ctx, const deers_attn_desc* d, const void* q, const vo
     p.sched = deers_get_schedule(ctx, d->B, d->H, (int)nq, d->causal, (int)grid, &p.sched_rows);
     {
         KernelTimerScope ts(ctx, DEERS_K_FWD);
-        attn_fwd_f16_kernel<D><<<grid, 320, smem, ctx->stream>>>(tq, tk, tv, p);
+        attn_fwd_f16_kernel<D><<<grid, 352, smem, ctx->stream>>>(tq, tk, tv, p);
     }
     ctx->launches += 1;
     DEERS_CUDA_TRY(ctx, cudaGetLastError());
