@@ -801,8 +801,9 @@ attn_bwd_dq_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
 }
 
 // delta[row] = sum_d dO[row][d] * O[row][d] and lse2[row] = lse[row] * log2(e) on the padded
-// [B*H][Tpad] grid (0 beyond T).  D/8 lanes share a row (16-byte loads), so a warp covers
-// 256 / D rows per step; grid-stride over row groups.
+// [B*H][Tpad] grid (0 beyond T).  D/8 lanes share a row (16-byte loads); a warp takes 4 * 256 / D
+// consecutive rows per step with all eight loads of a lane in flight before the first is used;
+// grid-stride over such row groups.  The row count fits 32 bits (checked by the launcher).
 template <int D>
 __global__ void __launch_bounds__(256)
 attn_bwd_prep_f16_kernel(const __half* __restrict__ o, const __half* __restrict__ d_o, const float* __restrict__ lse,
@@ -810,24 +811,35 @@ attn_bwd_prep_f16_kernel(const __half* __restrict__ o, const __half* __restrict_
                          long long so_b, long long so_h, long long so_t, long long sdo_b, long long sdo_h,
                          long long sdo_t) {
     constexpr int LPR = D / 8;                               // lanes per row
-    constexpr int RPW = 32 / LPR;                            // rows per warp step
+    constexpr int RPW = 32 / LPR;                            // rows per warp load
+    constexpr int U = 4;                                     // loads in flight per lane and tensor
     const int lane = threadIdx.x % 32;
     const int sub = lane % LPR, rw = lane / LPR;
-    const long long rows = (long long)B * H * Tpad;
-    const long long warp_global = (long long)blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
-    const long long warp_count = (long long)gridDim.x * (blockDim.x / 32);
-    for (long long base = warp_global * RPW; base < rows; base += warp_count * RPW) {
-        const long long row = base + rw;
-        float s = 0.f;
-        const bool in_grid = row < rows;
-        const int t = in_grid ? (int)(row % Tpad) : 0;
-        const int bh = in_grid ? (int)(row / Tpad) : 0;
-        const bool valid = in_grid && t < T;
-        if (valid) {
-            const int b = bh / H, h = bh % H;
-            const uint4 a = *reinterpret_cast<const uint4*>(o + b * so_b + h * so_h + (long long)t * so_t + sub * 8);
-            const uint4 g = *reinterpret_cast<const uint4*>(d_o + b * sdo_b + h * sdo_h + (long long)t * sdo_t + sub * 8);
-            const uint32_t av[4] = {a.x, a.y, a.z, a.w}, gv[4] = {g.x, g.y, g.z, g.w};
+    const unsigned rows = (unsigned)B * (unsigned)H * (unsigned)Tpad;
+    const unsigned warp_global = blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
+    const unsigned warp_count = gridDim.x * (blockDim.x / 32);
+    const unsigned ngroups = (rows + RPW * U - 1) / (RPW * U);
+    for (unsigned grp = warp_global; grp < ngroups; grp += warp_count) {
+        uint4 a[U], g[U];
+        unsigned row[U];
+        bool valid[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            row[u] = grp * (RPW * U) + u * RPW + rw;
+            const unsigned t = row[u] % (unsigned)Tpad, bh = row[u] / (unsigned)Tpad;
+            valid[u] = row[u] < rows && t < (unsigned)T;
+            a[u] = make_uint4(0u, 0u, 0u, 0u);
+            g[u] = a[u];
+            if (valid[u]) {
+                const unsigned b = bh / (unsigned)H, h = bh % (unsigned)H;
+                a[u] = *reinterpret_cast<const uint4*>(o + b * so_b + h * so_h + (long long)t * so_t + sub * 8);
+                g[u] = *reinterpret_cast<const uint4*>(d_o + b * sdo_b + h * sdo_h + (long long)t * sdo_t + sub * 8);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const uint32_t av[4] = {a[u].x, a[u].y, a[u].z, a[u].w}, gv[4] = {g[u].x, g[u].y, g[u].z, g[u].w};
+            float s = 0.f;
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const float2 af = __half22float2(*reinterpret_cast<const __half2*>(&av[e]));
@@ -835,12 +847,13 @@ attn_bwd_prep_f16_kernel(const __half* __restrict__ o, const __half* __restrict_
                 s = fmaf(af.x, gf.x, s);
                 s = fmaf(af.y, gf.y, s);
             }
-        }
 #pragma unroll
-        for (int off = LPR / 2; off >= 1; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-        if (in_grid && sub == 0) {
-            delta[row] = valid ? s : 0.f;
-            lse2[row] = valid ? lse[(long long)bh * T + t] * LOG2E : 0.f;
+            for (int off = LPR / 2; off >= 1; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+            if (row[u] < rows && sub == 0) {
+                const unsigned t = row[u] % (unsigned)Tpad, bh = row[u] / (unsigned)Tpad;
+                delta[row[u]] = valid[u] ? s : 0.f;
+                lse2[row[u]] = valid[u] ? lse[(long long)bh * T + t] * LOG2E : 0.f;
+            }
         }
     }
 }
@@ -869,7 +882,9 @@ int bwd_launch(deers_ctx* ctx, const deers_attn_desc* d, const void* q, const vo
     const long long prep_rows = BH * Tpad;
     {
         KernelTimerScope ts(ctx, DEERS_K_BWD_PREP);
-        const long long want = (prep_rows + 8 * (256 / D) - 1) / (8 * (256 / D));
+        if (prep_rows > 0x7fffffffLL) return DEERS_ERR_SHAPE;      // 32-bit row indices in the kernel
+        const long long per_block = 8LL * 4 * (256 / D);           // 8 warps x 4 loads x rows per load
+        const long long want = (prep_rows + per_block - 1) / per_block;
         const unsigned prep_grid = (unsigned)(want < 8LL * ctx->sm_count ? want : 8LL * ctx->sm_count);
         attn_bwd_prep_f16_kernel<D><<<prep_grid, 256, 0, ctx->stream>>>(
             (const __half*)o, (const __half*)d_o, lse, delta, lse2, d->B, d->H, d->T, Tpad, d->o_strides[0],
