@@ -20,9 +20,9 @@ SYMBOLS = [
     "deers_b200_attn_fwd", "deers_b200_attn_bwd", "deers_b200_status_string", "deers_b200_last_error",
     "deers_b200_launch_count", "deers_b200_selftest_umma", "deers_b200_kernel_timing",
     "deers_b200_kernel_time", "deers_b200_attn_bwd_f16_static", "deers_b200_attn_host_scratch_bytes",
-    "deers_b200_attn_fwd_bwd_host",
+    "deers_b200_attn_fwd_bwd_host", "deers_b200_rope_pack",
 ]
-K_FWD, K_BWD_PREP, K_BWD_MAIN, K_BWD_DQ = range(4)
+K_FWD, K_BWD_PREP, K_BWD_MAIN, K_BWD_DQ, K_ROPE = range(5)
 
 
 class AttnDesc(ctypes.Structure):
@@ -32,6 +32,12 @@ class AttnDesc(ctypes.Structure):
                 ("v_strides", ctypes.c_int64 * 4), ("o_strides", ctypes.c_int64 * 4),
                 ("do_strides", ctypes.c_int64 * 4), ("dq_strides", ctypes.c_int64 * 4),
                 ("dk_strides", ctypes.c_int64 * 4), ("dv_strides", ctypes.c_int64 * 4)]
+
+
+class RopeDesc(ctypes.Structure):
+    _fields_ = [("B", ctypes.c_int32), ("T", ctypes.c_int32), ("H", ctypes.c_int32), ("D", ctypes.c_int32),
+                ("dtype", ctypes.c_int32), ("inverse", ctypes.c_int32),
+                ("src_strides", ctypes.c_int64 * 4), ("dst_strides", ctypes.c_int64 * 4)]
 
 
 _lib = None
@@ -70,6 +76,7 @@ def lib() -> ctypes.CDLL:
     L.deers_b200_attn_host_scratch_bytes.argtypes = [dp, i32]
     L.deers_b200_attn_host_scratch_bytes.restype = sz
     L.deers_b200_attn_fwd_bwd_host.argtypes = [vp, dp] + [vp] * 9 + [i32, vp, sz]
+    L.deers_b200_rope_pack.argtypes = [vp, ctypes.POINTER(RopeDesc), vp, vp, vp, vp]
     L.deers_b200_status_string.argtypes = [i32]
     L.deers_b200_status_string.restype = ctypes.c_char_p
     L.deers_b200_last_error.argtypes = [vp]

@@ -127,12 +127,21 @@ def default_scale(head_dim: int) -> float:
     return 1.0 / math.sqrt(float(head_dim))
 
 
-def attention_fwd(q, k, v, scale: float, causal: bool = True):
-    """Storage-level forward: returns (o [B,H,T,D] compact, lse [B,H,T] float32)."""
+def attention_fwd(q, k, v, scale: float, causal: bool = True, token_major_out: bool = False):
+    """Storage-level forward: returns (o [B,H,T,D], lse [B,H,T] float32).
+
+    o is compact by default.  With ``token_major_out`` its memory is a compact [B,T,H,D] buffer
+    and the returned tensor is the [B,H,T,D] view of it, so the module's
+    ``permute([0,2,1,3]).reshape([B,T,C])`` (src/models/gpt.rs:144) is a free view instead of the
+    compaction copy of src/ops.rs:913: the kernels write through the view's strides."""
     _check_inputs("attention_fwd", (q, k, v))
     q, k, v = _compact(q), _compact(k), _compact(v)
     ctx = Context.current(q.device)
-    o = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+    if token_major_out:
+        B, H, T, D = q.shape
+        o = torch.empty((B, T, H, D), dtype=q.dtype, device=q.device).permute(0, 2, 1, 3)
+    else:
+        o = torch.empty(q.shape, dtype=q.dtype, device=q.device)
     lse = torch.empty(q.shape[:3], dtype=torch.float32, device=q.device)
     d = _desc(q, k, v, o, scale=scale, causal=causal)
     _lib.check(_lib.lib().deers_b200_attn_fwd(ctx.handle, ctypes.byref(d), q.data_ptr(), k.data_ptr(),
@@ -162,6 +171,104 @@ def attention_bwd(q, k, v, o, lse, d_o, scale: float, causal: bool = True, works
     return dq, dk, dv
 
 
+def precompute_rotary_embeddings(seq_len: int, head_dim: int, base: float = 10000.0,
+                                 dtype: torch.dtype = torch.float32, device="cpu"):
+    """cos / sin cache shaped [1, T, 1, D/2] like the reference's (src/models/gpt.rs:12-46): host
+    arithmetic in f32 (inv_freq = 1 / base^(2i/D), angle = t * inv_freq), rounded to f16 when asked."""
+    if head_dim % 2:
+        raise LayoutMismatch("RoPE requires an even head dimension")
+    if dtype not in _DTYPES:
+        raise DTypeMismatch("RoPE requires a floating-point dtype")
+    half = head_dim // 2
+    channel = (2 * torch.arange(half, dtype=torch.float32))
+    inv_freq = 1.0 / torch.pow(torch.tensor(base, dtype=torch.float32), channel / float(head_dim))
+    freqs = torch.arange(seq_len, dtype=torch.float32)[:, None] * inv_freq[None, :]
+    shape = (1, seq_len, 1, half)
+    return (freqs.cos().to(dtype).reshape(shape).to(device), freqs.sin().to(dtype).reshape(shape).to(device))
+
+
+def _rope_call(src, cos, sin, dst, src_strides, dst_strides, B, T, H, D, inverse: bool) -> None:
+    ctx = Context.current(src.device)
+    d = _lib.RopeDesc()
+    d.B, d.T, d.H, d.D = B, T, H, D
+    d.dtype, d.inverse = _DTYPES[src.dtype], int(inverse)
+    d.src_strides = (ctypes.c_int64 * 4)(*src_strides)
+    d.dst_strides = (ctypes.c_int64 * 4)(*dst_strides)
+    _lib.check(_lib.lib().deers_b200_rope_pack(ctx.handle, ctypes.byref(d), src.data_ptr(), cos.data_ptr(),
+                                               sin.data_ptr(), dst.data_ptr()), ctx.handle)
+
+
+def _check_rope(name: str, x, cos, sin, T: int, D: int):
+    if x.dim() != 4:
+        raise LayoutMismatch(f"{name}: RoPE expects a 4D attention tensor, got {tuple(x.shape)}")
+    if D % 2:
+        raise LayoutMismatch(f"{name}: RoPE requires an even head dimension")
+    if x.dtype not in _DTYPES:
+        raise DTypeMismatch(f"{name}: unsupported dtype {x.dtype}")
+    if x.device.type != "cuda":
+        raise DeviceMismatch(f"{name}: the fused op runs on the CUDA device only")
+    if cos.shape != sin.shape:
+        raise LayoutMismatch(f"{name}: RoPE cos/sin shapes must match")
+    if cos.numel() != T * (D // 2) or cos.shape[-1] != D // 2:
+        raise LayoutMismatch(f"{name}: RoPE cache must be [1, T, 1, D/2] for T={T}, D={D}, got {tuple(cos.shape)}")
+    for c in (cos, sin):
+        if c.dtype != x.dtype:
+            raise DTypeMismatch(f"{name}: cache {c.dtype} vs tensor {x.dtype}")
+        if c.device != x.device:
+            raise DeviceMismatch(f"{name}: cache on {c.device}, tensor on {x.device}")
+    return cos.contiguous(), sin.contiguous()
+
+
+class RotaryPack:
+    """``apply_rotary_emb(x, cos, sin).permute([0,2,1,3])`` (src/models/gpt.rs:49-73,135-136) as ONE op:
+    x is the [B,T,H,D] projection output (any strides with inner stride 1), the result is a compact
+    [B,H,T,D] tensor ready for ``CausalAttention``; backward rotates the incoming [B,H,T,D] gradient
+    back and accumulates it as a [B,T,H,D] tensor.  Same life cycle as the other deers ops."""
+
+    def __init__(self, x, cos, sin):
+        self.x, self.cos, self.sin = x, cos, sin
+
+    @classmethod
+    def new(cls, x, cos, sin) -> "RotaryPack":
+        if x.dim() == 4:
+            cos, sin = _check_rope("RotaryPack", x, cos, sin, x.shape[1], x.shape[3])
+        else:
+            _check_rope("RotaryPack", x, cos, sin, 0, 0)
+        if x.stride(3) != 1:
+            x = x.contiguous()                      # inputs that need contiguity are compacted by the op
+        return cls(x, cos, sin)
+
+    def forward(self) -> torch.Tensor:
+        B, T, H, D = self.x.shape
+        y = torch.empty((B, H, T, D), dtype=self.x.dtype, device=self.x.device)
+        ys = y.stride()
+        _rope_call(self.x, self.cos, self.sin, y, self.x.stride(), (ys[0], ys[2], ys[1], ys[3]), B, T, H, D, False)
+        return y
+
+    def backward(self, grads: "GradientStore", out_grad: torch.Tensor) -> None:
+        B, T, H, D = self.x.shape
+        if tuple(out_grad.shape) != (B, H, T, D):
+            raise LayoutMismatch(f"RotaryPack.backward: gradient {tuple(out_grad.shape)} vs {(B, H, T, D)}")
+        if out_grad.dtype != self.x.dtype:
+            raise DTypeMismatch(f"RotaryPack.backward: {out_grad.dtype} vs {self.x.dtype}")
+        g = out_grad if out_grad.stride(3) == 1 else out_grad.contiguous()
+        dx = torch.empty((B, T, H, D), dtype=self.x.dtype, device=self.x.device)
+        gs = g.stride()
+        _rope_call(g, self.cos, self.sin, dx, (gs[0], gs[2], gs[1], gs[3]), dx.stride(), B, T, H, D, True)
+        grads.accumulate(self.x, dx)
+
+    def dependencies(self) -> List[torch.Tensor]:
+        return [self.x]
+
+    def name(self) -> str:
+        return "RotaryPack"
+
+
+def rotary_pack(x, cos, sin) -> torch.Tensor:
+    """Tensor-method form: RotaryPack.new(..).forward()."""
+    return RotaryPack.new(x, cos, sin).forward()
+
+
 class GradientStore:
     """Insert-or-add gradient map keyed by tensor identity (src/backprop.rs:74-128)."""
 
@@ -188,21 +295,23 @@ class CausalAttention:
     pattern of LogSumExp / FusedLogSoftmax (src/ops.rs:1152-1159, 1214-1220).
     """
 
-    def __init__(self, q, k, v, scale: float, causal: bool = True):
+    def __init__(self, q, k, v, scale: float, causal: bool = True, token_major_out: bool = False):
         self.q, self.k, self.v = q, k, v
         self.scale, self.causal = float(scale), bool(causal)
+        self.token_major_out = bool(token_major_out)
         self.o: Optional[torch.Tensor] = None
         self.lse: Optional[torch.Tensor] = None
 
     @classmethod
-    def new(cls, q, k, v, scale: Optional[float] = None, causal: bool = True) -> "CausalAttention":
+    def new(cls, q, k, v, scale: Optional[float] = None, causal: bool = True,
+            token_major_out: bool = False) -> "CausalAttention":
         _check_inputs("CausalAttention", (q, k, v))
         if q.device.type != "cuda":
             raise DeviceMismatch("CausalAttention: the fused op runs on the CUDA device only")
-        return cls(q, k, v, default_scale(q.shape[3]) if scale is None else scale, causal)
+        return cls(q, k, v, default_scale(q.shape[3]) if scale is None else scale, causal, token_major_out)
 
     def forward(self) -> torch.Tensor:
-        self.o, self.lse = attention_fwd(self.q, self.k, self.v, self.scale, self.causal)
+        self.o, self.lse = attention_fwd(self.q, self.k, self.v, self.scale, self.causal, self.token_major_out)
         return self.o
 
     def backward(self, grads: GradientStore, out_grad: torch.Tensor) -> None:

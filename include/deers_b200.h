@@ -187,6 +187,37 @@ int deers_b200_attn_bwd_f16_static(deers_ctx* ctx, const deers_attn_desc* desc, 
                                    void* dk, void* dv);
 
 /*
+ * Rotary embedding fused with the head-major pack that feeds the attention op, and its inverse for
+ * the gradients.  Replaces, for q and for k: `apply_rotary_emb` (`src/models/gpt.rs:49-73`: two
+ * narrows, four multiplies, two adds and a `cat` that is built from two transposes,
+ * `src/tensor.rs:428-440`), the `permute([0,2,1,3])` that follows it (`gpt.rs:135-136`) and the
+ * compaction copy the batched GEMM then needs (`src/ops.rs:913`) — about 14 launches and three
+ * tensor-sized copies per layer; the backward of those ops is the same call with `inverse = 1`.
+ *
+ * One row of D elements is read at src + b*src_strides[0] + t*src_strides[1] + h*src_strides[2],
+ * split into halves x1 | x2, rotated with row t of the cos / sin cache ([T, D/2] contiguous, same
+ * dtype as the tensor: `precompute_rotary_embeddings`, `gpt.rs:12-46`) and written at the matching
+ * dst address:
+ *     inverse = 0:  y1 = x1*cos + x2*sin,      y2 = x1*(-sin) + x2*cos
+ *     inverse = 1:  x1 = y1*cos + y2*(-sin),   x2 = y1*sin + y2*cos
+ * Every multiply and add rounds to the storage type, exactly like the reference's separate ops, so
+ * results are bit-identical to its CPU path.  Strides are in elements, in (b, t, h, d) order for BOTH
+ * tensors, inner stride 1: the forward call passes the [B,T,H,D] strides of the projection output as
+ * src and the strides of a [B,H,T,D] buffer (b: H*T*D, t: D, h: T*D) as dst; the backward call swaps
+ * them.  Rows, halves and cache rows on 16-byte boundaries take the 16-byte path, anything else a
+ * scalar path.  Enqueued on the context's stream; no allocation, no synchronisation.
+ */
+typedef struct deers_rope_desc {
+    int32_t B, T, H, D;        /* D even */
+    int32_t dtype;             /* DEERS_F16 or DEERS_F32: tensor and cache */
+    int32_t inverse;           /* 0 rotate, 1 rotate back (gradients) */
+    int64_t src_strides[4];    /* (b, t, h, d), elements */
+    int64_t dst_strides[4];
+} deers_rope_desc;
+int deers_b200_rope_pack(deers_ctx* ctx, const deers_rope_desc* desc, const void* src, const void* cos_cache,
+                         const void* sin_cache, void* dst);
+
+/*
  * Status text, the way backend failures become `Error::Cuda(String)`
  * (`src/error.rs:40-41`).  last_error adds the detail of the most recent failure
  * on this context (CUDA error string, or which kernel wait gave up).
@@ -208,7 +239,7 @@ uint64_t deers_b200_launch_count(deers_ctx* ctx);
  * milliseconds and the number of launches of one kernel kind since timing was
  * enabled (or since the last call with reset != 0).
  */
-enum { DEERS_K_FWD = 0, DEERS_K_BWD_PREP = 1, DEERS_K_BWD_MAIN = 2, DEERS_K_BWD_DQ = 3, DEERS_K_COUNT = 4 };
+enum { DEERS_K_FWD = 0, DEERS_K_BWD_PREP = 1, DEERS_K_BWD_MAIN = 2, DEERS_K_BWD_DQ = 3, DEERS_K_ROPE = 4, DEERS_K_COUNT = 5 };
 int deers_b200_kernel_timing(deers_ctx* ctx, int enable);
 int deers_b200_kernel_time(deers_ctx* ctx, int kind, int reset, double* total_ms, uint64_t* launches);
 

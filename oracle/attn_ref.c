@@ -172,3 +172,43 @@ API int ref_attn_fwd_bwd(const float* q, const float* k, const float* v, const f
     }
     return fail;
 }
+
+/*
+ * Rotary embedding + head-major permute, f32, op by op as the reference graph evaluates it
+ * (paths inside the deers repository):
+ *   src/models/gpt.rs:49-73    apply_rotary_emb on [B,T,H,D]: x1 = x[..., :D/2], x2 = x[..., D/2:],
+ *                              y1 = x1*cos + x2*sin, y2 = x1*(sin * -1) + x2*cos, cat([y1, y2], 3)
+ *   src/models/gpt.rs:135-136  .permute([0,2,1,3]) -> [B,H,T,D]
+ *   src/ops.rs:130-173, 176-254 EWiseAdd / EWiseMul: one rounding per op (no fused multiply-add), and
+ *                              their backward (g*other, g) summed by backprop.rs:101-112
+ * inverse = 0: x is [B,T,H,D], y is [B,H,T,D].
+ * inverse = 1: x is the gradient w.r.t. y laid out [B,H,T,D], y receives the gradient w.r.t. x as
+ *              [B,T,H,D]: dx1 = dy1*cos + dy2*(sin * -1), dx2 = dy1*sin + dy2*cos.
+ * cos / sin: [T, D/2].  The products must round separately, so contraction into FMA is disabled.
+ */
+__attribute__((visibility("default"), optimize("fp-contract=off")))
+void ref_rope_pack(const float* x, const float* cosv, const float* sinv, int B, int T, int H, int D, int inverse,
+                   float* y) {
+    const int half = D / 2;
+#pragma omp parallel for collapse(2) schedule(static)
+    for (int b = 0; b < B; ++b) {
+        for (int t = 0; t < T; ++t) {
+            for (int h = 0; h < H; ++h) {
+                const size_t bthd = (((size_t)b * T + t) * H + h) * D;
+                const size_t bhtd = (((size_t)b * H + h) * T + t) * D;
+                const float* src = x + (inverse ? bhtd : bthd);
+                float* dst = y + (inverse ? bthd : bhtd);
+                for (int i = 0; i < half; ++i) {
+                    const float c = cosv[(size_t)t * half + i];
+                    const float s = inverse ? -sinv[(size_t)t * half + i] : sinv[(size_t)t * half + i];
+                    const float a = src[i], bb = src[half + i];
+                    const float p1 = a * c, p2 = bb * s;       /* EWiseMul, EWiseMul */
+                    const float ns = s * -1.0f;                 /* ScalarMul by -1 (exact) */
+                    const float p3 = a * ns, p4 = bb * c;
+                    dst[i] = p1 + p2;                           /* EWiseAdd */
+                    dst[half + i] = p3 + p4;
+                }
+            }
+        }
+    }
+}

@@ -38,6 +38,8 @@ def lib() -> ctypes.CDLL:
         L.ref_causal_mask.restype = None
         L.ref_attn_fwd.argtypes = [fp, fp, fp] + [ctypes.c_int] * 4 + [ctypes.c_float, ctypes.c_int, fp, fp]
         L.ref_attn_fwd.restype = ctypes.c_int
+        L.ref_rope_pack.argtypes = [fp, fp, fp] + [ctypes.c_int] * 5 + [fp]
+        L.ref_rope_pack.restype = None
         L.ref_attn_fwd_bwd.argtypes = ([fp, fp, fp, fp] + [ctypes.c_int] * 4 +
                                        [ctypes.c_float, ctypes.c_int] + [fp] * 5)
         L.ref_attn_fwd_bwd.restype = ctypes.c_int
@@ -95,3 +97,52 @@ def attn_fwd_bwd(q, k, v, d_o, scale=None, causal=True):
     if rc:
         raise MemoryError("oracle: allocation failed")
     return o, lse, dq, dk, dv
+
+
+def precompute_rotary_embeddings(seq_len: int, head_dim: int, base: float = 10000.0):
+    """cos / sin cache [T, D/2] in f32, the arithmetic of gpt.rs:12-46: inv_freq = 1 / base^(2i/D)
+    in f32, angle = t * inv_freq in f32, then cos / sin.  (The reference keeps the cache as
+    [1, T, 1, D/2]; the two unit axes only serve broadcasting.)"""
+    assert head_dim % 2 == 0, "RoPE requires an even head dimension"
+    half = head_dim // 2
+    channel = (2 * np.arange(half)).astype(np.float32)
+    inv_freq = (np.float32(1.0) / np.power(np.float32(base), channel / np.float32(head_dim))).astype(np.float32)
+    freqs = (np.arange(seq_len, dtype=np.float32)[:, None] * inv_freq[None, :]).astype(np.float32)
+    return np.cos(freqs).astype(np.float32), np.sin(freqs).astype(np.float32)
+
+
+def rope_pack(x, cos, sin, inverse: bool = False):
+    """f32: [B,T,H,D] -> rotated [B,H,T,D]; inverse: gradient [B,H,T,D] -> [B,T,H,D] (C restatement)."""
+    x = _c(x)
+    cos = np.ascontiguousarray(cos, dtype=np.float32)
+    sin = np.ascontiguousarray(sin, dtype=np.float32)
+    if inverse:
+        B, H, T, D = x.shape
+        y = np.empty((B, T, H, D), np.float32)
+    else:
+        B, T, H, D = x.shape
+        y = np.empty((B, H, T, D), np.float32)
+    assert cos.shape == (T, D // 2) and sin.shape == (T, D // 2)
+    lib().ref_rope_pack(_p(x), _p(cos), _p(sin), B, T, H, D, int(inverse), _p(y))
+    return y
+
+
+def rope_pack_f16(x, cos, sin, inverse: bool = False):
+    """f16 storage: the same op chain with every multiply and add rounded to f16, as the reference's
+    f16 element-wise ops do (numpy float16 arithmetic rounds each operation once)."""
+    x = np.asarray(x, np.float16)
+    cos = np.asarray(cos, np.float16)
+    sin = np.asarray(sin, np.float16)
+    if inverse:
+        src = np.transpose(x, (0, 2, 1, 3))                     # [B,H,T,D] -> [B,T,H,D]
+        s = (sin * np.float16(-1.0))[None, :, None, :]
+    else:
+        src = x
+        s = sin[None, :, None, :]
+    c = cos[None, :, None, :]
+    half = src.shape[3] // 2
+    a, b = src[..., :half], src[..., half:]
+    y1 = a * c + b * s
+    y2 = a * (s * np.float16(-1.0)) + b * c
+    y = np.concatenate([y1, y2], axis=3).astype(np.float16)     # [B,T,H,D]
+    return y if inverse else np.ascontiguousarray(np.transpose(y, (0, 2, 1, 3)))

@@ -1,4 +1,4 @@
-"""Generates tests/golden/attn_golden.npz.
+"""Generates tests/golden/attn_golden.npz and tests/golden/rope_golden.npz.
 
 The reference (deers) is Rust and cannot run in the build image, and its own
 attention test computes expected values with candle at test time, so there is no
@@ -7,6 +7,10 @@ implementation instead: float64 torch autograd over the exact op chain of
 src/models/gpt.rs:139-144 (matmul, scale, additive -inf mask, softmax, matmul),
 seeded, at small shapes including the shape of the reference's own attention
 test (tests/gpt.rs:38-49: B=2, T=3, 2 heads, head_dim 2).
+
+rope_golden.npz holds the rotary embedding + head-major permute of src/models/gpt.rs:49-73,135-136
+(x [B,T,H,D] -> y [B,H,T,D]) and its gradient, again as float64 torch autograd over the reference's op
+chain (narrow, mul, add, cat, permute), with the cos / sin cache of gpt.rs:12-46 computed in f32.
 
 Run from the repository root:  python tests/golden/make_golden.py
 """
@@ -42,7 +46,47 @@ def run(B, H, T, D, causal, seed):
     return {n: t.detach().to(torch.float32).numpy() for n, t in out.items()}
 
 
+ROPE_CASES = {  # name: (B, T, H, D)
+    "gpt_rs_shape": (2, 3, 2, 2),
+    "odd_T17_D8": (1, 17, 3, 8),
+    "T64_D32": (2, 64, 4, 32),
+    "T5_D64": (1, 5, 2, 64),
+}
+
+
+def rope_cache(T, D, base=10000.0):
+    half = D // 2
+    channel = (2 * np.arange(half)).astype(np.float32)
+    inv_freq = (np.float32(1.0) / np.power(np.float32(base), channel / np.float32(D))).astype(np.float32)
+    freqs = (np.arange(T, dtype=np.float32)[:, None] * inv_freq[None, :]).astype(np.float32)
+    return np.cos(freqs).astype(np.float32), np.sin(freqs).astype(np.float32)
+
+
+def run_rope(B, T, H, D, seed):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(B, T, H, D, generator=g, dtype=torch.float32)
+    dy = torch.randn(B, H, T, D, generator=g, dtype=torch.float32)
+    cos, sin = rope_cache(T, D)
+    c = torch.from_numpy(cos).double()[None, :, None, :]
+    s = torch.from_numpy(sin).double()[None, :, None, :]
+    x64 = x.double().requires_grad_(True)
+    x1, x2 = x64.narrow(3, 0, D // 2), x64.narrow(3, D // 2, D // 2)
+    y = torch.cat([x1 * c + x2 * s, x1 * (s * -1.0) + x2 * c], 3).permute(0, 2, 1, 3)
+    y.backward(dy.double())
+    out = dict(x=x, dy=dy, y=y.detach().contiguous(), dx=x64.grad)
+    res = {n: t.detach().to(torch.float32).numpy() for n, t in out.items()}
+    res["cos"], res["sin"] = cos, sin
+    return res
+
+
 def main():
+    rblob = {}
+    for idx, (name, (B, T, H, D)) in enumerate(ROPE_CASES.items()):
+        for key, arr in run_rope(B, T, H, D, 2000 + idx).items():
+            rblob[f"{name}/{key}"] = arr
+    rpath = os.path.join(os.path.dirname(os.path.abspath(__file__)), "rope_golden.npz")
+    np.savez_compressed(rpath, **rblob)
+    print(rpath, os.path.getsize(rpath), "bytes")
     blob = {}
     for idx, (name, (B, H, T, D, causal)) in enumerate(CASES.items()):
         for key, arr in run(B, H, T, D, causal, 1000 + idx).items():

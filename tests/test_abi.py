@@ -89,3 +89,26 @@ def test_ops_refuse_cpu_tensors():
         ops.CausalAttention.new(q, q.half(), q)
     with pytest.raises(LayoutMismatch):
         ops.CausalAttention.new(q[0], q[0], q[0])
+
+
+def test_rotary_pack_validation_without_a_gpu():
+    # Constructor errors follow the reference's conventions (src/error.rs:13-26; the asserts of
+    # apply_rotary_emb, src/models/gpt.rs:49-66); no compute call is made.
+    import pytest
+    import torch
+    from deers_b200 import ops
+    from deers_b200.errors import DeviceMismatch, DTypeMismatch, LayoutMismatch
+    cos, sin = ops.precompute_rotary_embeddings(5, 8)
+    assert tuple(cos.shape) == (1, 5, 1, 4) and cos.dtype == torch.float32
+    assert torch.equal(cos[0, 0, 0], torch.ones(4)) and torch.equal(sin[0, 0, 0], torch.zeros(4))
+    x = torch.zeros(2, 5, 3, 8)
+    with pytest.raises(DeviceMismatch):
+        ops.RotaryPack.new(x, cos, sin)                       # CPU tensors: there is no CPU fallback
+    with pytest.raises(LayoutMismatch):
+        ops.RotaryPack.new(torch.zeros(5, 3, 8), cos, sin)    # not 4-D
+    with pytest.raises(LayoutMismatch):
+        ops.RotaryPack.new(torch.zeros(2, 5, 3, 7), cos, sin)  # odd head_dim
+    with pytest.raises(DTypeMismatch):
+        ops.RotaryPack.new(torch.zeros(2, 5, 3, 8, dtype=torch.int64), cos, sin)
+    with pytest.raises(LayoutMismatch):
+        ops.precompute_rotary_embeddings(5, 7)

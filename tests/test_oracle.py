@@ -80,3 +80,42 @@ def test_gradients_by_finite_differences():
             args_p[name] = xp; args_m[name] = xm
             fd = (loss(args_p["q"], args_p["k"], args_p["v"]) - loss(args_m["q"], args_m["k"], args_m["v"])) / (2 * eps)
             assert abs(fd - g[idx]) < 2e-3, (name, idx, fd, g[idx])
+
+
+def _rope_golden():
+    import os
+    blob = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "rope_golden.npz"))
+    cases = {}
+    for key in blob.files:
+        name, field = key.split("/")
+        cases.setdefault(name, {})[field] = blob[key]
+    return cases
+
+
+def test_rope_oracle_matches_golden():
+    # float64 autograd over the reference's op chain (tests/golden/make_golden.py) vs the f32 restatement
+    for name, c in _rope_golden().items():
+        y = ref.rope_pack(c["x"], c["cos"], c["sin"])
+        dx = ref.rope_pack(c["dy"], c["cos"], c["sin"], inverse=True)
+        assert np.abs(y - c["y"]).max() <= 1e-6 * max(np.abs(c["y"]).max(), 1.0), name
+        assert np.abs(dx - c["dx"]).max() <= 1e-6 * max(np.abs(c["dx"]).max(), 1.0), name
+        cos, sin = ref.precompute_rotary_embeddings(c["x"].shape[1], c["x"].shape[3])
+        assert np.array_equal(cos, c["cos"]) and np.array_equal(sin, c["sin"])
+
+
+def test_rope_oracle_op_order_and_f16_emulation():
+    rng = np.random.default_rng(1)
+    B, T, H, D = 2, 9, 3, 16
+    x = rng.standard_normal((B, T, H, D)).astype(np.float32)
+    cos, sin = ref.precompute_rotary_embeddings(T, D)
+    # numpy f32 evaluates the same chain with one rounding per op: identical bits
+    a, b = x[..., :D // 2], x[..., D // 2:]
+    c, s = cos[None, :, None, :], sin[None, :, None, :]
+    want = np.concatenate([a * c + b * s, a * (s * np.float32(-1)) + b * c], 3).transpose(0, 2, 1, 3)
+    assert np.array_equal(ref.rope_pack(x, cos, sin), want)
+    # position 0 is the identity rotation; rotating back restores x up to rounding
+    assert np.array_equal(ref.rope_pack(x, cos, sin)[:, :, 0, :], x[:, 0].transpose(0, 1, 2))
+    back = ref.rope_pack(ref.rope_pack(x, cos, sin), cos, sin, inverse=True)
+    assert np.abs(back - x).max() < 1e-6
+    y16 = ref.rope_pack_f16(x, cos, sin)
+    assert y16.dtype == np.float16 and np.abs(y16.astype(np.float32) - ref.rope_pack(x, cos, sin)).max() < 1e-2
