@@ -172,6 +172,80 @@ def workload_name(name, dtype, B, T, H, D):
     return f"{name}: causal attention fwd+bwd, {dtype}, B={B} T={T} H={H} head_dim={D}, scale 1/sqrt(D)"
 
 
+def run_rope(args, dtype, B, T, H, D):
+    """The pack that feeds the op: rope(q), rope(k) [B,T,H,D] -> [B,H,T,D] and the inverse rotation of
+    dQ, dK back to [B,T,H,D]: four launches per step, each reading and writing one tensor once."""
+    import numpy as np
+    import torch
+    from deers_b200 import _lib, ops
+    from oracle import ref
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a B200: there is no CPU fallback")
+    dev = torch.device("cuda", 0)
+    tdtype = torch.float16 if dtype == "f16" else torch.float32
+    esize = 2 if dtype == "f16" else 4
+    gen = torch.Generator(device=dev).manual_seed(4321)
+    xq, xk = (torch.randn(B, T, H, D, device=dev, dtype=torch.float32, generator=gen).to(tdtype) for _ in range(2))
+    gq, gk = (torch.randn(B, H, T, D, device=dev, dtype=torch.float32, generator=gen).to(tdtype) for _ in range(2))
+    cos, sin = (c.to(dev) for c in ops.precompute_rotary_embeddings(T, D, dtype=tdtype))
+    opq, opk = ops.RotaryPack.new(xq, cos, sin), ops.RotaryPack.new(xk, cos, sin)
+    ctx = ops.Context.current(dev)
+
+    def step():
+        grads = ops.GradientStore()
+        opq.forward(); opk.forward()
+        opq.backward(grads, gq); opk.backward(grads, gk)
+
+    sampler = ClockSampler(0)
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    ctx.kernel_timing(True)
+    launches0 = ctx.launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(args.steps):
+        step()
+    ev1.record()
+    torch.cuda.synchronize()
+    ms = ev0.elapsed_time(ev1) / args.steps
+    launches = ctx.launch_count() - launches0
+    k_ms, k_n = ctx.kernel_time(_lib.K_ROPE)
+    ctx.kernel_timing(False)
+    ctx.sync()
+    clocks = sampler.stop()
+    n = B * T * H * D
+    bytes_per_launch = 2.0 * n * esize + 2.0 * T * (D // 2) * esize      # tensor in + out, cache once
+    peaks = load_peaks()
+    achieved = bytes_per_launch / (k_ms / max(k_n, 1) * 1e-3) / 1e9
+    # CPU leg: the C restatement on a bounded sample of batch entries (f32; the f16 path is numpy)
+    bs = max(1, min(B, int(2e8 // max(1, T * H * D))))
+    xs = np.random.default_rng(0).standard_normal((bs, T, H, D)).astype(np.float32)
+    c32, s32 = ref.precompute_rotary_embeddings(T, D)
+    ref.rope_pack(xs, c32, s32)
+    t0 = time.perf_counter()
+    reps = 3
+    for _ in range(reps):
+        ref.rope_pack(xs, c32, s32)
+    cpu_s = (time.perf_counter() - t0) / reps
+    cpu_gbs = 2.0 * xs.size * 4 / cpu_s / 1e9
+    line = {"metric": "rope_pack_gbs", "value": 4 * bytes_per_launch / (ms * 1e-3) / 1e9, "unit": "GB/s", "n_gpus": 1,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": dtype, "data": "synthetic",
+            "config": {"workload": f"{args.workload}: rotary embedding + head-major pack, {dtype}, B={B} T={T} H={H} head_dim={D}",
+                       "per_step": "rope(q), rope(k), inverse rope(dq), inverse rope(dk)",
+                       "l2": "tensors larger than L2" if n * esize > 126e6 else "tensors fit L2"},
+            "gpu_launches": int(launches), "clocks": clocks, "e2e": None,
+            "roofline": {"bound": "hbm", "kernel": "rope_pack_kernel", "achieved": achieved, "peak": peaks["hbm_gbs"],
+                         "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "traffic": None,
+                         "bytes_per_launch": bytes_per_launch, "avg_launch_ms": k_ms / max(k_n, 1),
+                         "peak_source": peaks["source"] + " copy bandwidth"},
+            "cpu_baseline": {"value": cpu_gbs, "unit": "GB/s", "cores": ref.num_threads(), "kind": "port",
+                             "sample": f"{bs} of {B} batch entries, f32 C restatement of apply_rotary_emb + permute, "
+                                       f"{cpu_s:.3f} s per pass"}}
+    print(json.dumps(line))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -188,6 +262,9 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--rope", action="store_true",
+                    help="time the fused rotary embedding + head-major pack (q and k, forward and inverse) "
+                         "on the workload's shape instead of attention; 1 GPU")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -196,6 +273,9 @@ def main():
         B, T, H, D = (int(x) for x in args.shape.split(","))
         dtype = args.dtype or "f16"
         args.workload = "custom"
+    if args.rope:
+        run_rope(args, dtype, B, T, H, D)
+        return
     if args.impl == "reference":
         run_reference(args, dtype, B, T, H, D)
         return
