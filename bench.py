@@ -246,6 +246,83 @@ def run_rope(args, dtype, B, T, H, D):
     print(json.dumps(line))
 
 
+def run_adamw(args):
+    """One optimizer step of the reference's training loop: gradient norm, clip, AdamW over every parameter
+    (src/optim.rs:214-297), fused into three kinds of launches."""
+    import numpy as np
+    import torch
+    from deers_b200 import _lib, ops
+    from oracle import ref
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a B200: there is no CPU fallback")
+    dev = torch.device("cuda", 0)
+    # GPT of the reference's README config: wte, 6 x (q, k, v, out proj, fc, proj), lm_head
+    shapes = [(50257, 192)] + [(192, 192)] * 4 * 6 + [(192, 768), (768, 192)] * 6 + [(50257, 192)]
+    gen = torch.Generator(device=dev).manual_seed(99)
+    params = [torch.randn(s, device=dev, generator=gen) for s in shapes]
+    glist = [torch.randn(s, device=dev, generator=gen) for s in shapes]
+    n_elem = sum(p.numel() for p in params)
+    opt = ops.AdamW(params, lr=6e-4, betas=(0.9, 0.95), weight_decay=0.1)
+    ctx = ops.Context.current(dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)     # 88 MB of state fits L2: flush between steps
+
+    def step():
+        grads = ops.GradientStore()
+        for p, g in zip(params, glist):
+            grads.insert(p, g)
+        norm = ops.grad_norm_device(params, grads)
+        opt.step_with_grads(grads, clip_norm=norm, max_norm=1.0)
+
+    sampler = ClockSampler(0)
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    ctx.kernel_timing(True)
+    launches0 = ctx.launch_count()
+    total_ms = 0.0
+    for _ in range(args.steps):
+        flush.zero_()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        step()
+        ev1.record()
+        torch.cuda.synchronize()
+        total_ms += ev0.elapsed_time(ev1)
+    ms = total_ms / args.steps
+    launches = ctx.launch_count() - launches0
+    k_ms, k_n = ctx.kernel_time(_lib.K_OPTIM)
+    ctx.kernel_timing(False)
+    ctx.sync()
+    clocks = sampler.stop()
+    bytes_step = n_elem * 4.0 * (1 + 7)            # norm pass reads g; step reads w, g, m, v and writes w, m, v
+    peaks = load_peaks()
+    achieved = bytes_step / (k_ms / args.steps * 1e-3) / 1e9
+    # CPU leg: the C restatement over the same tensors (clip + step), all host threads
+    hw = [p.cpu().numpy().reshape(-1).copy() for p in params]
+    hg = [g.cpu().numpy().reshape(-1).copy() for g in glist]
+    hm, hv = [np.zeros_like(w) for w in hw], [np.zeros_like(w) for w in hw]
+    t0 = time.perf_counter()
+    gs = [g.copy() for g in hg]
+    ref.clip_grad_norm(gs, 1.0)
+    for w, g, m, v in zip(hw, gs, hm, hv):
+        ref.adamw_step(w, g, m, v, 1, 6e-4, (0.9, 0.95), 1e-8, 0.1)
+    cpu_s = time.perf_counter() - t0
+    line = {"metric": "adamw_clip_step_params_per_s", "value": n_elem / (ms * 1e-3), "unit": "parameters/s", "n_gpus": 1,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"gradient norm + clip + AdamW over {len(shapes)} tensors, {n_elem} f32 parameters "
+                                   "(the reference's GPT: vocab 50257, n_embd 192, 6 layers)",
+                       "l2": "256 MB flush write between steps (88 MB of state would otherwise stay in L2)"},
+            "gpu_launches": int(launches), "clocks": clocks, "e2e": None,
+            "roofline": {"bound": "hbm", "kernel": "grad_sq_sum_kernel + grad_norm_kernel + adamw_kernel",
+                         "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
+                         "traffic": None, "bytes_per_step": bytes_step, "kernel_ms_per_step": k_ms / args.steps,
+                         "peak_source": peaks["source"] + " copy bandwidth"},
+            "cpu_baseline": {"value": n_elem / cpu_s, "unit": "parameters/s", "cores": ref.num_threads(), "kind": "port",
+                             "sample": f"the whole step once, f32 C restatement of clip_grad_norm + AdamW, {cpu_s:.3f} s"}}
+    print(json.dumps(line))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -265,6 +342,9 @@ def main():
     ap.add_argument("--rope", action="store_true",
                     help="time the fused rotary embedding + head-major pack (q and k, forward and inverse) "
                          "on the workload's shape instead of attention; 1 GPU")
+    ap.add_argument("--adamw", action="store_true",
+                    help="time the fused multi-tensor AdamW step with the gradient-norm clip on the parameter "
+                         "shapes of the reference's GPT (22 M parameters in 38 tensors) instead of attention; 1 GPU")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -275,6 +355,9 @@ def main():
         args.workload = "custom"
     if args.rope:
         run_rope(args, dtype, B, T, H, D)
+        return
+    if args.adamw:
+        run_adamw(args)
         return
     if args.impl == "reference":
         run_reference(args, dtype, B, T, H, D)

@@ -21,8 +21,9 @@ SYMBOLS = [
     "deers_b200_launch_count", "deers_b200_selftest_umma", "deers_b200_kernel_timing",
     "deers_b200_kernel_time", "deers_b200_attn_bwd_f16_static", "deers_b200_attn_host_scratch_bytes",
     "deers_b200_attn_fwd_bwd_host", "deers_b200_rope_pack",
+    "deers_b200_optim_scratch_bytes", "deers_b200_grad_norm", "deers_b200_grad_clip", "deers_b200_adamw_step",
 ]
-K_FWD, K_BWD_PREP, K_BWD_MAIN, K_BWD_DQ, K_ROPE = range(5)
+K_FWD, K_BWD_PREP, K_BWD_MAIN, K_BWD_DQ, K_ROPE, K_OPTIM = range(6)
 
 
 class AttnDesc(ctypes.Structure):
@@ -38,6 +39,16 @@ class RopeDesc(ctypes.Structure):
     _fields_ = [("B", ctypes.c_int32), ("T", ctypes.c_int32), ("H", ctypes.c_int32), ("D", ctypes.c_int32),
                 ("dtype", ctypes.c_int32), ("inverse", ctypes.c_int32),
                 ("src_strides", ctypes.c_int64 * 4), ("dst_strides", ctypes.c_int64 * 4)]
+
+
+class OptimTensor(ctypes.Structure):
+    _fields_ = [("w", ctypes.c_void_p), ("g", ctypes.c_void_p), ("m", ctypes.c_void_p), ("v", ctypes.c_void_p),
+                ("n", ctypes.c_int64)]
+
+
+class AdamWHyper(ctypes.Structure):
+    _fields_ = [("lr", ctypes.c_double), ("beta1", ctypes.c_double), ("beta2", ctypes.c_double),
+                ("eps", ctypes.c_double), ("weight_decay", ctypes.c_double), ("step", ctypes.c_int64)]
 
 
 _lib = None
@@ -77,6 +88,12 @@ def lib() -> ctypes.CDLL:
     L.deers_b200_attn_host_scratch_bytes.restype = sz
     L.deers_b200_attn_fwd_bwd_host.argtypes = [vp, dp] + [vp] * 9 + [i32, vp, sz]
     L.deers_b200_rope_pack.argtypes = [vp, ctypes.POINTER(RopeDesc), vp, vp, vp, vp]
+    tp = ctypes.POINTER(OptimTensor)
+    L.deers_b200_optim_scratch_bytes.argtypes = []
+    L.deers_b200_optim_scratch_bytes.restype = sz
+    L.deers_b200_grad_norm.argtypes = [vp, i32, tp, vp, vp, sz]
+    L.deers_b200_grad_clip.argtypes = [vp, i32, tp, vp, ctypes.c_double]
+    L.deers_b200_adamw_step.argtypes = [vp, i32, tp, ctypes.POINTER(AdamWHyper), vp, ctypes.c_double]
     L.deers_b200_status_string.argtypes = [i32]
     L.deers_b200_status_string.restype = ctypes.c_char_p
     L.deers_b200_last_error.argtypes = [vp]

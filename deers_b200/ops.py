@@ -285,6 +285,9 @@ class GradientStore:
     def get(self, tensor: torch.Tensor) -> Optional[torch.Tensor]:
         return self._grads.get(id(tensor))
 
+    def insert(self, tensor: torch.Tensor, grad: torch.Tensor) -> None:
+        self._grads[id(tensor)] = grad
+
 
 class CausalAttention:
     """The fused op: ``softmax(scale * q @ k^T + causal_mask) @ v`` on ``[B, H, T, D]`` tensors.
@@ -362,3 +365,122 @@ def attention_fwd_bwd_host(q, k, v, d_o, scale: float, causal: bool = True, chun
         lse.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), chunk_slices, scratch.data_ptr(),
         scratch.numel() * scratch.element_size()), ctx.handle)
     return o, dq, dk, dv, lse
+
+
+# ---------------------------------------------------------------------------------------------
+# Optimizer: multi-tensor AdamW with the gradient-norm clip folded in (f32)
+# ---------------------------------------------------------------------------------------------
+def _optim_table(parameters, grads: GradientStore, moments=None):
+    """The C array of deers_optim_tensor for the parameters that have a gradient (optim.rs:221-225
+    skips the others), plus the objects that must stay alive during the call."""
+    rows, keep = [], []
+    for p in parameters:
+        g = grads.get(p)
+        if g is None:
+            continue
+        if p.dtype != torch.float32 or g.dtype != torch.float32:
+            raise DTypeMismatch(f"optimizer: f32 parameters and gradients only, got {p.dtype} / {g.dtype}")
+        if p.device.type != "cuda" or g.device != p.device:
+            raise DeviceMismatch("optimizer: parameters and gradients must live on the CUDA device")
+        if tuple(g.shape) != tuple(p.shape):
+            raise LayoutMismatch(f"optimizer: gradient {tuple(g.shape)} vs parameter {tuple(p.shape)}")
+        if not p.is_contiguous():
+            raise LayoutMismatch("optimizer: parameters must be compact")
+        if not g.is_contiguous():
+            g = g.contiguous()
+            grads.insert(p, g)
+        m, v = moments(p) if moments is not None else (None, None)
+        rows.append((p, g, m, v))
+        keep.extend((p, g, m, v))
+    table = (_lib.OptimTensor * max(len(rows), 1))()
+    for i, (p, g, m, v) in enumerate(rows):
+        table[i].w, table[i].g = p.data_ptr(), g.data_ptr()
+        table[i].m = m.data_ptr() if m is not None else None
+        table[i].v = v.data_ptr() if v is not None else None
+        table[i].n = p.numel()
+    return table, len(rows), keep
+
+
+def grad_norm_device(parameters, grads: GradientStore) -> Optional[torch.Tensor]:
+    """sqrt(sum of squares of every gradient) as a one-element f32 tensor ON THE DEVICE (no host
+    synchronisation): what `AdamW.step_with_grads(..., clip_norm=...)` consumes."""
+    table, n, keep = _optim_table(parameters, grads)
+    if n == 0:
+        return None
+    dev = keep[0].device
+    ctx = Context.current(dev)
+    norm = torch.empty(1, dtype=torch.float32, device=dev)
+    nbytes = int(_lib.lib().deers_b200_optim_scratch_bytes())
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    _lib.check(_lib.lib().deers_b200_grad_norm(ctx.handle, n, table, norm.data_ptr(), scratch.data_ptr(), nbytes),
+               ctx.handle)
+    return norm
+
+
+def clip_grad_norm(parameters, grads: GradientStore, max_norm: float) -> float:
+    """`clip_grad_norm` (src/optim.rs:257-297): clips the global gradient norm to max_norm, scaling the
+    stored gradients in place, and returns the norm before clipping (one host read, like the reference)."""
+    assert max_norm > 0.0, "max_norm must be positive"
+    if len(parameters) == 0:
+        return 0.0
+    norm = grad_norm_device(parameters, grads)
+    if norm is None:
+        return 0.0
+    table, n, keep = _optim_table(parameters, grads)
+    ctx = Context.current(norm.device)
+    _lib.check(_lib.lib().deers_b200_grad_clip(ctx.handle, n, table, norm.data_ptr(), float(max_norm)), ctx.handle)
+    return float(norm.item())
+
+
+class AdamW:
+    """`AdamWConfig::new(lr).betas(..).eps(..).weight_decay(..).build(parameters)` and the optimizer it
+    builds (src/optim.rs:49-251), with every parameter updated by one fused launch.  Parameters are
+    compact f32 CUDA tensors updated in place; moments are created as zeros on first use."""
+
+    def __init__(self, parameters, lr: float, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.0):
+        self.parameters = list(parameters)
+        self._lr, self.betas, self.eps, self.weight_decay = float(lr), (float(betas[0]), float(betas[1])), float(eps), float(weight_decay)
+        self._m: Dict[int, torch.Tensor] = {}
+        self._v: Dict[int, torch.Tensor] = {}
+        self._step = 0
+
+    def set_lr(self, lr: float) -> None:
+        self._lr = float(lr)
+
+    def lr(self) -> float:
+        return self._lr
+
+    def step_count(self) -> int:
+        return self._step
+
+    def set_step_count(self, step: int) -> None:
+        self._step = int(step)
+
+    def state_for(self, parameter):
+        if id(parameter) not in self._m:
+            return None
+        return self._m[id(parameter)], self._v[id(parameter)]
+
+    def load_state_for(self, parameter, m, v) -> None:
+        self._m[id(parameter)], self._v[id(parameter)] = m.detach().contiguous(), v.detach().contiguous()
+
+    def _moments(self, p):
+        if id(p) not in self._m:
+            self._m[id(p)] = torch.zeros_like(p)
+            self._v[id(p)] = torch.zeros_like(p)
+        return self._m[id(p)], self._v[id(p)]
+
+    def step_with_grads(self, grads: GradientStore, clip_norm: Optional[torch.Tensor] = None,
+                        max_norm: float = 0.0) -> None:
+        """One AdamW step (optim.rs:214-251).  With `clip_norm` (the device tensor of
+        `grad_norm_device`) and `max_norm`, the clip of clip_grad_norm is applied to the gradients on
+        the fly inside the same launch, without a host round trip."""
+        self._step += 1
+        table, n, keep = _optim_table(self.parameters, grads, self._moments)
+        if n == 0:
+            return
+        ctx = Context.current(keep[0].device)
+        h = _lib.AdamWHyper(self._lr, self.betas[0], self.betas[1], self.eps, self.weight_decay, self._step)
+        _lib.check(_lib.lib().deers_b200_adamw_step(ctx.handle, n, table, ctypes.byref(h),
+                                                    clip_norm.data_ptr() if clip_norm is not None else None,
+                                                    float(max_norm)), ctx.handle)

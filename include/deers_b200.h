@@ -218,6 +218,53 @@ int deers_b200_rope_pack(deers_ctx* ctx, const deers_rope_desc* desc, const void
                          const void* sin_cache, void* dst);
 
 /*
+ * Multi-tensor AdamW step with the global gradient-norm clip folded in, f32.  Replaces
+ * `AdamW::step_with_grads` (`src/optim.rs:214-251`: about twelve element-wise ops and ten temporaries per
+ * parameter) and `clip_grad_norm` (`src/optim.rs:257-297`: a multiply, a full reduction and an add per
+ * parameter, a host read of the norm, and a scalar multiply per gradient when it clips).
+ *
+ * A parameter is described by device pointers to its weights w, gradient g and moments m, v (n f32
+ * elements each, 4-byte aligned; 16-byte alignment of all of them enables the 16-byte path); moments of
+ * a parameter seen for the first time must be zero (`param.zeros_like()`, `optim.rs:229,233`).  Up to
+ * 256 tensors per call.  Everything is enqueued on the context's stream; nothing allocates or
+ * synchronises.
+ *
+ *   grad_norm   norm_dev[0] = sqrt(sum over all tensors of g*g), f32, summed in a fixed order (the
+ *               reference sums each tensor left to right and adds the tensors in turn, so the last
+ *               bits can differ).  `scratch` is deers_b200_optim_scratch_bytes() of device memory.
+ *   grad_clip   what clip_grad_norm does after it has the norm: nothing if the norm is not finite or
+ *               <= max_norm, else every g *= (f32)(max_norm / ((f64)norm + 1e-6)) in place.  The
+ *               decision is taken on the device from norm_dev.  max_norm must be > 0
+ *               (DEERS_ERR_SHAPE otherwise; the reference asserts).
+ *   adamw_step  m = m*b1 + g*(1-b1);  v = v*b2 + (g*g)*(1-b2);  m_hat = m*(1/(1-b1^t));
+ *               v_hat = v*(1/(1-b2^t));  w = (wd > 0 ? w*(1-lr*wd) : w) - (m_hat/(sqrt(v_hat)+eps))*lr,
+ *               one rounding per operation and each scalar an f64 rounded to f32, exactly as the
+ *               reference's scalar ops do (`src/storage.rs:105-123`), so w, m, v are bit-identical to
+ *               its CPU path.  `hyper->step` is the step count AFTER the increment of
+ *               `optim.rs:215` (t >= 1).  With norm_dev != NULL the clip of grad_clip is applied to
+ *               g on the fly (g itself is left untouched), which removes the host round trip of
+ *               clip_grad_norm from the training step; with NULL the gradients are used as they are.
+ */
+typedef struct deers_optim_tensor {
+    void* w;        /* weights, updated in place (unused by grad_norm / grad_clip) */
+    void* g;        /* gradient; grad_clip scales it in place */
+    void* m;        /* first moment, updated in place */
+    void* v;        /* second moment, updated in place */
+    int64_t n;      /* elements */
+} deers_optim_tensor;
+typedef struct deers_adamw_hyper {
+    double lr, beta1, beta2, eps, weight_decay;   /* AdamWConfig defaults: betas (0.9, 0.999), eps 1e-8, wd 0 */
+    int64_t step;                                 /* t of the bias correction, >= 1 */
+} deers_adamw_hyper;
+size_t deers_b200_optim_scratch_bytes(void);
+int deers_b200_grad_norm(deers_ctx* ctx, int n_tensors, const deers_optim_tensor* tensors, float* norm_dev,
+                         void* scratch, size_t scratch_bytes);
+int deers_b200_grad_clip(deers_ctx* ctx, int n_tensors, const deers_optim_tensor* tensors, const float* norm_dev,
+                         double max_norm);
+int deers_b200_adamw_step(deers_ctx* ctx, int n_tensors, const deers_optim_tensor* tensors,
+                          const deers_adamw_hyper* hyper, const float* norm_dev, double max_norm);
+
+/*
  * Status text, the way backend failures become `Error::Cuda(String)`
  * (`src/error.rs:40-41`).  last_error adds the detail of the most recent failure
  * on this context (CUDA error string, or which kernel wait gave up).
@@ -239,7 +286,7 @@ uint64_t deers_b200_launch_count(deers_ctx* ctx);
  * milliseconds and the number of launches of one kernel kind since timing was
  * enabled (or since the last call with reset != 0).
  */
-enum { DEERS_K_FWD = 0, DEERS_K_BWD_PREP = 1, DEERS_K_BWD_MAIN = 2, DEERS_K_BWD_DQ = 3, DEERS_K_ROPE = 4, DEERS_K_COUNT = 5 };
+enum { DEERS_K_FWD = 0, DEERS_K_BWD_PREP = 1, DEERS_K_BWD_MAIN = 2, DEERS_K_BWD_DQ = 3, DEERS_K_ROPE = 4, DEERS_K_OPTIM = 5, DEERS_K_COUNT = 6 };
 int deers_b200_kernel_timing(deers_ctx* ctx, int enable);
 int deers_b200_kernel_time(deers_ctx* ctx, int kind, int reset, double* total_ms, uint64_t* launches);
 

@@ -212,3 +212,64 @@ void ref_rope_pack(const float* x, const float* cosv, const float* sinv, int B, 
         }
     }
 }
+
+/*
+ * AdamW and clip_grad_norm, f32, op by op as the reference evaluates them on its CPU backend
+ * (paths inside the deers repository):
+ *   src/optim.rs:214-251   step_with_grads: m = m*b1 + g*(1-b1); v = v*b2 + (g*g)*(1-b2);
+ *                          m_hat = m*(1/bc1); v_hat = v*(1/bc2); decayed = w*(1-lr*wd) if wd > 0;
+ *                          update = m_hat / (sqrt(v_hat) + eps); w = decayed - update*lr
+ *   src/storage.rs:105-123 scalar ops cast their f64 operand to f32 (`self.0 as f32`)
+ *   src/optim.rs:257-297   clip_grad_norm: total += sum(g*g) per parameter (left-to-right f32 sum,
+ *                          src/storage/cpu.rs:323-345), norm = sqrt(total)
+ * Products and sums round separately (contraction into FMA disabled).  Pinned by the literal values of
+ * the reference's own test (src/optim.rs:556-570: gradient [3, 4], max_norm 1 -> norm 5, [0.6, 0.8]).
+ */
+static double ref_powi(double a, int b) {      /* f64::powi: exponentiation by squaring */
+    const int recip = b < 0;
+    double r = 1.0;
+    for (;;) {
+        if (b & 1) r *= a;
+        b /= 2;
+        if (b == 0) break;
+        a *= a;
+    }
+    return recip ? 1.0 / r : r;
+}
+
+__attribute__((visibility("default"), optimize("fp-contract=off")))
+void ref_adamw_step(float* w, const float* g, float* m, float* v, long long n, double lr, double beta1, double beta2,
+                    double eps, double weight_decay, int step) {
+    const double bc1 = 1.0 - ref_powi(beta1, step), bc2 = 1.0 - ref_powi(beta2, step);
+    const float b1 = (float)beta1, omb1 = (float)(1.0 - beta1), b2 = (float)beta2, omb2 = (float)(1.0 - beta2);
+    const float ibc1 = (float)(1.0 / bc1), ibc2 = (float)(1.0 / bc2);
+    const float decay = (float)(1.0 - lr * weight_decay), lrf = (float)lr, epsf = (float)eps;
+#pragma omp parallel for schedule(static)
+    for (long long i = 0; i < n; ++i) {
+        const float gi = g[i];
+        const float t1 = m[i] * b1, t2 = gi * omb1;
+        const float mi = t1 + t2;
+        const float gg = gi * gi;
+        const float t3 = v[i] * b2, t4 = gg * omb2;
+        const float vi = t3 + t4;
+        const float m_hat = mi * ibc1, v_hat = vi * ibc2;
+        const float decayed = weight_decay > 0.0 ? w[i] * decay : w[i];
+        const float denom = sqrtf(v_hat) + epsf;
+        const float update = m_hat / denom;
+        const float ul = update * lrf;
+        m[i] = mi;
+        v[i] = vi;
+        w[i] = decayed - ul;
+    }
+}
+
+/* sum over one gradient of g*g: the product tensor first, then a left-to-right f32 sum. */
+__attribute__((visibility("default"), optimize("fp-contract=off")))
+float ref_grad_sq_sum(const float* g, long long n) {
+    float s = 0.0f;
+    for (long long i = 0; i < n; ++i) {
+        const float p = g[i] * g[i];
+        s = (i == 0) ? p : s + p;
+    }
+    return s;
+}

@@ -38,6 +38,10 @@ def lib() -> ctypes.CDLL:
         L.ref_causal_mask.restype = None
         L.ref_attn_fwd.argtypes = [fp, fp, fp] + [ctypes.c_int] * 4 + [ctypes.c_float, ctypes.c_int, fp, fp]
         L.ref_attn_fwd.restype = ctypes.c_int
+        L.ref_adamw_step.argtypes = [fp, fp, fp, fp, ctypes.c_longlong] + [ctypes.c_double] * 5 + [ctypes.c_int]
+        L.ref_adamw_step.restype = None
+        L.ref_grad_sq_sum.argtypes = [fp, ctypes.c_longlong]
+        L.ref_grad_sq_sum.restype = ctypes.c_float
         L.ref_rope_pack.argtypes = [fp, fp, fp] + [ctypes.c_int] * 5 + [fp]
         L.ref_rope_pack.restype = None
         L.ref_attn_fwd_bwd.argtypes = ([fp, fp, fp, fp] + [ctypes.c_int] * 4 +
@@ -146,3 +150,29 @@ def rope_pack_f16(x, cos, sin, inverse: bool = False):
     y2 = a * (s * np.float16(-1.0)) + b * c
     y = np.concatenate([y1, y2], axis=3).astype(np.float16)     # [B,T,H,D]
     return y if inverse else np.ascontiguousarray(np.transpose(y, (0, 2, 1, 3)))
+
+
+def adamw_step(w, g, m, v, step: int, lr: float, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.0):
+    """One AdamW step on one parameter, in place on contiguous f32 arrays w, m, v (optim.rs:214-251)."""
+    for a in (w, g, m, v):
+        assert a.dtype == np.float32 and a.flags.c_contiguous
+    lib().ref_adamw_step(_p(w), _p(g), _p(m), _p(v), w.size, lr, betas[0], betas[1], eps, weight_decay, step)
+
+
+def clip_grad_norm(grads, max_norm: float):
+    """clip_grad_norm (optim.rs:257-297) on a list of contiguous f32 gradient arrays, scaled in place when
+    the norm exceeds max_norm; returns the norm before clipping as a Python float (f32 value)."""
+    assert max_norm > 0.0, "max_norm must be positive"
+    if not grads:
+        return 0.0
+    total = np.float32(0.0)
+    for g in grads:
+        assert g.dtype == np.float32 and g.flags.c_contiguous
+        total = np.float32(total + np.float32(lib().ref_grad_sq_sum(_p(g), g.size)))
+    norm = np.float32(np.sqrt(total))
+    if not np.isfinite(norm) or norm <= np.float32(max_norm):
+        return float(norm)
+    scale = np.float32(max_norm / (float(norm) + 1e-6))
+    for g in grads:
+        g *= scale
+    return float(norm)

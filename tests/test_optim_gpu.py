@@ -1,0 +1,148 @@
+"""GPU parity of the fused multi-tensor AdamW / gradient-norm clip against the CPU oracle, through the C ABI."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+# the parameter shapes of the reference's GPT config (README: 6 layers, n_embd 192, vocab 50257 scaled
+# down here), plus odd sizes that leave the 16-byte path
+SHAPES = [(50, 192), (192, 192), (192, 192), (192, 768), (768, 192), (192,), (7,), (1,), (4099,), (333, 17)]
+
+
+def _make(seed, shapes=SHAPES, gscale=1.0):
+    rng = np.random.default_rng(seed)
+    ws = [rng.standard_normal(s).astype(np.float32) for s in shapes]
+    gs = [(gscale * rng.standard_normal(s)).astype(np.float32) for s in shapes]
+    return ws, gs
+
+
+def _device(ws, gs):
+    from deers_b200 import ops
+    params = [torch.from_numpy(w.copy()).cuda() for w in ws]
+    grads = ops.GradientStore()
+    for p, g in zip(params, gs):
+        grads.insert(p, torch.from_numpy(g.copy()).cuda())
+    return params, grads
+
+
+def test_adamw_steps_are_bit_exact_against_the_oracle():
+    from deers_b200 import ops
+    from oracle import ref
+    ws, _ = _make(0)
+    params, _ = _device(ws, ws)
+    opt = ops.AdamW(params, lr=1e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    host_m = [np.zeros_like(w) for w in ws]
+    host_v = [np.zeros_like(w) for w in ws]
+    for step in range(1, 6):
+        _, gs = _make(100 + step)
+        grads = ops.GradientStore()
+        for p, g in zip(params, gs):
+            grads.insert(p, torch.from_numpy(g).cuda())
+        opt.step_with_grads(grads)
+        for w, g, m, v in zip(ws, gs, host_m, host_v):
+            ref.adamw_step(w.reshape(-1), g.reshape(-1), m.reshape(-1), v.reshape(-1), step, 1e-3, (0.9, 0.95), 1e-8, 0.1)
+    ops.Context.current(params[0].device).sync()
+    assert opt.step_count() == 5
+    for p, w, m, v in zip(params, ws, host_m, host_v):
+        gm, gv = opt.state_for(p)
+        assert np.array_equal(p.cpu().numpy(), w)
+        assert np.array_equal(gm.cpu().numpy(), m) and np.array_equal(gv.cpu().numpy(), v)
+
+
+def test_no_weight_decay_and_missing_gradients():
+    from deers_b200 import ops
+    from oracle import ref
+    ws, gs = _make(3)
+    params, grads = _device(ws, gs)
+    extra = torch.ones(5, device="cuda")                        # a parameter without a gradient is skipped (optim.rs:221-225)
+    opt = ops.AdamW(params + [extra], lr=0.1)
+    opt.step_with_grads(grads)
+    ops.Context.current(extra.device).sync()
+    assert torch.equal(extra, torch.ones(5, device="cuda")) and opt.state_for(extra) is None
+    for p, w, g in zip(params, ws, gs):
+        m, v = np.zeros_like(w), np.zeros_like(w)
+        ref.adamw_step(w.reshape(-1), g.reshape(-1), m.reshape(-1), v.reshape(-1), 1, 0.1)
+        assert np.array_equal(p.cpu().numpy(), w)
+
+
+def test_reference_unit_tests_hold():
+    # src/optim.rs:417-471: x=0 moves toward 3 after one step; weight decay alone shrinks x.
+    from deers_b200 import ops
+    x = torch.zeros(1, device="cuda")
+    opt = ops.AdamW([x], lr=0.1)
+    grads = ops.GradientStore()
+    grads.insert(x, 2.0 * (x - 3.0))
+    opt.step_with_grads(grads)
+    assert x.item() > 0.0 and opt.step_count() == 1
+    y = torch.full((1,), 5.0, device="cuda")
+    opt = ops.AdamW([y], lr=0.1, weight_decay=0.1)
+    grads = ops.GradientStore()
+    grads.insert(y, torch.zeros(1, device="cuda"))
+    opt.step_with_grads(grads)
+    assert y.item() < 5.0
+
+
+def test_clip_grad_norm_known_answer_and_parity():
+    # src/optim.rs:556-570: gradient [3, 4], max_norm 1 -> norm 5, clipped [0.6, 0.8]
+    from deers_b200 import ops
+    from oracle import ref
+    x = torch.zeros(2, device="cuda")
+    grads = ops.GradientStore()
+    grads.insert(x, torch.tensor([3.0, 4.0], device="cuda"))
+    norm = ops.clip_grad_norm([x], grads, 1.0)
+    got = grads.get(x).cpu().numpy()
+    assert abs(norm - 5.0) < 1e-5 and abs(got[0] - 0.6) < 1e-4 and abs(got[1] - 0.8) < 1e-4
+    # many tensors: the norm differs from the left-to-right CPU sum only by f32 summation order
+    ws, gs = _make(5, gscale=3.0)
+    params, grads = _device(ws, gs)
+    host = [g.copy() for g in gs]
+    want = ref.clip_grad_norm([h.reshape(-1) for h in host], 1.0)
+    norm = ops.clip_grad_norm(params, grads, 1.0)
+    assert abs(norm - want) <= 2e-6 * want
+    for p, h in zip(params, host):
+        got = grads.get(p).cpu().numpy()
+        assert np.abs(got - h).max() <= 4e-6 * np.abs(h).max()
+    # below the threshold nothing changes, bit for bit
+    params, grads = _device(ws, gs)
+    norm = ops.clip_grad_norm(params, grads, 1e9)
+    for p, g in zip(params, gs):
+        assert np.array_equal(grads.get(p).cpu().numpy(), g)
+
+
+def test_fused_clip_inside_the_step_matches_clip_then_step():
+    from deers_b200 import ops
+    ws, gs = _make(8, gscale=5.0)
+    pa, ga = _device(ws, gs)
+    pb, gb = _device(ws, gs)
+    oa, ob = ops.AdamW(pa, lr=1e-2, weight_decay=0.01), ops.AdamW(pb, lr=1e-2, weight_decay=0.01)
+    ops.clip_grad_norm(pa, ga, 1.0)                       # the reference's order: clip (host read), then step
+    oa.step_with_grads(ga)
+    norm = ops.grad_norm_device(pb, gb)                   # fused: the norm never leaves the device
+    ob.step_with_grads(gb, clip_norm=norm, max_norm=1.0)
+    ops.Context.current(pa[0].device).sync()
+    for a, b, g in zip(pa, pb, gs):
+        assert torch.equal(a, b)
+        assert np.array_equal(gb.get(b).cpu().numpy(), g)   # the fused path leaves the stored gradients alone
+
+
+def test_full_model_sized_step():
+    # 22 M parameters in 38 tensors (the reference's GPT): sampled tensors bit-exact, the rest finite.
+    from deers_b200 import ops
+    from oracle import ref
+    shapes = [(50257, 192)] + [(192, 192)] * 4 * 6 + [(192, 768), (768, 192)] * 6 + [(50257, 192)]
+    g = torch.Generator(device="cuda").manual_seed(1)
+    params = [torch.randn(s, device="cuda", generator=g) for s in shapes]
+    before = [p.cpu().numpy().copy() for p in params[:3]]
+    grads = ops.GradientStore()
+    gl = [torch.randn(s, device="cuda", generator=g) for s in shapes]
+    for p, gr in zip(params, gl):
+        grads.insert(p, gr)
+    opt = ops.AdamW(params, lr=6e-4, betas=(0.9, 0.95), weight_decay=0.1)
+    opt.step_with_grads(grads)
+    ops.Context.current(params[0].device).sync()
+    for p, w, gr in zip(params[:3], before, gl[:3]):
+        m, v = np.zeros_like(w), np.zeros_like(w)
+        ref.adamw_step(w.reshape(-1), gr.cpu().numpy().reshape(-1), m.reshape(-1), v.reshape(-1), 1, 6e-4, (0.9, 0.95), 1e-8, 0.1)
+        assert np.array_equal(p.cpu().numpy(), w)
+    assert all(torch.isfinite(p).all().item() for p in params)

@@ -119,3 +119,36 @@ def test_rope_oracle_op_order_and_f16_emulation():
     assert np.abs(back - x).max() < 1e-6
     y16 = ref.rope_pack_f16(x, cos, sin)
     assert y16.dtype == np.float16 and np.abs(y16.astype(np.float32) - ref.rope_pack(x, cos, sin)).max() < 1e-2
+
+
+def test_clip_grad_norm_oracle_known_answer():
+    # Literal values of the reference's own test (src/optim.rs:556-570).
+    g = [np.array([3.0, 4.0], np.float32)]
+    norm = ref.clip_grad_norm(g, 1.0)
+    assert abs(norm - 5.0) < 1e-5 and abs(g[0][0] - 0.6) < 1e-4 and abs(g[0][1] - 0.8) < 1e-4
+    g = [np.array([0.3, 0.4], np.float32)]
+    assert abs(ref.clip_grad_norm(g, 1.0) - 0.5) < 1e-6 and g[0].tolist() == [np.float32(0.3), np.float32(0.4)]
+
+
+def test_adamw_oracle_op_order_and_reference_unit_tests():
+    rng = np.random.default_rng(0)
+    n = 1000
+    w, g = rng.standard_normal(n).astype(np.float32), rng.standard_normal(n).astype(np.float32)
+    m, v = (0.1 * rng.standard_normal(n)).astype(np.float32), (0.01 * np.abs(rng.standard_normal(n))).astype(np.float32)
+    w2, m2, v2 = w.copy(), m.copy(), v.copy()
+    ref.adamw_step(w2, g, m2, v2, 7, 1e-3, (0.9, 0.95), 1e-8, 0.1)
+    f = np.float32                                           # numpy f32: one rounding per op, like the reference
+    mm = m * f(0.9) + g * f(1 - 0.9)
+    vv = v * f(0.95) + (g * g) * f(1 - 0.95)
+    mh, vh = mm * f(1 / (1 - 0.9 ** 7)), vv * f(1 / (1 - 0.95 ** 7))
+    ww = w * f(1 - 1e-3 * 0.1) - (mh / (np.sqrt(vh) + f(1e-8))) * f(1e-3)
+    assert np.array_equal(mm, m2) and np.array_equal(vv, v2) and np.array_equal(ww, w2)
+    # src/optim.rs:417-432: minimise (x-3)^2 from x = 0 with lr 0.1: x moves toward 3
+    x, mx, vx = np.zeros(1, np.float32), np.zeros(1, np.float32), np.zeros(1, np.float32)
+    ref.adamw_step(x, np.array([-6.0], np.float32), mx, vx, 1, 0.1)
+    assert x[0] > 0.0
+    # src/optim.rs:535-553: x^2 + y^2 converges to the origin in 100 steps
+    p, pm, pv = np.array([5.0, -3.0], np.float32), np.zeros(2, np.float32), np.zeros(2, np.float32)
+    for step in range(1, 101):
+        ref.adamw_step(p, (2 * p).astype(np.float32), pm, pv, step, 0.1)
+    assert np.abs(p).max() < 0.1
