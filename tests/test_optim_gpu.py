@@ -99,10 +99,15 @@ def test_clip_grad_norm_known_answer_and_parity():
     host = [g.copy() for g in gs]
     want = ref.clip_grad_norm([h.reshape(-1) for h in host], 1.0)
     norm = ops.clip_grad_norm(params, grads, 1.0)
-    assert abs(norm - want) <= 2e-6 * want
+    # The reference sums 450 k squares left to right in f32 (relative error up to ~n * 2^-24); the device
+    # sums in a tree.  Against the exact value the device norm is tight; against the oracle it is within
+    # the oracle's own summation error.
+    exact = float(np.sqrt(sum(float(np.sum(g.astype(np.float64) ** 2)) for g in gs)))
+    assert abs(norm - exact) <= 1e-6 * exact
+    assert abs(norm - want) <= 1e-4 * want
     for p, h in zip(params, host):
         got = grads.get(p).cpu().numpy()
-        assert np.abs(got - h).max() <= 4e-6 * np.abs(h).max()
+        assert np.abs(got - h).max() <= 1e-4 * np.abs(h).max()
     # below the threshold nothing changes, bit for bit
     params, grads = _device(ws, gs)
     norm = ops.clip_grad_norm(params, grads, 1e9)
