@@ -22,8 +22,9 @@ SYMBOLS = [
     "deers_b200_kernel_time", "deers_b200_attn_bwd_f16_static", "deers_b200_attn_host_scratch_bytes",
     "deers_b200_attn_fwd_bwd_host", "deers_b200_rope_pack",
     "deers_b200_optim_scratch_bytes", "deers_b200_grad_norm", "deers_b200_grad_clip", "deers_b200_adamw_step",
+    "deers_b200_rmsnorm_fwd", "deers_b200_rmsnorm_bwd",
 ]
-K_FWD, K_BWD_PREP, K_BWD_MAIN, K_BWD_DQ, K_ROPE, K_OPTIM = range(6)
+K_FWD, K_BWD_PREP, K_BWD_MAIN, K_BWD_DQ, K_ROPE, K_OPTIM, K_NORM = range(7)
 
 
 class AttnDesc(ctypes.Structure):
@@ -94,6 +95,8 @@ def lib() -> ctypes.CDLL:
     L.deers_b200_grad_norm.argtypes = [vp, i32, tp, vp, vp, sz]
     L.deers_b200_grad_clip.argtypes = [vp, i32, tp, vp, ctypes.c_double]
     L.deers_b200_adamw_step.argtypes = [vp, i32, tp, ctypes.POINTER(AdamWHyper), vp, ctypes.c_double]
+    L.deers_b200_rmsnorm_fwd.argtypes = [vp, ctypes.c_int64, ctypes.c_int32, ctypes.c_double, vp, vp, vp]
+    L.deers_b200_rmsnorm_bwd.argtypes = [vp, ctypes.c_int64, ctypes.c_int32, vp, vp, vp, vp]
     L.deers_b200_status_string.argtypes = [i32]
     L.deers_b200_status_string.restype = ctypes.c_char_p
     L.deers_b200_last_error.argtypes = [vp]

@@ -484,3 +484,62 @@ class AdamW:
         _lib.check(_lib.lib().deers_b200_adamw_step(ctx.handle, n, table, ctypes.byref(h),
                                                     clip_norm.data_ptr() if clip_norm is not None else None,
                                                     float(max_norm)), ctx.handle)
+
+
+# ---------------------------------------------------------------------------------------------
+# RMSNorm (f32), one fused launch each way
+# ---------------------------------------------------------------------------------------------
+class RMSNorm:
+    """`RMSNorm::forward` (src/nn.rs:244-251) as one op with the TensorOp life cycle: ``new`` validates,
+    ``forward`` returns y and keeps the per-row inverse norm for ``backward``."""
+
+    def __init__(self, x, eps: float):
+        self.x, self.eps = x, float(eps)
+        self.inv: Optional[torch.Tensor] = None
+
+    @classmethod
+    def new(cls, x, eps: float) -> "RMSNorm":
+        if x.dim() < 1:
+            raise LayoutMismatch("RMSNorm: needs at least one axis")
+        if x.dtype != torch.float32:
+            raise DTypeMismatch(f"RMSNorm: f32 only, got {x.dtype}")
+        if x.device.type != "cuda":
+            raise DeviceMismatch("RMSNorm: the fused op runs on the CUDA device only")
+        return cls(x if x.is_contiguous() else x.contiguous(), eps)
+
+    def forward(self) -> torch.Tensor:
+        C = self.x.shape[-1]
+        rows = self.x.numel() // C
+        ctx = Context.current(self.x.device)
+        y = torch.empty_like(self.x)
+        self.inv = torch.empty(max(rows, 1), dtype=torch.float32, device=self.x.device)
+        _lib.check(_lib.lib().deers_b200_rmsnorm_fwd(ctx.handle, rows, C, self.eps, self.x.data_ptr(), y.data_ptr(),
+                                                     self.inv.data_ptr()), ctx.handle)
+        return y
+
+    def backward(self, grads: GradientStore, out_grad: torch.Tensor) -> None:
+        if self.inv is None:
+            raise RuntimeError("RMSNorm.backward before forward")
+        if tuple(out_grad.shape) != tuple(self.x.shape):
+            raise LayoutMismatch(f"RMSNorm.backward: gradient {tuple(out_grad.shape)} vs {tuple(self.x.shape)}")
+        if out_grad.dtype != torch.float32:
+            raise DTypeMismatch(f"RMSNorm.backward: {out_grad.dtype}")
+        g = out_grad if out_grad.is_contiguous() else out_grad.contiguous()
+        C = self.x.shape[-1]
+        rows = self.x.numel() // C
+        ctx = Context.current(self.x.device)
+        dx = torch.empty_like(self.x)
+        _lib.check(_lib.lib().deers_b200_rmsnorm_bwd(ctx.handle, rows, C, self.x.data_ptr(), self.inv.data_ptr(),
+                                                     g.data_ptr(), dx.data_ptr()), ctx.handle)
+        grads.accumulate(self.x, dx)
+
+    def dependencies(self) -> List[torch.Tensor]:
+        return [self.x]
+
+    def name(self) -> str:
+        return "RMSNorm"
+
+
+def rms_norm(x, eps: float) -> torch.Tensor:
+    """Module form: RMSNorm.new(x, eps).forward()."""
+    return RMSNorm.new(x, eps).forward()

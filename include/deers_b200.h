@@ -265,6 +265,21 @@ int deers_b200_adamw_step(deers_ctx* ctx, int n_tensors, const deers_optim_tenso
                           const deers_adamw_hyper* hyper, const float* norm_dev, double max_norm);
 
 /*
+ * RMSNorm forward and backward over the last axis of a compact [rows, C] f32 tensor.  Replaces
+ * `RMSNorm::forward` (`src/nn.rs:244-251`: x*x, mean over the last axis, + eps, ^-0.5, broadcast
+ * multiply — six graph ops) and the autograd backward of those ops (`src/ops.rs:210-214,638-643,675-679,
+ * 777-799`).  fwd writes y = x * inv and inv_norm[row] = 1/sqrt(mean(x*x) + eps) (rows floats the caller
+ * keeps for the backward, the way the attention op keeps its row lse); bwd writes
+ * dx = dy*inv - x * (sum(dy*x) * inv^3 / C).  eps is the module's f64 rounded to f32 (`storage.rs:105-123`).
+ * Row sums are f32 shuffle trees, the reference's are left-to-right f32 sums: parity is to rounding
+ * (1e-5 of the tensor's max-abs), not to the bit.  Enqueued on the context's stream; no allocation.
+ */
+int deers_b200_rmsnorm_fwd(deers_ctx* ctx, int64_t rows, int32_t C, double eps, const float* x, float* y,
+                           float* inv_norm);
+int deers_b200_rmsnorm_bwd(deers_ctx* ctx, int64_t rows, int32_t C, const float* x, const float* inv_norm,
+                           const float* dy, float* dx);
+
+/*
  * Status text, the way backend failures become `Error::Cuda(String)`
  * (`src/error.rs:40-41`).  last_error adds the detail of the most recent failure
  * on this context (CUDA error string, or which kernel wait gave up).
@@ -286,7 +301,7 @@ uint64_t deers_b200_launch_count(deers_ctx* ctx);
  * milliseconds and the number of launches of one kernel kind since timing was
  * enabled (or since the last call with reset != 0).
  */
-enum { DEERS_K_FWD = 0, DEERS_K_BWD_PREP = 1, DEERS_K_BWD_MAIN = 2, DEERS_K_BWD_DQ = 3, DEERS_K_ROPE = 4, DEERS_K_OPTIM = 5, DEERS_K_COUNT = 6 };
+enum { DEERS_K_FWD = 0, DEERS_K_BWD_PREP = 1, DEERS_K_BWD_MAIN = 2, DEERS_K_BWD_DQ = 3, DEERS_K_ROPE = 4, DEERS_K_OPTIM = 5, DEERS_K_NORM = 6, DEERS_K_COUNT = 7 };
 int deers_b200_kernel_timing(deers_ctx* ctx, int enable);
 int deers_b200_kernel_time(deers_ctx* ctx, int kind, int reset, double* total_ms, uint64_t* launches);
 

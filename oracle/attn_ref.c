@@ -273,3 +273,41 @@ float ref_grad_sq_sum(const float* g, long long n) {
     }
     return s;
 }
+
+/*
+ * RMSNorm forward and backward, f32, op by op as the reference graph evaluates it (paths inside the
+ * deers repository):
+ *   src/nn.rs:244-251        mean_sq = (x*x).mean([last], keep); inv = (mean_sq + eps)^-0.5; y = x * inv
+ *   src/tensor.rs:461-465    mean = sum * (1.0 / n as f64), the scalar cast to f32 (storage.rs:105-123)
+ *   src/storage/cpu.rs:323-345  sum: left-to-right f32
+ *   src/ops.rs:675-679       scalar power backward: g * e * arg^(e-1)
+ *   src/ops.rs:210-214 (multiply backward), 777-799 (broadcast backward: sum over the broadcast axis),
+ *   638-643 (scalar multiply backward), src/backprop.rs:101-112 (contributions to x are added as they
+ *   arrive; this restatement adds the broadcast-multiply term first, then the two x*x terms)
+ * No stored reference vector exists for RMSNorm (tests/nn.rs compares with candle at run time): unpinned,
+ * cross-checked against float64 autograd (tests/golden/make_golden.py).
+ */
+__attribute__((visibility("default"), optimize("fp-contract=off")))
+void ref_rmsnorm(const float* x, long long rows, int C, double eps, const float* dy, float* y, float* dx) {
+    const float inv_n = (float)(1.0 / (double)C), epsf = (float)eps;
+#pragma omp parallel for schedule(static)
+    for (long long r = 0; r < rows; ++r) {
+        const float* xr = x + r * C;
+        float s = 0.0f;
+        for (int c = 0; c < C; ++c) { const float p = xr[c] * xr[c]; s = c == 0 ? p : s + p; }
+        const float a = s * inv_n + epsf;
+        const float inv = powf(a, -0.5f);
+        if (y) for (int c = 0; c < C; ++c) y[r * C + c] = xr[c] * inv;
+        if (dy && dx) {
+            const float* g = dy + r * C;
+            float dinv = 0.0f;
+            for (int c = 0; c < C; ++c) { const float p = g[c] * xr[c]; dinv = c == 0 ? p : dinv + p; }
+            const float da = (dinv * -0.5f) * powf(a, -1.5f);
+            const float ds = da * inv_n;
+            for (int c = 0; c < C; ++c) {
+                const float t1 = g[c] * inv, t2 = ds * xr[c];
+                dx[r * C + c] = (t1 + t2) + t2;
+            }
+        }
+    }
+}

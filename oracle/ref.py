@@ -42,6 +42,8 @@ def lib() -> ctypes.CDLL:
         L.ref_adamw_step.restype = None
         L.ref_grad_sq_sum.argtypes = [fp, ctypes.c_longlong]
         L.ref_grad_sq_sum.restype = ctypes.c_float
+        L.ref_rmsnorm.argtypes = [fp, ctypes.c_longlong, ctypes.c_int, ctypes.c_double, fp, fp, fp]
+        L.ref_rmsnorm.restype = None
         L.ref_rope_pack.argtypes = [fp, fp, fp] + [ctypes.c_int] * 5 + [fp]
         L.ref_rope_pack.restype = None
         L.ref_attn_fwd_bwd.argtypes = ([fp, fp, fp, fp] + [ctypes.c_int] * 4 +
@@ -176,3 +178,18 @@ def clip_grad_norm(grads, max_norm: float):
     for g in grads:
         g *= scale
     return float(norm)
+
+
+def rmsnorm(x, eps: float, dy=None):
+    """RMSNorm over the last axis of a contiguous f32 array (nn.rs:244-251); returns y, or (y, dx) with dy."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    C = x.shape[-1]
+    rows = x.size // C
+    y = np.empty_like(x)
+    if dy is None:
+        lib().ref_rmsnorm(_p(x), rows, C, eps, None, _p(y), None)
+        return y
+    dy = np.ascontiguousarray(dy, dtype=np.float32)
+    dx = np.empty_like(x)
+    lib().ref_rmsnorm(_p(x), rows, C, eps, _p(dy), _p(y), _p(dx))
+    return y, dx

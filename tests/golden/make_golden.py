@@ -1,4 +1,4 @@
-"""Generates tests/golden/attn_golden.npz and tests/golden/rope_golden.npz.
+"""Generates tests/golden/attn_golden.npz, tests/golden/rope_golden.npz and tests/golden/rmsnorm_golden.npz.
 
 The reference (deers) is Rust and cannot run in the build image, and its own
 attention test computes expected values with candle at test time, so there is no
@@ -79,7 +79,29 @@ def run_rope(B, T, H, D, seed):
     return res
 
 
+NORM_CASES = {"gpt_rows": (8, 192, 1e-6), "odd_C7": (5, 7, 1e-5), "wide_C1024": (3, 1024, 1e-6), "C1": (4, 1, 1e-6)}
+
+
+def run_rmsnorm(rows, C, eps, seed):
+    """RMSNorm (src/nn.rs:244-251) and its gradient as float64 torch autograd over the reference's op chain."""
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(rows, C, generator=g, dtype=torch.float32)
+    dy = torch.randn(rows, C, generator=g, dtype=torch.float32)
+    x64 = x.double().requires_grad_(True)
+    y = x64 * ((x64 * x64).mean(1, keepdim=True) + eps).pow(-0.5)
+    y.backward(dy.double())
+    return dict(x=x.numpy(), dy=dy.numpy(), y=y.detach().float().numpy(), dx=x64.grad.float().numpy(),
+                eps=np.array(eps))
+
+
 def main():
+    nblob = {}
+    for idx, (name, (rows, C, eps)) in enumerate(NORM_CASES.items()):
+        for key, arr in run_rmsnorm(rows, C, eps, 3000 + idx).items():
+            nblob[f"{name}/{key}"] = arr
+    npath = os.path.join(os.path.dirname(os.path.abspath(__file__)), "rmsnorm_golden.npz")
+    np.savez_compressed(npath, **nblob)
+    print(npath, os.path.getsize(npath), "bytes")
     rblob = {}
     for idx, (name, (B, T, H, D)) in enumerate(ROPE_CASES.items()):
         for key, arr in run_rope(B, T, H, D, 2000 + idx).items():

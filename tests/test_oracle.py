@@ -152,3 +152,24 @@ def test_adamw_oracle_op_order_and_reference_unit_tests():
     for step in range(1, 101):
         ref.adamw_step(p, (2 * p).astype(np.float32), pm, pv, step, 0.1)
     assert np.abs(p).max() < 0.1
+
+
+def _npz(name):
+    import os
+    blob = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", name))
+    cases = {}
+    for key in blob.files:
+        case, field = key.split("/")
+        cases.setdefault(case, {})[field] = blob[key]
+    return cases
+
+
+def test_rmsnorm_oracle_matches_golden():
+    for name, c in _npz("rmsnorm_golden.npz").items():
+        y, dx = ref.rmsnorm(c["x"], float(c["eps"]), c["dy"])
+        assert_close(y, c["y"], 1e-5, f"{name}/y")
+        # at C = 1 the gradient cancels to ~eps: an absolute floor stands in for the missing scale
+        assert np.abs(dx - c["dx"]).max() <= 1e-5 * np.abs(c["dx"]).max() + 1e-6, name
+        # every output row has mean square 1 (up to eps)
+        if c["x"].shape[1] > 1:
+            assert np.allclose((y.astype(np.float64) ** 2).mean(1), 1.0, atol=1e-3)
