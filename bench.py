@@ -246,6 +246,74 @@ def run_rope(args, dtype, B, T, H, D):
     print(json.dumps(line))
 
 
+def run_rmsnorm(args, B, T, H, D):
+    """RMSNorm forward + backward over [B*T, H*D] f32 (src/nn.rs:244-251): 8 + 12 bytes per element."""
+    import numpy as np
+    import torch
+    from deers_b200 import _lib, ops
+    from oracle import ref
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a B200: there is no CPU fallback")
+    dev = torch.device("cuda", 0)
+    rows, C = B * T, H * D
+    gen = torch.Generator(device=dev).manual_seed(77)
+    x = torch.randn(rows, C, device=dev, generator=gen)
+    dy = torch.randn(rows, C, device=dev, generator=gen)
+    ctx = ops.Context.current(dev)
+    small = rows * C * 4 < 126e6
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if small else None
+
+    def step():
+        op = ops.RMSNorm.new(x, 1e-6)
+        op.forward()
+        op.backward(ops.GradientStore(), dy)
+
+    sampler = ClockSampler(0)
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    ctx.kernel_timing(True)
+    launches0 = ctx.launch_count()
+    total_ms = 0.0
+    for _ in range(args.steps):
+        if flush is not None:
+            flush.zero_()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        step()
+        ev1.record()
+        torch.cuda.synchronize()
+        total_ms += ev0.elapsed_time(ev1)
+    ms = total_ms / args.steps
+    launches = ctx.launch_count() - launches0
+    k_ms, k_n = ctx.kernel_time(_lib.K_NORM)
+    ctx.kernel_timing(False)
+    ctx.sync()
+    clocks = sampler.stop()
+    bytes_step = rows * C * 4.0 * 5 + rows * 4.0 * 2
+    peaks = load_peaks()
+    achieved = bytes_step / (k_ms / args.steps * 1e-3) / 1e9
+    sr = max(1, min(rows, int(5e7 // C)))
+    xs = np.random.default_rng(0).standard_normal((sr, C)).astype(np.float32)
+    ref.rmsnorm(xs, 1e-6, xs)
+    t0 = time.perf_counter()
+    ref.rmsnorm(xs, 1e-6, xs)
+    cpu_s = time.perf_counter() - t0
+    line = {"metric": "rmsnorm_fwd_bwd_gbs", "value": bytes_step / (ms * 1e-3) / 1e9, "unit": "GB/s", "n_gpus": 1,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"{args.workload}: RMSNorm forward + backward, f32, rows={rows} C={C}",
+                       "l2": "256 MB flush write between steps" if small else "tensors larger than L2"},
+            "gpu_launches": int(launches), "clocks": clocks, "e2e": None,
+            "roofline": {"bound": "hbm", "kernel": "rmsnorm_kernel (forward + backward)", "achieved": achieved,
+                         "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "traffic": None,
+                         "bytes_per_step": bytes_step, "kernel_ms_per_step": k_ms / args.steps,
+                         "peak_source": peaks["source"] + " copy bandwidth"},
+            "cpu_baseline": {"value": sr * C * 4.0 * 5 / cpu_s / 1e9, "unit": "GB/s", "cores": ref.num_threads(),
+                             "kind": "port", "sample": f"{sr} of {rows} rows, f32 C restatement, {cpu_s:.3f} s"}}
+    print(json.dumps(line))
+
+
 def run_adamw(args):
     """One optimizer step of the reference's training loop: gradient norm, clip, AdamW over every parameter
     (src/optim.rs:214-297), fused into three kinds of launches."""
@@ -342,6 +410,8 @@ def main():
     ap.add_argument("--rope", action="store_true",
                     help="time the fused rotary embedding + head-major pack (q and k, forward and inverse) "
                          "on the workload's shape instead of attention; 1 GPU")
+    ap.add_argument("--rmsnorm", action="store_true",
+                    help="time the fused RMSNorm forward + backward on [B*T, H*D] f32 rows of the workload; 1 GPU")
     ap.add_argument("--adamw", action="store_true",
                     help="time the fused multi-tensor AdamW step with the gradient-norm clip on the parameter "
                          "shapes of the reference's GPT (22 M parameters in 38 tensors) instead of attention; 1 GPU")
@@ -358,6 +428,9 @@ def main():
         return
     if args.adamw:
         run_adamw(args)
+        return
+    if args.rmsnorm:
+        run_rmsnorm(args, B, T, H, D)
         return
     if args.impl == "reference":
         run_reference(args, dtype, B, T, H, D)
