@@ -5,19 +5,19 @@
 // each) at or left of its diagonal.  The whole list is treated as ONE stream of (item, KV tile)
 // steps, so loads and the S product run two steps ahead across item boundaries.
 //   warp 0      TMA producer: Q per item (2 buffers), K and V tiles through 2-stage rings
-//   warp 10     issues the S = Q K^T products into a double-buffered TMEM tile, two steps ahead
+//   last warp   issues the S = Q K^T products into a double-buffered TMEM tile, two steps ahead
 //   warp 1      issues the O += P V products, with P read from TMEM and the accumulator resident
 //               in TMEM (two O accumulators alternate between items).  One thread cannot issue
 //               both streams fast enough: its barrier waits and commits between the batches of
 //               eight instructions left the tensor core idle a third of the time.  The two
 //               streams are ordered by barriers only (S of step g+2 overwrites P of step g once
 //               the product that read it has completed).
-//   warps 2-9   two softmax warpgroups that split the 128 key columns of a step; thread r of a
-//               warpgroup owns query row r (= TMEM lane r).  Per step a thread reads its 64
-//               scores, exchanges its partial row max with the twin thread of the other
-//               warpgroup, keeps the running max / partial sum, stores P (f16 pairs) back into
-//               TMEM over the scores it has just read, and rescales its half of O only when the
-//               row max grew by more than 2^8.  At the end of an item the two partial sums are
+//   warps 2-17  four softmax warpgroups that split the 128 key columns of a step (32 each); thread r
+//               of a warpgroup owns query row r (= TMEM lane r).  Per step a thread reads its 32
+//               scores, exchanges its partial row max with the twin threads of the other
+//               warpgroups, keeps the running max / partial sum, stores P (f16 pairs) back into
+//               TMEM over the scores it has just read, and rescales its quarter of O only when the
+//               row max grew by more than 2^8.  At the end of an item the partial sums are
 //               combined, O is normalised and O and the row lse are stored.
 // Scale, causal mask, softmax and both products happen in this one pass; the T x T scores
 // never reach global memory.
@@ -58,6 +58,15 @@ constexpr uint32_t BLOCK_BYTES = 128 * 128;   // one 64-column block of a 128-ro
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
 constexpr float RESCALE_THRESHOLD = 8.0f;     // log2 units: P stays below 2^8, safe in f16
+// Softmax warpgroups per CTA.  Four (32 key columns each) rather than two: the softmax threads are bound by
+// instruction latency, not by any one pipe, and four resident warps per scheduler hide it better than two.
+#ifndef DEERS_FWD_NWG
+#define DEERS_FWD_NWG 4
+#endif
+constexpr int NWG = DEERS_FWD_NWG;
+constexpr int CW = 128 / NWG;                 // key columns of a step per warpgroup
+constexpr int FWD_THREADS = 32 * (2 + 4 * NWG + 1);
+constexpr int S_WARP = 2 + 4 * NWG;           // the warp that issues S
 
 struct FwdParams {
     __half* o;
@@ -84,9 +93,9 @@ struct FwdSmem {
     static constexpr uint32_t Q = 0;                         // two buffers (alternate between items)
     static constexpr uint32_t K = Q + 2 * TILE;              // two stages
     static constexpr uint32_t V = K + 2 * TILE;              // two stages
-    static constexpr uint32_t XCH = V + 2 * TILE;            // [2 parities][2 warpgroups][128] partial row max
-    static constexpr uint32_t LX = XCH + 2 * 2 * BM * 4;     // [2 parities][2 warpgroups][128] partial row sum
-    static constexpr uint32_t BARS = LX + 2 * 2 * BM * 4;
+    static constexpr uint32_t XCH = V + 2 * TILE;            // [2 parities][NWG warpgroups][128] partial row max
+    static constexpr uint32_t LX = XCH + 2 * NWG * BM * 4;   // [2 parities][NWG warpgroups][128] partial row sum
+    static constexpr uint32_t BARS = LX + 2 * NWG * BM * 4;
     static constexpr uint32_t TOTAL = BARS + 256;
 };
 
@@ -135,13 +144,13 @@ struct WorkCursor {
 };
 
 template <int D>
-__global__ void __launch_bounds__(352, 1)
+__global__ void __launch_bounds__(FWD_THREADS, 1)
 attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                     const __grid_constant__ CUtensorMap tmap_v, const FwdParams p) {
     using L = FwdSmem<D>;
     constexpr uint32_t TILE_BYTES = L::TILE;
     constexpr int DBLK = D / 64;
-    constexpr int DH = D / 2;                                // O columns per softmax warpgroup
+    constexpr int DH = D / NWG;                              // O columns per softmax warpgroup
     constexpr uint32_t TMEM_COLS = 512;
     // S of even steps (P in place) | S of odd steps | O of even items | O of odd items
     constexpr uint32_t TM_S = 0, TM_O = 256;
@@ -174,11 +183,11 @@ attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             mbar_init(&bars[F_K_FULL + s], 1);
             mbar_init(&bars[F_V_FULL + s], 1); mbar_init(&bars[F_PV_DONE + s], 1);
             mbar_init(&bars[F_S_FULL + s], 1);
-            mbar_init(&bars[F_P_FULL + s], 256);
-            mbar_init(&bars[F_O_DONE + s], 1); mbar_init(&bars[F_O_FREE + s], 256);
+            mbar_init(&bars[F_P_FULL + s], 128 * NWG);
+            mbar_init(&bars[F_O_DONE + s], 1); mbar_init(&bars[F_O_FREE + s], 128 * NWG);
         }
-        mbar_init(&bars[F_XCH], 256);
-        mbar_init(&bars[F_LX], 256);
+        mbar_init(&bars[F_XCH], 128 * NWG);
+        mbar_init(&bars[F_LX], 128 * NWG);
         fence_barrier_init();
         tma_prefetch_desc(&tmap_q); tma_prefetch_desc(&tmap_k); tma_prefetch_desc(&tmap_v);
     }
@@ -248,7 +257,7 @@ attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 const uint32_t p_tmem = tmem + TM_S + st * 128u;       // P sits where this step's S was
 #pragma unroll
                 for (int ks = 0; ks < BN / 16; ++ks)
-                    umma_ts(o_tmem, p_tmem + (uint32_t)(ks >> 2) * 64u + (uint32_t)(ks & 3) * 8u, v_mn + mnmajor_step(ks),
+                    umma_ts(o_tmem, p_tmem + (uint32_t)(ks / (CW / 16)) * CW + (uint32_t)(ks % (CW / 16)) * 8u, v_mn + mnmajor_step(ks),
                             IDESC_O, (pc.j > 0 || ks > 0));
                 umma_commit(&bars[F_PV_DONE + st]);
                 FWD_TRACE(0, gp, 2);
@@ -257,7 +266,7 @@ attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 FWD_TRACE(0, gp, 3);
             }
         }
-    } else if (warp == 10) {
+    } else if (warp == S_WARP) {
         // ------------------------------ S issuer ------------------------------
         if (lane == 0) {
             constexpr uint32_t IDESC_S = idesc_f16(BM, BN, 0, 0);      // S: K-major A (Q) and B (K)
@@ -287,9 +296,9 @@ attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 sc.advance(p, nq, n_items);
             }
         }
-    } else if (warp < 10) {
+    } else if (warp < S_WARP) {
         // ------------------------------ softmax + epilogue ------------------------------
-        const int g = (warp - 2) >> 2;                          // warpgroup: key columns [64g, 64g+64)
+        const int g = (warp - 2) >> 2;                          // warpgroup: key columns [CW*g, CW*g + CW)
         const int lane_base = (warp & 3) * 32;
         const int row = lane_base + lane;                       // row inside the query tile == TMEM lane
         const uint32_t t_lane = (uint32_t)lane_base << 16;
@@ -304,13 +313,15 @@ attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             if (pend_n < 0) return true;
             const int n = pend_n;
             pend_n = -1;
-            // Combine the two partial row sums.
-            float* lxp = lx + (n & 1) * 2 * BM;
+            // Combine the partial row sums of the warpgroups.
+            float* lxp = lx + (n & 1) * NWG * BM;
             lxp[g * BM + row] = pend_l;
             mbar_arrive(&bars[F_LX]);
             if (lane == 0) FWD_STATE(warp, -1, n, 9);
             if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[F_LX], (uint32_t)n & 1u, DEERS_KERR_FWD_F16 | 9))) return false;
-            const float l = pend_l + lxp[(g ^ 1) * BM + row];
+            float l = 0.f;
+#pragma unroll
+            for (int w = 0; w < NWG; ++w) l += lxp[w * BM + row];        // same order in every warpgroup
             if (lane == 0) FWD_STATE(warp, -1, n, 10);
             if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[F_O_DONE + (n & 1)], ((uint32_t)n >> 1) & 1u, DEERS_KERR_FWD_F16 | 10))) return false;
             tc_fence_after_sync();
@@ -320,17 +331,22 @@ attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             // that every store instruction writes whole contiguous row segments.
             constexpr int NP = DH / 8;
             uint4 oc[NP];
-#pragma unroll
-            for (int c = 0; c < DH / 32; ++c) {
-                uint32_t r[32];
-                tmem_ld_x32(tmem + TM_O + (uint32_t)(n & 1) * D + t_lane + g * DH + c * 32, r);
-                tmem_wait_ld();
-                if (c == DH / 32 - 1) {                         // accumulator is in registers: release it
-                    tc_fence_before_sync();
-                    mbar_arrive(&bars[F_O_FREE + (n & 1)]);
+            {
+                uint32_t r[DH];
+                const uint32_t to = tmem + TM_O + (uint32_t)(n & 1) * D + t_lane + g * DH;
+                if constexpr (DH == 64) {
+                    tmem_ld_x32(to, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+                    tmem_ld_x32(to + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[DH - 32]));
+                } else if constexpr (DH == 32) {
+                    tmem_ld_x32(to, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+                } else {
+                    tmem_ld_x16(to, *reinterpret_cast<uint32_t(*)[16]>(&r[0]));
                 }
+                tmem_wait_ld();
+                tc_fence_before_sync();
+                mbar_arrive(&bars[F_O_FREE + (n & 1)]);         // accumulator is in registers: release it
 #pragma unroll
-                for (int q8 = 0; q8 < 4; ++q8) oc[c * 4 + q8] = pack8_f16(r + q8 * 8, inv);
+                for (int q8 = 0; q8 < NP; ++q8) oc[q8] = pack8_f16(r + q8 * 8, inv);
             }
             transpose_pieces<NP>(oc, (uint32_t)lane);
             const int grow0 = pend_grow - lane + (lane & ~(NP - 1));
@@ -357,18 +373,11 @@ attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 if (lane == 0) FWD_STATE(warp, (int)gstep, n, j * 100 + 11);
                 if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[F_S_FULL + sb], (gstep >> 1) & 1u, DEERS_KERR_FWD_F16 | 11))) { alive = false; break; }
                 tc_fence_after_sync();
-                float s[64];
-                {
-                    const uint32_t ts = tmem + TM_S + sb * 128u + t_lane + 64 * g;
+                float s[CW];
+                const uint32_t ts = tmem + TM_S + sb * 128u + t_lane + CW * g;
 #pragma unroll
-                    for (int cc = 0; cc < 2; ++cc) {
-                        uint32_t r[32];
-                        tmem_ld_x32(ts + cc * 32, r);
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) s[cc * 32 + i] = __uint_as_float(r[i]);
-                    }
-                    tmem_wait_ld();
-                }
+                for (int cc = 0; cc < CW / 32; ++cc) tmem_ld_x32(ts + cc * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[cc * 32]));
+                tmem_wait_ld();
                 if (tr) FWD_TRACE(1 + g, gstep, 1);
                 // Steps that touch the diagonal or the end of the sequence are scaled here and
                 // masked with -inf; all others keep raw scores and fold the scale into the
@@ -378,8 +387,8 @@ attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 float c1 = sl2;
                 if (edge) {
 #pragma unroll
-                    for (int i = 0; i < 64; ++i) {
-                        const int col = k0 + 64 * g + i;
+                    for (int i = 0; i < CW; ++i) {
+                        const int col = k0 + CW * g + i;
                         const bool masked = (col >= p.T) || (p.causal && col > q0 + row);
                         s[i] = masked ? -INFINITY : s[i] * sl2;
                     }
@@ -388,20 +397,20 @@ attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 float mx = s[0];
                 if (c1 >= 0.f) {
 #pragma unroll
-                    for (int i = 1; i < 64; ++i) mx = fmaxf(mx, s[i]);
+                    for (int i = 1; i < CW; ++i) mx = fmaxf(mx, s[i]);
                 } else {
 #pragma unroll
-                    for (int i = 1; i < 64; ++i) mx = fminf(mx, s[i]);
+                    for (int i = 1; i < CW; ++i) mx = fminf(mx, s[i]);
                 }
                 mx *= c1;
-                // Exchange the partial row max with the twin thread of the other warpgroup.
+                // Exchange the partial row max with the twin threads of the other warpgroups.
                 if (tr) FWD_TRACE(1 + g, gstep, 2);
-                float* xp = xch + sb * 2 * BM;
+                float* xp = xch + sb * NWG * BM;
                 xp[g * BM + row] = mx;
                 mbar_arrive(&bars[F_XCH]);
-                if (lane == 0) FWD_STATE(warp, (int)gstep, n, j * 100 + 12);
                 if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[F_XCH], gstep & 1u, DEERS_KERR_FWD_F16 | 12))) { alive = false; break; }
-                mx = fmaxf(mx, xp[(g ^ 1) * BM + row]);
+#pragma unroll
+                for (int w = 0; w < NWG; ++w) mx = fmaxf(mx, xp[w * BM + row]);
                 if (tr) FWD_TRACE(1 + g, gstep, 3);
 
                 const float m_new = fmaxf(m_used, mx);
@@ -412,10 +421,10 @@ attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 const float alpha = (j == 0) ? 0.f : ex2(m_used - m_safe);
                 const bool warp_grow = __any_sync(0xffffffffu, grow);
 
-                uint32_t pk[32];
+                uint32_t pk[CW / 2];
                 float rs = 0.f;
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
+                for (int i = 0; i < CW / 2; ++i) {
                     const float e0 = ex2(fmaf(s[2 * i], c1, -m_safe));
                     const float e1 = ex2(fmaf(s[2 * i + 1], c1, -m_safe));
                     rs += e0 + e1;
@@ -427,26 +436,34 @@ attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
 
                 if (j > 0 && warp_grow) {
                     // O += P V of the previous step must have landed before O is rescaled.
-                    if (lane == 0) FWD_STATE(warp, (int)gstep, n, j * 100 + 13);
                     if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[F_PV_DONE + ((gstep - 1u) & 1u)], ((gstep - 1u) >> 1) & 1u, DEERS_KERR_FWD_F16 | 13))) { alive = false; break; }
                     tc_fence_after_sync();
                     const uint32_t to = tmem + TM_O + (uint32_t)(n & 1) * D + t_lane + g * DH;
+                    if constexpr (DH % 32 == 0) {
 #pragma unroll
-                    for (int cc = 0; cc < DH / 32; ++cc) {
-                        uint32_t r[32];
-                        tmem_ld_x32(to + cc * 32, r);
+                        for (int cc = 0; cc < DH / 32; ++cc) {
+                            uint32_t r[32];
+                            tmem_ld_x32(to + cc * 32, r);
+                            tmem_wait_ld();
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+                            tmem_st_x32(to + cc * 32, r);
+                        }
+                    } else {
+                        uint32_t r[16];
+                        tmem_ld_x16(to, r);
                         tmem_wait_ld();
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-                        tmem_st_x32(to + cc * 32, r);
+                        for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+                        tmem_st_x16(to, r);
                     }
                 }
-                // P replaces this warpgroup's half of S in TMEM (32 packed columns).
-                tmem_st_x32(tmem + TM_S + sb * 128u + t_lane + 64 * g, pk);
+                // P replaces this warpgroup's part of S in TMEM (CW / 2 packed columns).
+                if constexpr (CW == 64) tmem_st_x32(ts, *reinterpret_cast<uint32_t(*)[32]>(&pk[0]));
+                else tmem_st_x16(ts, *reinterpret_cast<uint32_t(*)[16]>(&pk[0]));
                 tmem_wait_st();
                 tc_fence_before_sync();
                 mbar_arrive(&bars[F_P_FULL + sb]);
-                if (lane == 0) FWD_STATE(warp, (int)gstep, n, j * 100 + 14);
                 if (tr) FWD_TRACE(1 + g, gstep, 5);
                 if (j == 0 && !epilogue()) { alive = false; break; }          // previous item's O tile
             }
@@ -486,7 +503,7 @@ int fwd_launch(deers_ctx* ctx, const deers_attn_desc* d, const void* q, const vo
     p.sched = deers_get_schedule(ctx, d->B, d->H, (int)nq, d->causal, (int)grid, &p.sched_rows);
     {
         KernelTimerScope ts(ctx, DEERS_K_FWD);
-        attn_fwd_f16_kernel<D><<<grid, 352, smem, ctx->stream>>>(tq, tk, tv, p);
+        attn_fwd_f16_kernel<D><<<grid, FWD_THREADS, smem, ctx->stream>>>(tq, tk, tv, p);
     }
     ctx->launches += 1;
     DEERS_CUDA_TRY(ctx, cudaGetLastError());
