@@ -9,6 +9,8 @@
 // row lse of the attention op); the backward reads x and dy once and writes dx:
 //     inv = 1 / sqrt(sum(x*x) / n + eps)            y  = x * inv
 //     dx  = dy * inv - x * (sum(dy * x) * inv^3 / n)
+// Rows of up to 1024 elements are owned by a warp, up to 8192 by a block (both keep the row in registers: one
+// pass over HBM); longer rows take two passes of 16-byte loads.
 // HBM-bound: 8 bytes per element forward, 12 backward.  Sums are f32 shuffle trees (the reference
 // sums left to right), so parity is to rounding, not to the bit.
 #include "common.cuh"
@@ -24,7 +26,7 @@ __device__ __forceinline__ float warp_sum(float v) {
 }
 
 // BWD = false: y = x * inv, inv_out[row] = inv.   BWD = true: dx from x, dy and the saved inv.
-template <bool BWD, bool VEC>
+template <bool BWD, bool VEC, bool VEC2 = false>
 __global__ void __launch_bounds__(256) rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ dy,
                                                       float* __restrict__ out, float* __restrict__ inv_io, long long rows,
                                                       int C, float eps, float inv_n) {
@@ -74,6 +76,40 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const float* __restrict__ 
                     reinterpret_cast<float4*>(orow)[p] = o;
                 }
             }
+        } else if (VEC2) {                                      // long aligned rows: two passes of 16-byte loads
+            const int nv = C / 4;
+            const float4* x4 = reinterpret_cast<const float4*>(xr);
+            const float4* g4 = BWD ? reinterpret_cast<const float4*>(dy + row * C) : nullptr;
+            float acc = 0.f;
+            for (int p = lane; p < nv; p += 32) {
+                const float4 a = x4[p];
+                if (BWD) {
+                    const float4 b = g4[p];
+                    acc += a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w;
+                } else {
+                    acc += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+                }
+            }
+            acc = warp_sum(acc);
+            float inv, k = 0.f;
+            if (BWD) {
+                inv = inv_io[row];
+                k = acc * inv * inv * inv * inv_n;
+            } else {
+                inv = 1.0f / sqrtf(acc * inv_n + eps);
+                if (lane == 0) inv_io[row] = inv;
+            }
+            for (int p = lane; p < nv; p += 32) {               // the row (<= a few KB per lane group) is still in L1 / L2
+                const float4 a = x4[p];
+                float4 o;
+                if (BWD) {
+                    const float4 b = g4[p];
+                    o.x = b.x * inv - a.x * k; o.y = b.y * inv - a.y * k; o.z = b.z * inv - a.z * k; o.w = b.w * inv - a.w * k;
+                } else {
+                    o.x = a.x * inv; o.y = a.y * inv; o.z = a.z * inv; o.w = a.w * inv;
+                }
+                reinterpret_cast<float4*>(orow)[p] = o;
+            }
         } else {                                                // any C, any alignment: two passes over the row
             const float* gr = BWD ? dy + row * C : nullptr;
             float acc = 0.f;
@@ -92,11 +128,70 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const float* __restrict__ 
     }
 }
 
+// Rows of 1025 .. 8192 elements: a whole block owns a row, which still stays in registers (one pass over HBM).
+template <bool BWD>
+__global__ void __launch_bounds__(256) rmsnorm_block_kernel(const float* __restrict__ x, const float* __restrict__ dy,
+                                                            float* __restrict__ out, float* __restrict__ inv_io, long long rows,
+                                                            int C, float eps, float inv_n) {
+    __shared__ float part[8];
+    const int nv = C / 4;                                       // <= 256 * RN_MAXV
+    for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+        const float4* x4 = reinterpret_cast<const float4*>(x + row * C);
+        const float4* g4 = BWD ? reinterpret_cast<const float4*>(dy + row * C) : nullptr;
+        float4 xv[RN_MAXV], gv[RN_MAXV];
+        float acc = 0.f;
+#pragma unroll
+        for (int i = 0; i < RN_MAXV; ++i) {
+            const int p = threadIdx.x + 256 * i;
+            if (p < nv) {
+                xv[i] = x4[p];
+                if (BWD) {
+                    gv[i] = g4[p];
+                    acc += xv[i].x * gv[i].x + xv[i].y * gv[i].y + xv[i].z * gv[i].z + xv[i].w * gv[i].w;
+                } else {
+                    acc += xv[i].x * xv[i].x + xv[i].y * xv[i].y + xv[i].z * xv[i].z + xv[i].w * xv[i].w;
+                }
+            }
+        }
+        acc = warp_sum(acc);
+        __syncthreads();                                        // part[] of the previous row has been read
+        if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = acc;
+        __syncthreads();
+        float tot = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) tot += part[w];
+        float inv, k = 0.f;
+        if (BWD) {
+            inv = inv_io[row];
+            k = tot * inv * inv * inv * inv_n;
+        } else {
+            inv = 1.0f / sqrtf(tot * inv_n + eps);
+            if (threadIdx.x == 0) inv_io[row] = inv;
+        }
+        float4* o4 = reinterpret_cast<float4*>(out + row * C);
+#pragma unroll
+        for (int i = 0; i < RN_MAXV; ++i) {
+            const int p = threadIdx.x + 256 * i;
+            if (p < nv) {
+                float4 o;
+                if (BWD) {
+                    o.x = gv[i].x * inv - xv[i].x * k; o.y = gv[i].y * inv - xv[i].y * k;
+                    o.z = gv[i].z * inv - xv[i].z * k; o.w = gv[i].w * inv - xv[i].w * k;
+                } else {
+                    o.x = xv[i].x * inv; o.y = xv[i].y * inv; o.z = xv[i].z * inv; o.w = xv[i].w * inv;
+                }
+                o4[p] = o;
+            }
+        }
+    }
+}
+
 template <bool BWD>
 int rms_launch(deers_ctx* ctx, long long rows, int C, float eps, const float* x, const float* dy, float* out, float* inv) {
     if (rows == 0) return DEERS_OK;
     uintptr_t bits = (uintptr_t)x | (uintptr_t)out | (BWD ? (uintptr_t)dy : 0);
-    const bool vec = (C % 4) == 0 && C <= 32 * RN_MAXV * 4 && (bits & 15u) == 0;
+    const bool aligned = (C % 4) == 0 && (bits & 15u) == 0;
+    const bool vec = aligned && C <= 32 * RN_MAXV * 4;
     const long long want = (rows + 7) / 8;
     const long long cap = 16LL * ctx->sm_count;
     const unsigned grid = (unsigned)(want < cap ? want : cap);
@@ -104,6 +199,10 @@ int rms_launch(deers_ctx* ctx, long long rows, int C, float eps, const float* x,
     {
         KernelTimerScope ts(ctx, DEERS_K_NORM);
         if (vec) rmsnorm_kernel<BWD, true><<<grid, 256, 0, ctx->stream>>>(x, dy, out, inv, rows, C, eps, inv_n);
+        else if (aligned && C <= 256 * RN_MAXV * 4) {
+            const unsigned bgrid = (unsigned)(rows < cap ? rows : cap);
+            rmsnorm_block_kernel<BWD><<<bgrid, 256, 0, ctx->stream>>>(x, dy, out, inv, rows, C, eps, inv_n);
+        } else if (aligned) rmsnorm_kernel<BWD, false, true><<<grid, 256, 0, ctx->stream>>>(x, dy, out, inv, rows, C, eps, inv_n);
         else rmsnorm_kernel<BWD, false><<<grid, 256, 0, ctx->stream>>>(x, dy, out, inv, rows, C, eps, inv_n);
     }
     ctx->launches += 1;

@@ -30,7 +30,7 @@ def test_golden_vectors():
         assert np.abs(dx - blob[f"{name}/dx"]).max() <= TOL * np.abs(blob[f"{name}/dx"]).max() + 1e-6, name
 
 
-@pytest.mark.parametrize("shape", [(4, 256, 192), (3, 5, 7), (2, 1024), (33, 1028), (1, 4100), (6, 1)])
+@pytest.mark.parametrize("shape", [(4, 256, 192), (3, 5, 7), (2, 1024), (33, 1028), (5, 8192), (2, 8196), (1, 4100 * 4), (6, 1), (3, 1026)])
 def test_shapes_against_the_oracle(shape):
     from oracle import ref
     rng = np.random.default_rng(sum(shape))
