@@ -101,7 +101,8 @@ __device__ __forceinline__ void item_tile(int B, int H, int ntile, int w, int& s
     bh = group * 16 + within % gsize;
 }
 
-// n-th work item of this CTA, or -1 when its list is exhausted.
+// n-th work item of this CTA, or -1 when its list is exhausted.  Callers fetch item n+1 when item n
+// starts, so the table read (an L2 round trip) is never waited for at an item boundary.
 __device__ __forceinline__ int next_item(const BwdParams& p, int n, int n_items) {
     int w;
     if (p.sched) w = n < p.sched_rows ? p.sched[n * (int)gridDim.x + (int)blockIdx.x] : -1;
@@ -200,7 +201,7 @@ attn_bwd_dkdv_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         if (lane == 0) {
             uint32_t gi = 0;                                    // query-tile iterations so far (all items)
             bool ok = true;
-            for (int n = 0, w = next_item(p, 0, n_items); ok && w >= 0; ++n, w = next_item(p, n, n_items)) {
+            for (int n = 0, w = next_item(p, 0, n_items), wn = next_item(p, 1, n_items); ok && w >= 0; ++n, w = wn, wn = next_item(p, n + 1, n_items)) {
                 int kt, bh;
                 item_tile(p.B, p.H, nq, w, kt, bh);             // low KV tiles carry the most work
                 const int b = bh / p.H, h = bh % p.H;
@@ -264,7 +265,7 @@ attn_bwd_dkdv_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
             auto a_tmem = [&](uint32_t base, int ks) { return tmem + base + (uint32_t)(ks >> 2) * 64u + (uint32_t)(ks & 3) * 8u; };
             uint32_t gi = 0;
             bool ok = true;
-            for (int n = 0, w = next_item(p, 0, n_items); ok && w >= 0; ++n, w = next_item(p, n, n_items)) {
+            for (int n = 0, w = next_item(p, 0, n_items), wn = next_item(p, 1, n_items); ok && w >= 0; ++n, w = wn, wn = next_item(p, n + 1, n_items)) {
                 int kt, bh;
                 item_tile(p.B, p.H, nq, w, kt, bh);
                 const int niter = nq - (p.causal ? kt : 0);
@@ -333,7 +334,7 @@ attn_bwd_dkdv_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         const bool tr = lane == 0 && (warp == 2 || warp == 6);
 #endif
 
-        for (int n = 0, w = next_item(p, 0, n_items); alive && w >= 0; ++n, w = next_item(p, n, n_items)) {
+        for (int n = 0, w = next_item(p, 0, n_items), wn = next_item(p, 1, n_items); alive && w >= 0; ++n, w = wn, wn = next_item(p, n + 1, n_items)) {
             int kt, bh;
             item_tile(p.B, p.H, nq, w, kt, bh);
             const int b = bh / p.H, h = bh % p.H;
@@ -552,7 +553,7 @@ attn_bwd_dq_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         if (lane == 0) {
             uint32_t kvc = 0;                                   // K/V stage uses so far (all items)
             bool ok = true;
-            for (int n = 0, w = next_item(p, 0, n_items); ok && w >= 0; ++n, w = next_item(p, n, n_items)) {
+            for (int n = 0, w = next_item(p, 0, n_items), wn = next_item(p, 1, n_items); ok && w >= 0; ++n, w = wn, wn = next_item(p, n + 1, n_items)) {
                 int slot, bh;
                 item_tile(p.B, p.H, nq, w, slot, bh);
                 const int qt = nq - 1 - slot;                   // late query tiles carry the most work
@@ -609,7 +610,7 @@ attn_bwd_dq_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
             };
             uint32_t kvc = 0;                                   // K/V stage uses == KV iterations so far
             bool ok = true;
-            for (int n = 0, w = next_item(p, 0, n_items); ok && w >= 0; ++n, w = next_item(p, n, n_items)) {
+            for (int n = 0, w = next_item(p, 0, n_items), wn = next_item(p, 1, n_items); ok && w >= 0; ++n, w = wn, wn = next_item(p, n + 1, n_items)) {
                 int slot, bh;
                 item_tile(p.B, p.H, nq, w, slot, bh);
                 const int qt = nq - 1 - slot;
@@ -712,7 +713,7 @@ attn_bwd_dq_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
             return true;
         };
 
-        for (int n = 0, w = next_item(p, 0, n_items); alive && w >= 0; ++n, w = next_item(p, n, n_items)) {
+        for (int n = 0, w = next_item(p, 0, n_items), wn = next_item(p, 1, n_items); alive && w >= 0; ++n, w = wn, wn = next_item(p, n + 1, n_items)) {
             int slot, bh;
             item_tile(p.B, p.H, nq, w, slot, bh);
             const int qt = nq - 1 - slot;

@@ -113,6 +113,7 @@ enum FwdBar { F_Q_FULL = 0, F_Q_EMPTY = 2, F_K_FULL = 4, F_V_FULL = 6, F_PV_DONE
 struct WorkCursor {
     int n;          // index of the item inside this CTA's list
     int w;          // global item index
+    int w_next;     // global item index of the item after this one (prefetched)
     int j;          // KV tile inside the item
     int ntiles, qt, bh;
     __device__ __forceinline__ void load(const FwdParams& p, int nq) {
@@ -124,14 +125,22 @@ struct WorkCursor {
         bh = group * 16 + within % gsize;
         ntiles = p.causal ? qt + 1 : nq;
     }
+    __device__ __forceinline__ int table(const FwdParams& p, int idx, int n_items) const {
+        int v;
+        if (p.sched) v = idx < p.sched_rows ? p.sched[idx * (int)gridDim.x + (int)blockIdx.x] : -1;
+        else v = (int)blockIdx.x + idx * (int)gridDim.x;
+        return v < n_items ? v : -1;
+    }
+    // Item n becomes current; the table entry of item n+1 is requested now and not looked at before the
+    // next call, so its L2 round trip is off the item boundary.
     __device__ __forceinline__ void fetch(const FwdParams& p, int nq, int n_items) {
-        if (p.sched) w = n < p.sched_rows ? p.sched[n * (int)gridDim.x + (int)blockIdx.x] : -1;
-        else w = (int)blockIdx.x + n * (int)gridDim.x;
-        if (w >= n_items) w = -1;
+        w = w_next;
+        w_next = table(p, n + 1, n_items);
         if (w >= 0) load(p, nq);
     }
     __device__ __forceinline__ void init(const FwdParams& p, int nq, int n_items) {
         n = 0; j = 0;
+        w_next = table(p, 0, n_items);
         fetch(p, nq, n_items);
     }
     __device__ __forceinline__ bool valid(int) const { return w >= 0; }
@@ -313,11 +322,9 @@ attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             if (pend_n < 0) return true;
             const int n = pend_n;
             pend_n = -1;
-            // Combine the partial row sums of the warpgroups.
+            // Combine the partial row sums of the warpgroups (published when the item's last step ended,
+            // so this wait has long been satisfied).
             float* lxp = lx + (n & 1) * NWG * BM;
-            lxp[g * BM + row] = pend_l;
-            mbar_arrive(&bars[F_LX]);
-            if (lane == 0) FWD_STATE(warp, -1, n, 9);
             if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[F_LX], (uint32_t)n & 1u, DEERS_KERR_FWD_F16 | 9))) return false;
             float l = 0.f;
 #pragma unroll
@@ -348,6 +355,13 @@ attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
 #pragma unroll
                 for (int q8 = 0; q8 < NP; ++q8) oc[q8] = pack8_f16(r + q8 * 8, inv);
             }
+#ifdef DEERS_FWD_DIRECT_STORE
+            if (pend_grow < p.T) {
+                __half* orow = p.o + b * p.so_b + h * p.so_h + (long long)pend_grow * p.so_t + g * DH;
+#pragma unroll
+                for (int c = 0; c < NP; ++c) *reinterpret_cast<uint4*>(orow + c * 8) = oc[c];
+            }
+#else
             transpose_pieces<NP>(oc, (uint32_t)lane);
             const int grow0 = pend_grow - lane + (lane & ~(NP - 1));
             __half* ob = p.o + b * p.so_b + h * p.so_h + g * DH + (lane & (NP - 1)) * 8;
@@ -356,6 +370,7 @@ attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 const int grow = grow0 + c;
                 if (grow < p.T) *reinterpret_cast<uint4*>(ob + (long long)grow * p.so_t) = oc[c];
             }
+#endif
             if (g == 0 && pend_grow < p.T) p.lse[(long long)pend_bh * p.T + pend_grow] = (pend_m + log2f(l)) * LN2;
             return true;
         };
@@ -386,12 +401,12 @@ attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 const bool edge = (p.causal && j == qt) || (k0 + BN > p.T);
                 float c1 = sl2;
                 if (edge) {
+                    // Column CW*g + i of this tile is valid iff i <= lim: on the diagonal tile (where
+                    // k0 == q0) the key may not lie right of the query, and keys end at T.
+                    int lim = p.T - 1 - k0 - CW * g;
+                    if (p.causal && j == qt) lim = min(lim, row - CW * g);
 #pragma unroll
-                    for (int i = 0; i < CW; ++i) {
-                        const int col = k0 + CW * g + i;
-                        const bool masked = (col >= p.T) || (p.causal && col > q0 + row);
-                        s[i] = masked ? -INFINITY : s[i] * sl2;
-                    }
+                    for (int i = 0; i < CW; ++i) s[i] = (i > lim) ? -INFINITY : s[i] * sl2;
                     c1 = 1.0f;
                 }
                 float mx = s[0];
@@ -469,6 +484,8 @@ attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             }
             if (!alive) break;
             pend_n = n; pend_grow = q0 + row; pend_bh = bh; pend_m = m_used; pend_l = l;
+            lx[(n & 1) * NWG * BM + g * BM + row] = l;                       // partial row sum for the epilogue
+            mbar_arrive(&bars[F_LX]);
             // advance the cursor by a whole item
             c.j = ntiles - 1;
             c.advance(p, nq, n_items);
