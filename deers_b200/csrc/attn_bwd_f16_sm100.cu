@@ -72,7 +72,7 @@ struct BwdParams {
     int causal;
     float scale;
     unsigned int* err;
-    const int* sched;           // balanced schedule table[n * grid + cta] (or nullptr: strided)
+    const int4* sched;          // balanced schedule table[n * grid + cta] = {slot, slice, batch, head} (or nullptr: strided)
     int sched_rows;
 };
 
@@ -101,13 +101,16 @@ __device__ __forceinline__ void item_tile(int B, int H, int ntile, int w, int& s
     bh = group * 16 + within % gsize;
 }
 
-// n-th work item of this CTA, or -1 when its list is exhausted.  Callers fetch item n+1 when item n
-// starts, so the table read (an L2 round trip) is never waited for at an item boundary.
-__device__ __forceinline__ int next_item(const BwdParams& p, int n, int n_items) {
-    int w;
-    if (p.sched) w = n < p.sched_rows ? p.sched[n * (int)gridDim.x + (int)blockIdx.x] : -1;
-    else w = (int)blockIdx.x + n * (int)gridDim.x;
-    return w < n_items ? w : -1;
+// n-th work item of this CTA as {slot, slice, batch, head}; slot < 0 when its list is exhausted.  Callers
+// fetch item n+1 when item n starts, so the table read (an L2 round trip) is never waited for at an item
+// boundary; the table spares the single issuing threads the integer divisions of item_tile.
+__device__ __forceinline__ int4 next_item(const BwdParams& p, int n, int n_items, int ntile) {
+    if (p.sched) return n < p.sched_rows ? p.sched[n * (int)gridDim.x + (int)blockIdx.x] : make_int4(-1, 0, 0, 0);
+    const int w = (int)blockIdx.x + n * (int)gridDim.x;
+    if (w >= n_items) return make_int4(-1, 0, 0, 0);
+    int slot, bh;
+    item_tile(p.B, p.H, ntile, w, slot, bh);
+    return make_int4(slot, bh, bh / p.H, bh % p.H);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -201,10 +204,10 @@ attn_bwd_dkdv_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         if (lane == 0) {
             uint32_t gi = 0;                                    // query-tile iterations so far (all items)
             bool ok = true;
-            for (int n = 0, w = next_item(p, 0, n_items), wn = next_item(p, 1, n_items); ok && w >= 0; ++n, w = wn, wn = next_item(p, n + 1, n_items)) {
-                int kt, bh;
-                item_tile(p.B, p.H, nq, w, kt, bh);             // low KV tiles carry the most work
-                const int b = bh / p.H, h = bh % p.H;
+            for (int4 cur = next_item(p, 0, n_items, nq), nxt = next_item(p, 1, n_items, nq), n4 = make_int4(0, 0, 0, 0); ok && cur.x >= 0;
+                     ++n4.x, cur = nxt, nxt = next_item(p, n4.x + 1, n_items, nq)) {
+                const int n = n4.x, kt = cur.x, bh = cur.y;
+                const int b = cur.z, h = cur.w;
                 const int i0 = p.causal ? kt : 0;
                 const int niter = nq - i0;
                 // K / V are single-buffered: wait until the previous item's S^T and dP^T products are done.
@@ -265,9 +268,9 @@ attn_bwd_dkdv_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
             auto a_tmem = [&](uint32_t base, int ks) { return tmem + base + (uint32_t)(ks >> 2) * 64u + (uint32_t)(ks & 3) * 8u; };
             uint32_t gi = 0;
             bool ok = true;
-            for (int n = 0, w = next_item(p, 0, n_items), wn = next_item(p, 1, n_items); ok && w >= 0; ++n, w = wn, wn = next_item(p, n + 1, n_items)) {
-                int kt, bh;
-                item_tile(p.B, p.H, nq, w, kt, bh);
+            for (int4 cur = next_item(p, 0, n_items, nq), nxt = next_item(p, 1, n_items, nq), n4 = make_int4(0, 0, 0, 0); ok && cur.x >= 0;
+                     ++n4.x, cur = nxt, nxt = next_item(p, n4.x + 1, n_items, nq)) {
+                const int n = n4.x, kt = cur.x, bh = cur.y;
                 const int niter = nq - (p.causal ? kt : 0);
                 if (!mbar_wait(ws, &bars[A_KV_FULL], (uint32_t)n & 1u, DEERS_KERR_BWD_F16 | 5)) break;
                 if (!mbar_wait(ws, &bars[A_Q_FULL + gi % 3u], (gi / 3u) & 1u, DEERS_KERR_BWD_F16 | 6)) break;
@@ -334,10 +337,10 @@ attn_bwd_dkdv_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         const bool tr = lane == 0 && (warp == 2 || warp == 6);
 #endif
 
-        for (int n = 0, w = next_item(p, 0, n_items), wn = next_item(p, 1, n_items); alive && w >= 0; ++n, w = wn, wn = next_item(p, n + 1, n_items)) {
-            int kt, bh;
-            item_tile(p.B, p.H, nq, w, kt, bh);
-            const int b = bh / p.H, h = bh % p.H;
+        for (int4 cur = next_item(p, 0, n_items, nq), nxt = next_item(p, 1, n_items, nq), n4 = make_int4(0, 0, 0, 0); alive && cur.x >= 0;
+                 ++n4.x, cur = nxt, nxt = next_item(p, n4.x + 1, n_items, nq)) {
+            const int n = n4.x, kt = cur.x, bh = cur.y;
+            const int b = cur.z, h = cur.w;
             const int k0 = kt * BT;
             const int i0 = p.causal ? kt : 0;
             const int niter = nq - i0;
@@ -553,11 +556,11 @@ attn_bwd_dq_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         if (lane == 0) {
             uint32_t kvc = 0;                                   // K/V stage uses so far (all items)
             bool ok = true;
-            for (int n = 0, w = next_item(p, 0, n_items), wn = next_item(p, 1, n_items); ok && w >= 0; ++n, w = wn, wn = next_item(p, n + 1, n_items)) {
-                int slot, bh;
-                item_tile(p.B, p.H, nq, w, slot, bh);
+            for (int4 cur = next_item(p, 0, n_items, nq), nxt = next_item(p, 1, n_items, nq), n4 = make_int4(0, 0, 0, 0); ok && cur.x >= 0;
+                     ++n4.x, cur = nxt, nxt = next_item(p, n4.x + 1, n_items, nq)) {
+                const int n = n4.x, slot = cur.x, bh = cur.y;
                 const int qt = nq - 1 - slot;                   // late query tiles carry the most work
-                const int b = bh / p.H, h = bh % p.H;
+                const int b = cur.z, h = cur.w;
                 const int ntiles = p.causal ? qt + 1 : nq;
                 // Q / dO are single-buffered: wait until the previous item's S and dP products are done.
                 if (!mbar_wait(ws, &bars[Q_QDO_EMPTY], ((uint32_t)n & 1u) ^ 1u, DEERS_KERR_BWD_F16 | 0x10)) break;
@@ -610,9 +613,9 @@ attn_bwd_dq_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
             };
             uint32_t kvc = 0;                                   // K/V stage uses == KV iterations so far
             bool ok = true;
-            for (int n = 0, w = next_item(p, 0, n_items), wn = next_item(p, 1, n_items); ok && w >= 0; ++n, w = wn, wn = next_item(p, n + 1, n_items)) {
-                int slot, bh;
-                item_tile(p.B, p.H, nq, w, slot, bh);
+            for (int4 cur = next_item(p, 0, n_items, nq), nxt = next_item(p, 1, n_items, nq), n4 = make_int4(0, 0, 0, 0); ok && cur.x >= 0;
+                     ++n4.x, cur = nxt, nxt = next_item(p, n4.x + 1, n_items, nq)) {
+                const int n = n4.x, slot = cur.x, bh = cur.y;
                 const int qt = nq - 1 - slot;
                 const int ntiles = p.causal ? qt + 1 : nq;
                 const uint32_t tm_dq = tmem + TM_DQ;
@@ -713,11 +716,11 @@ attn_bwd_dq_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
             return true;
         };
 
-        for (int n = 0, w = next_item(p, 0, n_items), wn = next_item(p, 1, n_items); alive && w >= 0; ++n, w = wn, wn = next_item(p, n + 1, n_items)) {
-            int slot, bh;
-            item_tile(p.B, p.H, nq, w, slot, bh);
+        for (int4 cur = next_item(p, 0, n_items, nq), nxt = next_item(p, 1, n_items, nq), n4 = make_int4(0, 0, 0, 0); alive && cur.x >= 0;
+                 ++n4.x, cur = nxt, nxt = next_item(p, n4.x + 1, n_items, nq)) {
+            const int n = n4.x, slot = cur.x, bh = cur.y;
             const int qt = nq - 1 - slot;
-            const int b = bh / p.H, h = bh % p.H;
+            const int b = cur.z, h = cur.w;
             const int q0 = qt * BT;
             const int ntiles = p.causal ? qt + 1 : nq;
             const float lse2_r = p.lse2[(long long)bh * p.Tpad + q0 + r];      // padded: 0 beyond T

@@ -76,7 +76,7 @@ struct FwdParams {
     int causal;
     float scale;
     unsigned int* err;
-    const int* sched;           // balanced schedule table[n * grid + cta] (or nullptr: strided)
+    const int4* sched;          // balanced schedule table[n * grid + cta] = {slot, slice, batch, head} (or nullptr: strided)
     int sched_rows;
 };
 
@@ -112,35 +112,38 @@ enum FwdBar { F_Q_FULL = 0, F_Q_EMPTY = 2, F_K_FULL = 4, F_V_FULL = 6, F_PV_DONE
 // slices come first (balance) and the group's K and V (a few MB) stay in L2.
 struct WorkCursor {
     int n;          // index of the item inside this CTA's list
-    int w;          // global item index
-    int w_next;     // global item index of the item after this one (prefetched)
+    int w;          // >= 0 while the cursor points at an item
+    int4 e_next;    // table entry of the item after this one (prefetched)
     int j;          // KV tile inside the item
-    int ntiles, qt, bh;
-    __device__ __forceinline__ void load(const FwdParams& p, int nq) {
+    int ntiles, qt, bh, b, h;
+    // {slot, slice, batch, head} of this CTA's idx-th item; slot < 0 past the end.  With a host-built table
+    // this is one load; the strided fallback pays the integer divisions.
+    __device__ __forceinline__ int4 table(const FwdParams& p, int idx, int nq, int n_items) const {
+        if (p.sched) return idx < p.sched_rows ? p.sched[idx * (int)gridDim.x + (int)blockIdx.x] : make_int4(-1, 0, 0, 0);
+        const int v = (int)blockIdx.x + idx * (int)gridDim.x;
+        if (v >= n_items) return make_int4(-1, 0, 0, 0);
         const int BH = p.B * p.H;
-        const int group = w / (16 * nq);
+        const int group = v / (16 * nq);
         const int gsize = min(16, BH - group * 16);
-        const int within = w - group * 16 * nq;
-        qt = nq - 1 - within / gsize;
-        bh = group * 16 + within % gsize;
-        ntiles = p.causal ? qt + 1 : nq;
-    }
-    __device__ __forceinline__ int table(const FwdParams& p, int idx, int n_items) const {
-        int v;
-        if (p.sched) v = idx < p.sched_rows ? p.sched[idx * (int)gridDim.x + (int)blockIdx.x] : -1;
-        else v = (int)blockIdx.x + idx * (int)gridDim.x;
-        return v < n_items ? v : -1;
+        const int within = v - group * 16 * nq;
+        const int s = group * 16 + within % gsize;
+        return make_int4(within / gsize, s, s / p.H, s % p.H);
     }
     // Item n becomes current; the table entry of item n+1 is requested now and not looked at before the
     // next call, so its L2 round trip is off the item boundary.
     __device__ __forceinline__ void fetch(const FwdParams& p, int nq, int n_items) {
-        w = w_next;
-        w_next = table(p, n + 1, n_items);
-        if (w >= 0) load(p, nq);
+        const int4 e = e_next;
+        e_next = table(p, n + 1, nq, n_items);
+        w = e.x;
+        if (e.x >= 0) {
+            qt = nq - 1 - e.x;                              // heaviest (latest) query tiles first
+            bh = e.y; b = e.z; h = e.w;
+            ntiles = p.causal ? qt + 1 : nq;
+        }
     }
     __device__ __forceinline__ void init(const FwdParams& p, int nq, int n_items) {
         n = 0; j = 0;
-        w_next = table(p, 0, n_items);
+        e_next = table(p, 0, nq, n_items);
         fetch(p, nq, n_items);
     }
     __device__ __forceinline__ bool valid(int) const { return w >= 0; }
@@ -218,7 +221,7 @@ attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             WorkCursor c;
             c.init(p, nq, n_items);
             for (uint32_t g = 0; c.valid(n_items); ++g) {      // g: global step = K / V stage use
-                const int b = c.bh / p.H, h = c.bh % p.H;
+                const int b = c.b, h = c.h;
                 if (c.j == 0) {
                     const int qb = c.n & 1;
                     FWD_STATE(0, (int)g, c.n, c.j * 10 + 1);
@@ -316,7 +319,7 @@ attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         bool alive = true;
 
         // Deferred epilogue of the previous item (runs after this item's first P has been handed over).
-        int pend_n = -1, pend_grow = 0, pend_bh = 0;
+        int pend_n = -1, pend_grow = 0, pend_bh = 0, pend_b = 0, pend_h = 0;
         float pend_m = 0.f, pend_l = 0.f;
         auto epilogue = [&]() -> bool {
             if (pend_n < 0) return true;
@@ -333,7 +336,7 @@ attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[F_O_DONE + (n & 1)], ((uint32_t)n >> 1) & 1u, DEERS_KERR_FWD_F16 | 10))) return false;
             tc_fence_after_sync();
             const float inv = 1.f / l;
-            const int b = pend_bh / p.H, h = pend_bh % p.H;
+            const int b = pend_b, h = pend_h;
             // The thread's half row of O, as 16-byte pieces, is transposed within lane groups so
             // that every store instruction writes whole contiguous row segments.
             constexpr int NP = DH / 8;
@@ -483,7 +486,7 @@ attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 if (j == 0 && !epilogue()) { alive = false; break; }          // previous item's O tile
             }
             if (!alive) break;
-            pend_n = n; pend_grow = q0 + row; pend_bh = bh; pend_m = m_used; pend_l = l;
+            pend_n = n; pend_grow = q0 + row; pend_bh = bh; pend_b = c.b; pend_h = c.h; pend_m = m_used; pend_l = l;
             lx[(n & 1) * NWG * BM + g * BM + row] = l;                       // partial row sum for the epilogue
             mbar_arrive(&bars[F_LX]);
             // advance the cursor by a whole item

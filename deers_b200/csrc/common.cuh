@@ -87,7 +87,7 @@ enum {
 // loaded so far, which balances the causal triangle for any slice count.  Returns nullptr (plain
 // strided assignment) when the table would not fit.
 constexpr int DEERS_SCHED_CAP = 1 << 20;                 // table entries
-const int* deers_get_schedule(deers_ctx* ctx, int B, int H, int ntile, int causal, int grid, int* rows);
+const int4* deers_get_schedule(deers_ctx* ctx, int B, int H, int ntile, int causal, int grid, int* rows);
 
 // f32 FFMA path (attn_f32.cu)
 int launch_attn_fwd_f32(deers_ctx* ctx, const deers_attn_desc* d, const float* q, const float* k,

@@ -181,14 +181,14 @@ extern "C" int deers_b200_sync(deers_ctx* ctx) {
 // ---------------------------------------------------------------------------
 // Work schedule of the persistent kernels
 // ---------------------------------------------------------------------------
-const int* deers_get_schedule(deers_ctx* ctx, int B, int H, int ntile, int causal, int grid, int* rows) {
+const int4* deers_get_schedule(deers_ctx* ctx, int B, int H, int ntile, int causal, int grid, int* rows) {
     *rows = 0;
     const long long n_items = (long long)B * H * ntile;
     if (!ctx->sched_dev || grid < 1 || n_items < 1) return nullptr;
     const int key[5] = {B, H, ntile, causal, grid};
     if (memcmp(key, ctx->sched_key, sizeof(key)) == 0) {
         *rows = ctx->sched_rows;
-        return ctx->sched_rows > 0 ? ctx->sched_dev : nullptr;
+        return ctx->sched_rows > 0 ? reinterpret_cast<const int4*>(ctx->sched_dev) : nullptr;
     }
     memcpy(ctx->sched_key, key, sizeof(key));
     ctx->sched_rows = 0;
@@ -210,11 +210,20 @@ const int* deers_get_schedule(deers_ctx* ctx, int B, int H, int ntile, int causa
     }
     size_t nrows = 0;
     for (auto& v : lists) nrows = v.size() > nrows ? v.size() : nrows;
-    if (nrows * (size_t)grid > (size_t)DEERS_SCHED_CAP) return nullptr;
-    std::vector<int> table(nrows * grid, -1);
+    if (nrows * (size_t)grid * 4 > (size_t)DEERS_SCHED_CAP) return nullptr;
+    // Entry = {slot, slice, batch, head}: the kernels' single issuing threads would otherwise spend about a
+    // thousand cycles per item on the integer divisions that turn an item index into these.
+    std::vector<int4> table(nrows * grid, make_int4(-1, 0, 0, 0));
     for (int c = 0; c < grid; ++c)
-        for (size_t n = 0; n < lists[c].size(); ++n) table[n * grid + c] = lists[c][n];
-    if (cudaMemcpyAsync(ctx->sched_dev, table.data(), table.size() * sizeof(int), cudaMemcpyHostToDevice, ctx->stream) !=
+        for (size_t n = 0; n < lists[c].size(); ++n) {
+            const long long w = lists[c][n];
+            const int group = (int)(w / (16LL * ntile));
+            const int gsize = BH - group * 16 < 16 ? BH - group * 16 : 16;
+            const int within = (int)(w - (long long)group * 16 * ntile);
+            const int bh = group * 16 + within % gsize;
+            table[n * grid + c] = make_int4(within / gsize, bh, bh / H, bh % H);
+        }
+    if (cudaMemcpyAsync(ctx->sched_dev, table.data(), table.size() * sizeof(int4), cudaMemcpyHostToDevice, ctx->stream) !=
             cudaSuccess ||
         cudaStreamSynchronize(ctx->stream) != cudaSuccess) {           // the host vector goes away on return
         ctx->sched_key[0] = -1;
@@ -222,7 +231,7 @@ const int* deers_get_schedule(deers_ctx* ctx, int B, int H, int ntile, int causa
     }
     ctx->sched_rows = (int)nrows;
     *rows = ctx->sched_rows;
-    return ctx->sched_dev;
+    return reinterpret_cast<const int4*>(ctx->sched_dev);
 }
 
 // ---------------------------------------------------------------------------
