@@ -314,6 +314,71 @@ def run_rmsnorm(args, B, T, H, D):
     print(json.dumps(line))
 
 
+def run_decode(args, dtype, B, T, H, D):
+    """One sampling step with a KV cache: q [B,H,1,D] against K, V [B,H,T,D]; reads K and V once."""
+    import numpy as np
+    import torch
+    from deers_b200 import _lib, ops
+    from oracle import ref
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a B200: there is no CPU fallback")
+    dev = torch.device("cuda", 0)
+    tdtype = torch.float16 if dtype == "f16" else torch.float32
+    esize = 2 if dtype == "f16" else 4
+    gen = torch.Generator(device=dev).manual_seed(31)
+    k, v = (torch.randn(B, H, T, D, device=dev, dtype=torch.float32, generator=gen).to(tdtype) for _ in range(2))
+    q = torch.randn(B, H, 1, D, device=dev, dtype=torch.float32, generator=gen).to(tdtype)
+    ctx = ops.Context.current(dev)
+    small = 2 * B * H * T * D * esize < 126e6
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if small else None
+    sampler = ClockSampler(0)
+    for _ in range(max(args.warmup, 3)):
+        ops.attention_decode(q, k, v)
+    torch.cuda.synchronize()
+    ctx.kernel_timing(True)
+    launches0 = ctx.launch_count()
+    total_ms = 0.0
+    for _ in range(args.steps):
+        if flush is not None:
+            flush.zero_()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        ops.attention_decode(q, k, v)
+        ev1.record()
+        torch.cuda.synchronize()
+        total_ms += ev0.elapsed_time(ev1)
+    ms = total_ms / args.steps
+    launches = ctx.launch_count() - launches0
+    k_ms, k_n = ctx.kernel_time(_lib.K_DECODE)
+    ctx.kernel_timing(False)
+    ctx.sync()
+    clocks = sampler.stop()
+    bytes_step = 2.0 * B * H * T * D * esize
+    peaks = load_peaks()
+    achieved = bytes_step / (k_ms / args.steps * 1e-3) / 1e9
+    ns = max(1, min(B * H, int(2e8 // (T * D))))
+    ks = np.random.default_rng(0).standard_normal((1, ns, T, D)).astype(np.float32)
+    qs = np.random.default_rng(1).standard_normal((1, ns, 1, D)).astype(np.float32)
+    ref.attn_decode(qs, ks, ks)
+    t0 = time.perf_counter()
+    ref.attn_decode(qs, ks, ks)
+    cpu_s = time.perf_counter() - t0
+    line = {"metric": "attn_decode_tokens_per_s", "value": B / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": dtype, "data": "synthetic",
+            "config": {"workload": f"{args.workload}: decode attention, one new token per slice, {dtype}, B={B} H={H} "
+                                   f"cache T={T} head_dim={D}",
+                       "l2": "256 MB flush write between steps" if small else "cache larger than L2"},
+            "gpu_launches": int(launches), "clocks": clocks, "e2e": None,
+            "roofline": {"bound": "hbm", "kernel": "decode_partial_kernel + decode_combine_kernel", "achieved": achieved,
+                         "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "traffic": None,
+                         "bytes_per_step": bytes_step, "kernel_ms_per_step": k_ms / args.steps,
+                         "peak_source": peaks["source"] + " copy bandwidth"},
+            "cpu_baseline": {"value": 2.0 * ns * T * D * 4 / cpu_s / 1e9, "unit": "GB/s", "cores": 1, "kind": "port",
+                             "sample": f"{ns} of {B * H} slices, numpy f32 restatement, {cpu_s:.3f} s"}}
+    print(json.dumps(line))
+
+
 def run_adamw(args):
     """One optimizer step of the reference's training loop: gradient norm, clip, AdamW over every parameter
     (src/optim.rs:214-297), fused into three kinds of launches."""
@@ -412,6 +477,9 @@ def main():
                          "on the workload's shape instead of attention; 1 GPU")
     ap.add_argument("--rmsnorm", action="store_true",
                     help="time the fused RMSNorm forward + backward on [B*T, H*D] f32 rows of the workload; 1 GPU")
+    ap.add_argument("--decode", action="store_true",
+                    help="time decode-time attention (one new token per slice against a cache of T rows) on the "
+                         "workload's B, H, T, head_dim instead of the training step; 1 GPU")
     ap.add_argument("--adamw", action="store_true",
                     help="time the fused multi-tensor AdamW step with the gradient-norm clip on the parameter "
                          "shapes of the reference's GPT (22 M parameters in 38 tensors) instead of attention; 1 GPU")
@@ -431,6 +499,9 @@ def main():
         return
     if args.rmsnorm:
         run_rmsnorm(args, B, T, H, D)
+        return
+    if args.decode:
+        run_decode(args, dtype, B, T, H, D)
         return
     if args.impl == "reference":
         run_reference(args, dtype, B, T, H, D)

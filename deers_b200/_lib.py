@@ -23,8 +23,9 @@ SYMBOLS = [
     "deers_b200_attn_fwd_bwd_host", "deers_b200_rope_pack",
     "deers_b200_optim_scratch_bytes", "deers_b200_grad_norm", "deers_b200_grad_clip", "deers_b200_adamw_step",
     "deers_b200_rmsnorm_fwd", "deers_b200_rmsnorm_bwd",
+    "deers_b200_attn_decode_workspace_bytes", "deers_b200_attn_decode",
 ]
-K_FWD, K_BWD_PREP, K_BWD_MAIN, K_BWD_DQ, K_ROPE, K_OPTIM, K_NORM = range(7)
+K_FWD, K_BWD_PREP, K_BWD_MAIN, K_BWD_DQ, K_ROPE, K_OPTIM, K_NORM, K_DECODE = range(8)
 
 
 class AttnDesc(ctypes.Structure):
@@ -50,6 +51,13 @@ class OptimTensor(ctypes.Structure):
 class AdamWHyper(ctypes.Structure):
     _fields_ = [("lr", ctypes.c_double), ("beta1", ctypes.c_double), ("beta2", ctypes.c_double),
                 ("eps", ctypes.c_double), ("weight_decay", ctypes.c_double), ("step", ctypes.c_int64)]
+
+
+class DecodeDesc(ctypes.Structure):
+    _fields_ = [("B", ctypes.c_int32), ("H", ctypes.c_int32), ("Tq", ctypes.c_int32), ("Tk", ctypes.c_int32),
+                ("D", ctypes.c_int32), ("dtype", ctypes.c_int32), ("causal", ctypes.c_int32), ("scale", ctypes.c_float),
+                ("q_strides", ctypes.c_int64 * 4), ("k_strides", ctypes.c_int64 * 4),
+                ("v_strides", ctypes.c_int64 * 4), ("o_strides", ctypes.c_int64 * 4)]
 
 
 _lib = None
@@ -97,6 +105,10 @@ def lib() -> ctypes.CDLL:
     L.deers_b200_adamw_step.argtypes = [vp, i32, tp, ctypes.POINTER(AdamWHyper), vp, ctypes.c_double]
     L.deers_b200_rmsnorm_fwd.argtypes = [vp, ctypes.c_int64, ctypes.c_int32, ctypes.c_double, vp, vp, vp]
     L.deers_b200_rmsnorm_bwd.argtypes = [vp, ctypes.c_int64, ctypes.c_int32, vp, vp, vp, vp]
+    ddp = ctypes.POINTER(DecodeDesc)
+    L.deers_b200_attn_decode_workspace_bytes.argtypes = [ddp]
+    L.deers_b200_attn_decode_workspace_bytes.restype = sz
+    L.deers_b200_attn_decode.argtypes = [vp, ddp, vp, vp, vp, vp, vp, vp, sz]
     L.deers_b200_status_string.argtypes = [i32]
     L.deers_b200_status_string.restype = ctypes.c_char_p
     L.deers_b200_last_error.argtypes = [vp]

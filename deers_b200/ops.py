@@ -543,3 +543,42 @@ class RMSNorm:
 def rms_norm(x, eps: float) -> torch.Tensor:
     """Module form: RMSNorm.new(x, eps).forward()."""
     return RMSNorm.new(x, eps).forward()
+
+
+# ---------------------------------------------------------------------------------------------
+# Decode-time attention against a key / value cache
+# ---------------------------------------------------------------------------------------------
+def attention_decode(q, k_cache, v_cache, scale: Optional[float] = None, causal: bool = True, want_lse: bool = False):
+    """``softmax(scale * q @ k^T + causal_mask(B, Tq, Tk - Tq)) @ v`` for Tq new rows against Tk cached rows
+    (the mask of src/nn/functional.rs:12-55 with seqlen_offset = Tk - Tq).  q: [B,H,Tq,D]; caches:
+    [B,H,Tk,D] (views of a larger cache are read in place).  Returns o [B,H,Tq,D] (and lse [B,H,Tq])."""
+    if q.dim() != 4 or k_cache.dim() != 4 or v_cache.dim() != 4:
+        raise LayoutMismatch("attention_decode: expected [B, H, T, D] tensors")
+    B, H, Tq, D = q.shape
+    Tk = k_cache.shape[2]
+    if tuple(k_cache.shape) != (B, H, Tk, D) or tuple(v_cache.shape) != (B, H, Tk, D) or Tk < Tq:
+        raise LayoutMismatch(f"attention_decode: q {tuple(q.shape)}, k {tuple(k_cache.shape)}, v {tuple(v_cache.shape)}")
+    for t in (k_cache, v_cache):
+        if t.dtype != q.dtype:
+            raise DTypeMismatch(f"attention_decode: {t.dtype} vs {q.dtype}")
+        if t.device != q.device:
+            raise DeviceMismatch(f"attention_decode: {t.device} vs {q.device}")
+    if q.dtype not in _DTYPES:
+        raise DTypeMismatch(f"attention_decode: unsupported dtype {q.dtype}")
+    if q.device.type != "cuda":
+        raise DeviceMismatch("attention_decode: the op runs on the CUDA device only")
+    q, k_cache, v_cache = (t if t.stride(3) == 1 else t.contiguous() for t in (q, k_cache, v_cache))
+    ctx = Context.current(q.device)
+    o = torch.empty_like(q, memory_format=torch.contiguous_format)
+    lse = torch.empty((B, H, Tq), dtype=torch.float32, device=q.device) if want_lse else None
+    d = _lib.DecodeDesc()
+    d.B, d.H, d.Tq, d.Tk, d.D = B, H, Tq, Tk, D
+    d.dtype, d.causal, d.scale = _DTYPES[q.dtype], int(causal), default_scale(D) if scale is None else float(scale)
+    d.q_strides, d.k_strides, d.v_strides, d.o_strides = _strides(q), _strides(k_cache), _strides(v_cache), _strides(o)
+    need = int(_lib.lib().deers_b200_attn_decode_workspace_bytes(ctypes.byref(d)))
+    ws = torch.empty(max(need, 256), dtype=torch.uint8, device=q.device)
+    _lib.check(_lib.lib().deers_b200_attn_decode(ctx.handle, ctypes.byref(d), q.data_ptr(), k_cache.data_ptr(),
+                                                 v_cache.data_ptr(), o.data_ptr(),
+                                                 lse.data_ptr() if lse is not None else None, ws.data_ptr(), need),
+               ctx.handle)
+    return (o, lse) if want_lse else o

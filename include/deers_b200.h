@@ -280,6 +280,30 @@ int deers_b200_rmsnorm_bwd(deers_ctx* ctx, int64_t rows, int32_t C, const float*
                            const float* dy, float* dx);
 
 /*
+ * Decode-time attention with a key / value cache: Tq new query rows (1 when sampling) against Tk = Tq +
+ * seqlen_offset cached key and value rows per (batch, head) slice,
+ *     O = softmax(scale * Q K^T + mask) V,   key j masked for query i iff causal and j > i + (Tk - Tq),
+ * the mask `functional::causal_mask(batch, tgt_len = Tq, seqlen_offset = Tk - Tq)` builds
+ * (`src/nn/functional.rs:12-55`).  The reference has no cache: its sampling loop re-runs the whole prefix
+ * through `GPT::forward` for every token; with this entry point a step reads K and V once (split over the
+ * keys across CTAs, merged by a second launch).  q, o: [B,H,Tq,D]; k_cache, v_cache: [B,H,Tk,D]; strides in
+ * elements, inner stride 1 (a cache allocated for more than Tk rows is passed with its own row / slice
+ * strides).  f16 or f32 storage, f32 arithmetic; D <= 256, Tq <= 128, B*H <= 65535.  lse (optional, [B,H,Tq]
+ * f32, natural log) like deers_b200_attn_fwd.  Workspace: deers_b200_attn_decode_workspace_bytes(desc)
+ * of device memory.  Enqueued on the context's stream; no allocation, no synchronisation.
+ */
+typedef struct deers_decode_desc {
+    int32_t B, H, Tq, Tk, D;
+    int32_t dtype;            /* DEERS_F16 / DEERS_F32 */
+    int32_t causal;
+    float scale;
+    int64_t q_strides[4], k_strides[4], v_strides[4], o_strides[4];
+} deers_decode_desc;
+size_t deers_b200_attn_decode_workspace_bytes(const deers_decode_desc* desc);
+int deers_b200_attn_decode(deers_ctx* ctx, const deers_decode_desc* desc, const void* q, const void* k_cache,
+                           const void* v_cache, void* o, float* lse, void* workspace, size_t workspace_bytes);
+
+/*
  * Status text, the way backend failures become `Error::Cuda(String)`
  * (`src/error.rs:40-41`).  last_error adds the detail of the most recent failure
  * on this context (CUDA error string, or which kernel wait gave up).
@@ -301,7 +325,7 @@ uint64_t deers_b200_launch_count(deers_ctx* ctx);
  * milliseconds and the number of launches of one kernel kind since timing was
  * enabled (or since the last call with reset != 0).
  */
-enum { DEERS_K_FWD = 0, DEERS_K_BWD_PREP = 1, DEERS_K_BWD_MAIN = 2, DEERS_K_BWD_DQ = 3, DEERS_K_ROPE = 4, DEERS_K_OPTIM = 5, DEERS_K_NORM = 6, DEERS_K_COUNT = 7 };
+enum { DEERS_K_FWD = 0, DEERS_K_BWD_PREP = 1, DEERS_K_BWD_MAIN = 2, DEERS_K_BWD_DQ = 3, DEERS_K_ROPE = 4, DEERS_K_OPTIM = 5, DEERS_K_NORM = 6, DEERS_K_DECODE = 7, DEERS_K_COUNT = 8 };
 int deers_b200_kernel_timing(deers_ctx* ctx, int enable);
 int deers_b200_kernel_time(deers_ctx* ctx, int kind, int reset, double* total_ms, uint64_t* launches);
 

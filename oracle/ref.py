@@ -193,3 +193,20 @@ def rmsnorm(x, eps: float, dy=None):
     dx = np.empty_like(x)
     lib().ref_rmsnorm(_p(x), rows, C, eps, _p(dy), _p(y), _p(dx))
     return y, dx
+
+
+def attn_decode(q, k, v, scale=None, causal=True):
+    """Tq query rows against Tk >= Tq key / value rows, f32, the op chain of gpt.rs:139-144 with the additive
+    mask of functional.rs:12-55 at seqlen_offset = Tk - Tq (the pinned ref_causal_mask); returns (o, lse)."""
+    q, k, v = (np.ascontiguousarray(a, dtype=np.float32) for a in (q, k, v))
+    B, H, Tq, D = q.shape
+    Tk = k.shape[2]
+    scale = default_scale(D) if scale is None else scale
+    s = np.einsum("bhid,bhjd->bhij", q, k).astype(np.float32) * np.float32(scale)
+    if causal:
+        s = s + causal_mask(B, Tq, Tk - Tq)
+    m = s.max(axis=3, keepdims=True)
+    e = np.exp(s - m)
+    lse = (np.log(e.sum(axis=3, keepdims=True, dtype=np.float32)) + m).astype(np.float32)
+    p = np.exp(s - lse).astype(np.float32)
+    return np.einsum("bhij,bhjd->bhid", p, v).astype(np.float32), lse[..., 0]

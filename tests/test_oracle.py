@@ -173,3 +173,17 @@ def test_rmsnorm_oracle_matches_golden():
         # every output row has mean square 1 (up to eps)
         if c["x"].shape[1] > 1:
             assert np.allclose((y.astype(np.float64) ** 2).mean(1), 1.0, atol=1e-3)
+
+
+def test_decode_oracle_agrees_with_the_square_oracle():
+    # Tq == Tk reduces to the causal forward; with Tq < Tk the rows equal the last rows of the square case.
+    rng = np.random.default_rng(2)
+    B, H, T, D = 1, 2, 12, 8
+    q, k, v = (rng.standard_normal((B, H, T, D)).astype(np.float32) for _ in range(3))
+    o_sq, lse_sq = ref.attn_fwd(q, k, v)
+    o_d, lse_d = ref.attn_decode(q, k, v)
+    assert_close(o_d, o_sq, TOL_F32, "square o")
+    assert_close(lse_d, lse_sq, TOL_F32, "square lse")
+    o_tail, lse_tail = ref.attn_decode(q[:, :, -3:], k, v)
+    assert_close(o_tail, o_sq[:, :, -3:], TOL_F32, "tail o")
+    assert_close(lse_tail, lse_sq[:, :, -3:], TOL_F32, "tail lse")
