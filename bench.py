@@ -657,9 +657,9 @@ def main():
         roofline = None
         if dtype == "f16":
             achieved = dkdv_flops / (bwd_avg * 1e-3) / 1e12
-            # DRAM traffic of this kernel from the ncu capture summarised in
-            # profiles/attn_f16_kernels_B8_T2048_H16_D128.md (374.8 MB for 128 slices of T=2048, D=128),
-            # scaled by the slices one launch processes; traffic is proportional to the slice count.
+            # DRAM traffic of this kernel from an ncu capture of a small case (376.0 MB for the 128 slices of
+            # B=8, H=16 at T=2048, D=128; summary under profiles/), scaled by the slices one launch
+            # processes; traffic is proportional to the slice count.
             traffic = 376.0e6 / 128 * n_local if (T == 2048 and D == 128) else None
             roofline = {"bound": "tensor", "kernel": "attn_bwd_dkdv_f16_kernel", "achieved": achieved, "peak": peak,
                         "unit": UNIT, "frac": achieved / peak, "traffic": traffic,

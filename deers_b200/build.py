@@ -1,7 +1,6 @@
 """Builds ``libdeers_b200.so`` in-tree with nvcc for sm_100a.
 
-These are the same commands a ``build.rs`` on the deers side would run; see
-INTEGRATION.md.  Usage: ``python -m deers_b200.build [--force] [--verbose]``.
+These are the same commands a ``build.rs`` on the deers side would run.  Usage: ``python -m deers_b200.build [--force] [--verbose]``.
 """
 from __future__ import annotations
 
@@ -45,6 +44,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         objs.append(o)
         if force or _stale(o, [s] + headers):
             trace = os.environ.get("DEERS_TRACE")      # development aid: per-iteration clock stamps
+            # DEERS_NVCC_EXTRA: extra nvcc flags (development aid: -D switches of the kernels)
             cmd = [_nvcc()] + [f for f in NVCC_FLAGS if not f.startswith("--use_fast_math")] + \
                   ([f"-DDEERS_TRACE={trace}"] if trace else []) + \
                   os.environ.get("DEERS_NVCC_EXTRA", "").split() + \
