@@ -379,6 +379,71 @@ def run_decode(args, dtype, B, T, H, D):
     print(json.dumps(line))
 
 
+def run_gemm(args):
+    """Linear forward y = x W on the tcgen05 GEMM, with torch.matmul (cuBLAS) timed beside it for context."""
+    import numpy as np
+    import torch
+    from deers_b200 import _lib, ops
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a B200: there is no CPU fallback")
+    M, N, K = (int(v) for v in args.gemm.split(","))
+    dev = torch.device("cuda", 0)
+    gen = torch.Generator(device=dev).manual_seed(5)
+    x = torch.randn(M, K, device=dev, generator=gen).to(torch.float16)
+    w = (torch.randn(K, N, device=dev, generator=gen) / K ** 0.5).to(torch.float16)
+    ctx = ops.Context.current(dev)
+    op = ops.Linear.new(x, w)
+    sampler = ClockSampler(0)
+    for _ in range(max(args.warmup, 3)):
+        op.forward()
+    torch.cuda.synchronize()
+    ctx.kernel_timing(True)
+    launches0 = ctx.launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(args.steps):
+        op.forward()
+    ev1.record()
+    torch.cuda.synchronize()
+    ms = ev0.elapsed_time(ev1) / args.steps
+    launches = ctx.launch_count() - launches0
+    k_ms, k_n = ctx.kernel_time(_lib.K_GEMM)
+    ctx.kernel_timing(False)
+    ctx.sync()
+    clocks = sampler.stop()
+    for _ in range(3):
+        torch.matmul(x, w)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        torch.matmul(x, w)
+    e1.record()
+    torch.cuda.synchronize()
+    lib_ms = e0.elapsed_time(e1) / args.steps
+    flops = 2.0 * M * N * K
+    peaks = load_peaks()
+    achieved = flops / (k_ms / max(k_n, 1) * 1e-3) / 1e12
+    xs, ws_ = x[:min(M, 2048)].float().cpu().numpy(), w.float().cpu().numpy()
+    t0 = time.perf_counter()
+    xs @ ws_
+    cpu_s = time.perf_counter() - t0
+    line = {"metric": "gemm_f16_tflops", "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": 1,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": f"Linear forward y[{M},{N}] = x[{M},{K}] W[{K},{N}], f16 in / f32 accumulate / f16 out",
+                       "l2": "operands larger than L2" if (M * K + K * N + M * N) * 2 > 126e6 else "operands fit L2",
+                       "library_gemm_tflops_for_context": flops / (lib_ms * 1e-3) / 1e12},
+            "gpu_launches": int(launches), "clocks": clocks, "e2e": None,
+            "roofline": {"bound": "tensor", "kernel": "gemm_f16_kernel", "achieved": achieved, "peak": peaks["tflops_burst"],
+                         "unit": "TFLOP/s", "frac": achieved / peaks["tflops_burst"], "traffic": None,
+                         "flops_per_launch": flops, "avg_launch_ms": k_ms / max(k_n, 1),
+                         "peak_source": peaks["source"] + " burst bf16 (kernel timed alone)"},
+            "cpu_baseline": {"value": 2.0 * xs.shape[0] * N * K / cpu_s / 1e12, "unit": "TFLOP/s", "cores": os.cpu_count(),
+                             "kind": "port", "sample": f"{xs.shape[0]} of {M} rows, numpy f32 matmul, {cpu_s:.3f} s"}}
+    print(json.dumps(line))
+
+
 def run_adamw(args):
     """One optimizer step of the reference's training loop: gradient norm, clip, AdamW over every parameter
     (src/optim.rs:214-297), fused into three kinds of launches."""
@@ -480,6 +545,8 @@ def main():
     ap.add_argument("--decode", action="store_true",
                     help="time decode-time attention (one new token per slice against a cache of T rows) on the "
                          "workload's B, H, T, head_dim instead of the training step; 1 GPU")
+    ap.add_argument("--gemm", default=None, metavar="M,N,K",
+                    help="time the tcgen05 f16 GEMM y[M,N] = x[M,K] W[K,N] (Linear forward) instead of attention; 1 GPU")
     ap.add_argument("--adamw", action="store_true",
                     help="time the fused multi-tensor AdamW step with the gradient-norm clip on the parameter "
                          "shapes of the reference's GPT (22 M parameters in 38 tensors) instead of attention; 1 GPU")
@@ -502,6 +569,9 @@ def main():
         return
     if args.decode:
         run_decode(args, dtype, B, T, H, D)
+        return
+    if args.gemm:
+        run_gemm(args)
         return
     if args.impl == "reference":
         run_reference(args, dtype, B, T, H, D)

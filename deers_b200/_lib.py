@@ -23,9 +23,9 @@ SYMBOLS = [
     "deers_b200_attn_fwd_bwd_host", "deers_b200_rope_pack",
     "deers_b200_optim_scratch_bytes", "deers_b200_grad_norm", "deers_b200_grad_clip", "deers_b200_adamw_step",
     "deers_b200_rmsnorm_fwd", "deers_b200_rmsnorm_bwd",
-    "deers_b200_attn_decode_workspace_bytes", "deers_b200_attn_decode",
+    "deers_b200_attn_decode_workspace_bytes", "deers_b200_attn_decode", "deers_b200_gemm_f16",
 ]
-K_FWD, K_BWD_PREP, K_BWD_MAIN, K_BWD_DQ, K_ROPE, K_OPTIM, K_NORM, K_DECODE = range(8)
+K_FWD, K_BWD_PREP, K_BWD_MAIN, K_BWD_DQ, K_ROPE, K_OPTIM, K_NORM, K_DECODE, K_GEMM = range(9)
 
 
 class AttnDesc(ctypes.Structure):
@@ -109,6 +109,8 @@ def lib() -> ctypes.CDLL:
     L.deers_b200_attn_decode_workspace_bytes.argtypes = [ddp]
     L.deers_b200_attn_decode_workspace_bytes.restype = sz
     L.deers_b200_attn_decode.argtypes = [vp, ddp, vp, vp, vp, vp, vp, vp, sz]
+    i64 = ctypes.c_int64
+    L.deers_b200_gemm_f16.argtypes = [vp, i32, i32, i32, vp, i64, i32, vp, i64, i32, vp, i64]
     L.deers_b200_status_string.argtypes = [i32]
     L.deers_b200_status_string.restype = ctypes.c_char_p
     L.deers_b200_last_error.argtypes = [vp]

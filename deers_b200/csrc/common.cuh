@@ -79,6 +79,7 @@ enum {
     DEERS_KERR_FWD_F16 = 0x100,
     DEERS_KERR_BWD_F16 = 0x200,
     DEERS_KERR_SELFTEST = 0x300,
+    DEERS_KERR_GEMM = 0x400,
 };
 
 // Work schedule shared by the persistent f16 kernels (ctx.cu).  Work items are ordered in groups

@@ -582,3 +582,58 @@ def attention_decode(q, k_cache, v_cache, scale: Optional[float] = None, causal:
                                                  lse.data_ptr() if lse is not None else None, ws.data_ptr(), need),
                ctx.handle)
     return (o, lse) if want_lse else o
+
+
+# ---------------------------------------------------------------------------------------------
+# Linear projections (f16): forward and the two backward products on the tcgen05 GEMM
+# ---------------------------------------------------------------------------------------------
+def _gemm(M, N, K, a, a_mn, b, b_mn, dev, dtype):
+    ctx = Context.current(dev)
+    c = torch.empty((M, N), dtype=dtype, device=dev)
+    _lib.check(_lib.lib().deers_b200_gemm_f16(ctx.handle, M, N, K, a.data_ptr(), a.stride(0), int(a_mn), b.data_ptr(),
+                                              b.stride(0), int(b_mn), c.data_ptr(), c.stride(0)), ctx.handle)
+    return c
+
+
+class Linear:
+    """``x.matmul(weight)`` of `Linear::forward` (src/nn.rs:184-190; weight is [in_features, out_features])
+    as a TensorOp-style node whose backward accumulates dx = dy @ W^T and dW = x^T @ dy
+    (src/ops.rs:1089-1101).  f16 tensors on the CUDA device; x is [..., in_features]."""
+
+    def __init__(self, x, weight):
+        self.x, self.weight = x, weight
+
+    @classmethod
+    def new(cls, x, weight) -> "Linear":
+        if weight.dim() != 2 or x.dim() < 1 or x.shape[-1] != weight.shape[0]:
+            raise LayoutMismatch(f"Linear: x {tuple(x.shape)} vs weight {tuple(weight.shape)}")
+        if x.dtype != torch.float16 or weight.dtype != torch.float16:
+            raise DTypeMismatch(f"Linear: f16 only on this path, got {x.dtype} / {weight.dtype}")
+        if x.device.type != "cuda" or weight.device != x.device:
+            raise DeviceMismatch("Linear: tensors must live on the same CUDA device")
+        if weight.shape[0] % 8 or weight.shape[1] % 8:
+            raise LayoutMismatch("Linear: in_features and out_features must be multiples of 8 (16-byte rows)")
+        return cls(x if x.is_contiguous() else x.contiguous(), weight if weight.is_contiguous() else weight.contiguous())
+
+    def forward(self) -> torch.Tensor:
+        K, N = self.weight.shape
+        x2 = self.x.reshape(-1, K)
+        y = _gemm(x2.shape[0], N, K, x2, False, self.weight, True, self.x.device, self.x.dtype)
+        return y.reshape(*self.x.shape[:-1], N)
+
+    def backward(self, grads: GradientStore, out_grad: torch.Tensor) -> None:
+        K, N = self.weight.shape
+        x2 = self.x.reshape(-1, K)
+        g2 = out_grad.reshape(-1, N)
+        g2 = g2 if g2.is_contiguous() else g2.contiguous()
+        rows = x2.shape[0]
+        dx = _gemm(rows, K, N, g2, False, self.weight, False, self.x.device, self.x.dtype)
+        dw = _gemm(K, N, rows, x2, True, g2, True, self.x.device, self.x.dtype)
+        grads.accumulate(self.x, dx.reshape(self.x.shape))
+        grads.accumulate(self.weight, dw)
+
+    def dependencies(self) -> List[torch.Tensor]:
+        return [self.x, self.weight]
+
+    def name(self) -> str:
+        return "Linear"

@@ -304,6 +304,22 @@ int deers_b200_attn_decode(deers_ctx* ctx, const deers_decode_desc* desc, const 
                            const void* v_cache, void* o, float* lse, void* workspace, size_t workspace_bytes);
 
 /*
+ * f16 GEMM with f32 accumulation for the projections around the attention op: C[M,N] = A * B, C row-major
+ * with leading dimension ldc.  Replaces the `cublasGemmStridedBatchedEx` call behind `Tensor::matmul`
+ * for f16 operands (`src/storage/cuda.rs:1147-1177`) as `Linear::forward` uses it (`src/nn.rs:184-190`,
+ * weight stored [in_features, out_features]) and as the matmul backward does (`src/ops.rs:1089-1101`):
+ *     a_mn_major = 0: A is stored [M][K] (K contiguous);   1: A is stored [K][M] (M contiguous)
+ *     b_mn_major = 0: B is stored [N][K] (K contiguous);   1: B is stored [K][N] (N contiguous)
+ *     forward  y  = x  W     : gemm(M=rows, N=out, K=in,  x, 0,  W, 1)
+ *     dgrad    dx = dy W^T   : gemm(M=rows, N=in,  K=out, dy, 0, W, 0)      (W read as [N'=in][K'=out])
+ *     wgrad    dW = x^T dy   : gemm(M=in,   N=out, K=rows, x, 1, dy, 1)
+ * Leading dimensions in elements, multiples of 8 (16-byte rows); N a multiple of 8; pointers 16-byte
+ * aligned (DEERS_ERR_LAYOUT otherwise).  Enqueued on the context's stream; no allocation.
+ */
+int deers_b200_gemm_f16(deers_ctx* ctx, int32_t M, int32_t N, int32_t K, const void* a, int64_t lda, int32_t a_mn_major,
+                        const void* b, int64_t ldb, int32_t b_mn_major, void* c, int64_t ldc);
+
+/*
  * Status text, the way backend failures become `Error::Cuda(String)`
  * (`src/error.rs:40-41`).  last_error adds the detail of the most recent failure
  * on this context (CUDA error string, or which kernel wait gave up).
@@ -325,7 +341,7 @@ uint64_t deers_b200_launch_count(deers_ctx* ctx);
  * milliseconds and the number of launches of one kernel kind since timing was
  * enabled (or since the last call with reset != 0).
  */
-enum { DEERS_K_FWD = 0, DEERS_K_BWD_PREP = 1, DEERS_K_BWD_MAIN = 2, DEERS_K_BWD_DQ = 3, DEERS_K_ROPE = 4, DEERS_K_OPTIM = 5, DEERS_K_NORM = 6, DEERS_K_DECODE = 7, DEERS_K_COUNT = 8 };
+enum { DEERS_K_FWD = 0, DEERS_K_BWD_PREP = 1, DEERS_K_BWD_MAIN = 2, DEERS_K_BWD_DQ = 3, DEERS_K_ROPE = 4, DEERS_K_OPTIM = 5, DEERS_K_NORM = 6, DEERS_K_DECODE = 7, DEERS_K_GEMM = 8, DEERS_K_COUNT = 9 };
 int deers_b200_kernel_timing(deers_ctx* ctx, int enable);
 int deers_b200_kernel_time(deers_ctx* ctx, int kind, int reset, double* total_ms, uint64_t* launches);
 
