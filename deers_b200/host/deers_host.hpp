@@ -253,6 +253,145 @@ inline Tensor Tensor::causal_attention(const Tensor& k, const Tensor& v, float s
     return CausalAttention::make(*this, k, v, scale)->forward();
 }
 
+// apply_rotary_emb(x, cos, sin).permute([0,2,1,3]) (src/models/gpt.rs:49-73,135-136) as one op: x is a compact
+// [B,T,H,D] tensor, cos / sin are [1,T,1,D/2] (or [T,D/2]) of the same dtype; the result is [B,H,T,D].
+class RotaryPack : public TensorOp, public std::enable_shared_from_this<RotaryPack> {
+public:
+    static std::shared_ptr<RotaryPack> make(const Tensor& x, const Tensor& cos, const Tensor& sin) {
+        const auto& s = x.layout().shape;
+        if (s.size() != 4) throw Error(Error::Kind::LayoutMismatch, "RoPE expects a 4D attention tensor");
+        if (s[3] % 2) throw Error(Error::Kind::LayoutMismatch, "RoPE requires an even head dimension");
+        if (cos.layout().shape != sin.layout().shape) throw Error(Error::Kind::LayoutMismatch, "RoPE cos/sin shapes must match");
+        if (cos.layout().size() != s[1] * (s[3] / 2)) throw Error(Error::Kind::LayoutMismatch, "RoPE cache must match sequence length and head_dim / 2");
+        if (cos.dtype() != x.dtype() || sin.dtype() != x.dtype()) throw Error(Error::Kind::DTypeMismatch, "RoPE cache dtype");
+        if (!x.layout().is_compact() || !cos.layout().is_compact() || !sin.layout().is_compact())
+            throw Error(Error::Kind::LayoutMismatch, "RotaryPack: compact inputs expected");
+        return std::shared_ptr<RotaryPack>(new RotaryPack(x, cos, sin));
+    }
+    Tensor forward() override {
+        const auto& s = x_.layout().shape;                              // [B,T,H,D]
+        const Layout out = Layout::contiguous({s[0], s[2], s[1], s[3]});
+        auto y = std::make_shared<CudaStorage>((size_t)out.size() * dtype_size(x_.dtype()), x_.dtype());
+        call(x_.storage().ptr(), x_.layout(), y->ptr(), out, false);
+        return Tensor(y, out, shared_from_this());
+    }
+    void backward(GradientStore& grads, const Tensor& out_grad) const override {
+        const auto& s = x_.layout().shape;
+        if (out_grad.layout().shape != std::vector<int64_t>{s[0], s[2], s[1], s[3]})
+            throw Error(Error::Kind::LayoutMismatch, "RotaryPack: out_grad shape");
+        const Layout dl = Layout::contiguous(s);
+        auto dx = std::make_shared<CudaStorage>((size_t)dl.size() * dtype_size(x_.dtype()), x_.dtype());
+        call(out_grad.storage().ptr(), dl, dx->ptr(), out_grad.layout(), true);
+        grads.accumulate(x_, Tensor(dx, dl));
+    }
+    std::vector<const Tensor*> dependencies() const override { return {&x_}; }
+    const char* name() const override { return "RotaryPack"; }
+
+private:
+    RotaryPack(const Tensor& x, const Tensor& cos, const Tensor& sin) : x_(x), cos_(cos), sin_(sin) {}
+    // bthd: layout of the [B,T,H,D] side; bhtd: layout of the [B,H,T,D] side; inverse reads bhtd, writes bthd.
+    void call(const void* src, const Layout& bthd, void* dst, const Layout& bhtd, bool inverse) const {
+        Runtime& rt = x_.storage().runtime();
+        const auto& s = x_.layout().shape;
+        deers_rope_desc d{};
+        d.B = (int32_t)s[0]; d.T = (int32_t)s[1]; d.H = (int32_t)s[2]; d.D = (int32_t)s[3];
+        d.dtype = (int32_t)x_.dtype(); d.inverse = inverse ? 1 : 0;
+        const int64_t a[4] = {bthd.strides[0], bthd.strides[1], bthd.strides[2], 1};          // (b, t, h, d)
+        const int64_t b[4] = {bhtd.strides[0], bhtd.strides[2], bhtd.strides[1], 1};
+        for (int i = 0; i < 4; ++i) { d.src_strides[i] = inverse ? b[i] : a[i]; d.dst_strides[i] = inverse ? a[i] : b[i]; }
+        rt.check(deers_b200_rope_pack(rt.ctx(), &d, src, cos_.storage().ptr(), sin_.storage().ptr(), dst));
+    }
+    Tensor x_, cos_, sin_;
+};
+
+// RMSNorm::forward (src/nn.rs:244-251) over the last axis of a compact f32 tensor, one launch each way.
+class RMSNorm : public TensorOp, public std::enable_shared_from_this<RMSNorm> {
+public:
+    static std::shared_ptr<RMSNorm> make(const Tensor& x, double eps) {
+        if (x.layout().shape.empty()) throw Error(Error::Kind::LayoutMismatch, "RMSNorm: needs at least one axis");
+        if (x.dtype() != DType::F32) throw Error(Error::Kind::DTypeMismatch, "RMSNorm: f32 only");
+        if (!x.layout().is_compact()) throw Error(Error::Kind::LayoutMismatch, "RMSNorm: compact input expected");
+        return std::shared_ptr<RMSNorm>(new RMSNorm(x, eps));
+    }
+    Tensor forward() override {
+        Runtime& rt = x_.storage().runtime();
+        const int64_t C = x_.layout().shape.back(), rows = x_.layout().size() / C;
+        auto y = std::make_shared<CudaStorage>((size_t)x_.layout().size() * 4, DType::F32);
+        inv_ = std::make_shared<CudaStorage>((size_t)(rows ? rows : 1) * 4, DType::F32);
+        rt.check(deers_b200_rmsnorm_fwd(rt.ctx(), rows, (int32_t)C, eps_, (const float*)x_.storage().ptr(), (float*)y->ptr(),
+                                        (float*)inv_->ptr()));
+        return Tensor(y, x_.layout(), shared_from_this());
+    }
+    void backward(GradientStore& grads, const Tensor& out_grad) const override {
+        if (!inv_) throw std::logic_error("RMSNorm::backward before forward");
+        if (out_grad.layout().shape != x_.layout().shape || !out_grad.layout().is_compact())
+            throw Error(Error::Kind::LayoutMismatch, "RMSNorm: out_grad layout");
+        Runtime& rt = x_.storage().runtime();
+        const int64_t C = x_.layout().shape.back(), rows = x_.layout().size() / C;
+        auto dx = std::make_shared<CudaStorage>((size_t)x_.layout().size() * 4, DType::F32);
+        rt.check(deers_b200_rmsnorm_bwd(rt.ctx(), rows, (int32_t)C, (const float*)x_.storage().ptr(), (const float*)inv_->ptr(),
+                                        (const float*)out_grad.storage().ptr(), (float*)dx->ptr()));
+        grads.accumulate(x_, Tensor(dx, x_.layout()));
+    }
+    std::vector<const Tensor*> dependencies() const override { return {&x_}; }
+    const char* name() const override { return "RMSNorm"; }
+
+private:
+    RMSNorm(const Tensor& x, double eps) : x_(x), eps_(eps) {}
+    Tensor x_;
+    double eps_;
+    std::shared_ptr<CudaStorage> inv_;
+};
+
+// AdamWConfig + AdamW (src/optim.rs:49-251) over compact f32 parameters, every parameter in one launch; with
+// `clip_max_norm > 0` the global gradient-norm clip of clip_grad_norm (optim.rs:257-297) is applied inside it.
+class AdamW {
+public:
+    AdamW(std::vector<Tensor> parameters, double lr, double beta1 = 0.9, double beta2 = 0.999, double eps = 1e-8,
+          double weight_decay = 0.0)
+        : params_(std::move(parameters)), lr_(lr), b1_(beta1), b2_(beta2), eps_(eps), wd_(weight_decay) {}
+    void set_lr(double lr) { lr_ = lr; }
+    double lr() const { return lr_; }
+    size_t step_count() const { return step_; }
+    void set_step_count(size_t s) { step_ = s; }
+    void step_with_grads(const GradientStore& grads, double clip_max_norm = 0.0) {
+        ++step_;
+        std::vector<deers_optim_tensor> table;
+        Runtime* rt = nullptr;
+        for (const Tensor& p : params_) {
+            const Tensor* g = grads.get(p);
+            if (!g) continue;                                           // optim.rs:221-225
+            if (p.dtype() != DType::F32 || g->dtype() != DType::F32) throw Error(Error::Kind::DTypeMismatch, "AdamW: f32 only");
+            if (!p.layout().is_compact() || !g->layout().is_compact() || g->layout().shape != p.layout().shape)
+                throw Error(Error::Kind::LayoutMismatch, "AdamW: compact parameters and gradients of equal shape expected");
+            rt = &p.storage().runtime();
+            auto& mv = state_[p.id()];
+            if (!mv.first) {                                            // param.zeros_like()
+                const std::vector<float> zeros((size_t)p.layout().size(), 0.f);
+                mv.first = Tensor::from_vec(zeros, p.layout().shape, DType::F32).storage_ptr();
+                mv.second = Tensor::from_vec(zeros, p.layout().shape, DType::F32).storage_ptr();
+            }
+            table.push_back({p.storage().ptr(), g->storage().ptr(), mv.first->ptr(), mv.second->ptr(), p.layout().size()});
+        }
+        if (table.empty()) return;
+        const deers_adamw_hyper h{lr_, b1_, b2_, eps_, wd_, (int64_t)step_};
+        if (clip_max_norm > 0.0) {
+            CudaStorage norm(4, DType::F32), scratch(deers_b200_optim_scratch_bytes(), DType::F32);
+            rt->check(deers_b200_grad_norm(rt->ctx(), (int)table.size(), table.data(), (float*)norm.ptr(), scratch.ptr(), scratch.bytes()));
+            rt->check(deers_b200_adamw_step(rt->ctx(), (int)table.size(), table.data(), &h, (const float*)norm.ptr(), clip_max_norm));
+            rt->synchronize();                                          // norm / scratch are freed on return
+        } else {
+            rt->check(deers_b200_adamw_step(rt->ctx(), (int)table.size(), table.data(), &h, nullptr, 0.0));
+        }
+    }
+
+private:
+    std::vector<Tensor> params_;
+    double lr_, b1_, b2_, eps_, wd_;
+    size_t step_ = 0;
+    std::map<uint64_t, std::pair<std::shared_ptr<CudaStorage>, std::shared_ptr<CudaStorage>>> state_;
+};
+
 // Tensor::backward for a graph that consists of this one op (src/backprop.rs:52-66 walks the
 // sorted nodes and calls op.backward for each).
 inline GradientStore backward(const Tensor& out, const Tensor& out_grad) {

@@ -10,6 +10,12 @@
 extern "C" int ref_attn_fwd_bwd(const float* q, const float* k, const float* v, const float* d_o, int B, int H, int T,
                                 int D, float scale, int causal, float* o, float* lse, float* dq, float* dk, float* dv);
 
+extern "C" void ref_rope_pack(const float* x, const float* cosv, const float* sinv, int B, int T, int H, int D, int inverse,
+                              float* y);
+extern "C" void ref_rmsnorm(const float* x, long long rows, int C, double eps, const float* dy, float* y, float* dx);
+extern "C" void ref_adamw_step(float* w, const float* g, float* m, float* v, long long n, double lr, double beta1,
+                               double beta2, double eps, double weight_decay, int step);
+
 static float max_rel(const std::vector<float>& got, const std::vector<float>& want) {
     float err = 0.f, mx = 1e-30f;
     for (size_t i = 0; i < want.size(); ++i) {
@@ -68,9 +74,76 @@ static int run_case(deers::DType dtype, int B, int H, int T, int D, float tol) {
     return ok ? 0 : 1;
 }
 
+// The other ops of the mirror (rotary pack, RMSNorm, AdamW) against the oracle's restatements, f32.
+static int run_other_ops() {
+    int fails = 0;
+    std::mt19937 rng(99);
+    std::normal_distribution<float> dist(0.f, 1.f);
+    {   // RotaryPack: bit-exact forward and backward
+        const int B = 2, T = 9, H = 3, D = 16;
+        std::vector<float> x((size_t)B * T * H * D), dy(x.size()), cs((size_t)T * D / 2), sn(cs.size());
+        for (auto& v : x) v = dist(rng);
+        for (auto& v : dy) v = dist(rng);
+        for (int t = 0; t < T; ++t)
+            for (int i = 0; i < D / 2; ++i) {
+                const float f = (float)t * (1.0f / std::pow(10000.0f, (float)(2 * i) / (float)D));
+                cs[(size_t)t * D / 2 + i] = std::cos(f); sn[(size_t)t * D / 2 + i] = std::sin(f);
+            }
+        std::vector<float> want_y(x.size()), want_dx(x.size());
+        ref_rope_pack(x.data(), cs.data(), sn.data(), B, T, H, D, 0, want_y.data());
+        ref_rope_pack(dy.data(), cs.data(), sn.data(), B, T, H, D, 1, want_dx.data());
+        auto tx = deers::Tensor::from_vec(x, {B, T, H, D}, deers::DType::F32);
+        auto tc = deers::Tensor::from_vec(cs, {1, T, 1, D / 2}, deers::DType::F32);
+        auto ts = deers::Tensor::from_vec(sn, {1, T, 1, D / 2}, deers::DType::F32);
+        auto y = deers::RotaryPack::make(tx, tc, ts)->forward();
+        auto grads = deers::backward(y, deers::Tensor::from_vec(dy, {B, H, T, D}, deers::DType::F32));
+        deers::Runtime::get().synchronize();
+        const bool ok = y.to_vec<float>() == want_y && grads.get(tx)->to_vec<float>() == want_dx &&
+                        std::string(y.op()->name()) == "RotaryPack";
+        std::printf("%s RotaryPack bit-exact\n", ok ? "PASS" : "FAIL");
+        fails += !ok;
+    }
+    {   // RMSNorm
+        const int rows = 37, C = 192;
+        std::vector<float> x((size_t)rows * C), dy(x.size()), wy(x.size()), wdx(x.size());
+        for (auto& v : x) v = dist(rng);
+        for (auto& v : dy) v = dist(rng);
+        ref_rmsnorm(x.data(), rows, C, 1e-6, dy.data(), wy.data(), wdx.data());
+        auto tx = deers::Tensor::from_vec(x, {rows, C}, deers::DType::F32);
+        auto y = deers::RMSNorm::make(tx, 1e-6)->forward();
+        auto grads = deers::backward(y, deers::Tensor::from_vec(dy, {rows, C}, deers::DType::F32));
+        deers::Runtime::get().synchronize();
+        const float e1 = max_rel(y.to_vec<float>(), wy), e2 = max_rel(grads.get(tx)->to_vec<float>(), wdx);
+        const bool ok = e1 <= 1e-5f && e2 <= 1e-5f;
+        std::printf("%s RMSNorm y %.2e dx %.2e\n", ok ? "PASS" : "FAIL", e1, e2);
+        fails += !ok;
+    }
+    {   // AdamW: three steps, bit-exact
+        const int n = 5000;
+        std::vector<float> w(n), m(n, 0.f), v(n, 0.f);
+        for (auto& e : w) e = dist(rng);
+        auto tw = deers::Tensor::from_vec(w, {n}, deers::DType::F32);
+        deers::AdamW opt({tw}, 1e-3, 0.9, 0.95, 1e-8, 0.1);
+        for (int step = 1; step <= 3; ++step) {
+            std::vector<float> g(n);
+            for (auto& e : g) e = dist(rng);
+            deers::GradientStore grads;
+            grads.accumulate(tw, deers::Tensor::from_vec(g, {n}, deers::DType::F32));
+            opt.step_with_grads(grads);
+            ref_adamw_step(w.data(), g.data(), m.data(), v.data(), n, 1e-3, 0.9, 0.95, 1e-8, 0.1, step);
+        }
+        deers::Runtime::get().synchronize();
+        const bool ok = tw.to_vec<float>() == w && opt.step_count() == 3;
+        std::printf("%s AdamW bit-exact\n", ok ? "PASS" : "FAIL");
+        fails += !ok;
+    }
+    return fails;
+}
+
 int main() {
     int fails = 0;
     try {
+        fails += run_other_ops();
         fails += run_case(deers::DType::F32, 2, 3, 96, 32, 1e-4f);
         fails += run_case(deers::DType::F16, 2, 2, 300, 128, 2e-2f);
         fails += run_case(deers::DType::F16, 1, 3, 200, 64, 2e-2f);
