@@ -154,12 +154,21 @@ def workspace_bytes(q, scale: float = 1.0, causal: bool = True, pass_: int = 1) 
     return int(_lib.lib().deers_b200_attn_workspace_bytes(ctypes.byref(d), pass_))
 
 
-def attention_bwd(q, k, v, o, lse, d_o, scale: float, causal: bool = True, workspace: Optional[torch.Tensor] = None):
-    """Storage-level backward: returns (dq, dk, dv), each compact [B,H,T,D]."""
+def attention_bwd(q, k, v, o, lse, d_o, scale: float, causal: bool = True, workspace: Optional[torch.Tensor] = None,
+                  dv_out: Optional[torch.Tensor] = None):
+    """Storage-level backward: returns (dq, dk, dv), each compact [B,H,T,D].  `dv_out` (a [B,H,T,D] view
+    with inner stride 1, e.g. the v slice of a fused dqkv buffer seen head-major) receives dV in place
+    instead: the kernels write through its strides."""
     _check_inputs("attention_bwd", (q, k, v, o, d_o))
     q, k, v, o, d_o = _compact(q), _compact(k), _compact(v), _compact(o), _compact(d_o)
     ctx = Context.current(q.device)
-    dq, dk, dv = (torch.empty(q.shape, dtype=q.dtype, device=q.device) for _ in range(3))
+    dq, dk = (torch.empty(q.shape, dtype=q.dtype, device=q.device) for _ in range(2))
+    if dv_out is not None:
+        if tuple(dv_out.shape) != tuple(q.shape) or dv_out.dtype != q.dtype or not _usable(dv_out):
+            raise LayoutMismatch("attention_bwd: dv_out must be a [B,H,T,D] view with inner stride 1 and aligned rows")
+        dv = dv_out
+    else:
+        dv = torch.empty(q.shape, dtype=q.dtype, device=q.device)
     d = _desc(q, k, v, o, d_o, dq, dk, dv, scale=scale, causal=causal)
     need = int(_lib.lib().deers_b200_attn_workspace_bytes(ctypes.byref(d), 1))
     if workspace is None or workspace.numel() * workspace.element_size() < need:
@@ -245,14 +254,21 @@ class RotaryPack:
         _rope_call(self.x, self.cos, self.sin, y, self.x.stride(), (ys[0], ys[2], ys[1], ys[3]), B, T, H, D, False)
         return y
 
-    def backward(self, grads: "GradientStore", out_grad: torch.Tensor) -> None:
+    def backward(self, grads: "GradientStore", out_grad: torch.Tensor, dx_out: Optional[torch.Tensor] = None) -> None:
+        """`dx_out` (a [B,T,H,D] view with inner stride 1, e.g. the q slice of a fused dqkv buffer) receives
+        the gradient in place instead of a fresh tensor."""
         B, T, H, D = self.x.shape
         if tuple(out_grad.shape) != (B, H, T, D):
             raise LayoutMismatch(f"RotaryPack.backward: gradient {tuple(out_grad.shape)} vs {(B, H, T, D)}")
         if out_grad.dtype != self.x.dtype:
             raise DTypeMismatch(f"RotaryPack.backward: {out_grad.dtype} vs {self.x.dtype}")
         g = out_grad if out_grad.stride(3) == 1 else out_grad.contiguous()
-        dx = torch.empty((B, T, H, D), dtype=self.x.dtype, device=self.x.device)
+        if dx_out is not None:
+            if tuple(dx_out.shape) != (B, T, H, D) or dx_out.dtype != self.x.dtype or dx_out.stride(3) != 1:
+                raise LayoutMismatch("RotaryPack.backward: dx_out must be a [B,T,H,D] view with inner stride 1")
+            dx = dx_out
+        else:
+            dx = torch.empty((B, T, H, D), dtype=self.x.dtype, device=self.x.device)
         gs = g.stride()
         _rope_call(g, self.cos, self.sin, dx, (gs[0], gs[2], gs[1], gs[3]), dx.stride(), B, T, H, D, True)
         grads.accumulate(self.x, dx)
