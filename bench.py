@@ -444,6 +444,85 @@ def run_gemm(args):
     print(json.dumps(line))
 
 
+def run_block(args, B, T, H, D):
+    """The attention block of src/models/gpt.rs:118-147 in f16 on this library's kernels, forward + backward."""
+    import torch
+    from deers_b200 import _lib, ops
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a B200: there is no CPU fallback")
+    dev = torch.device("cuda", 0)
+    C = H * D
+    gen = torch.Generator(device=dev).manual_seed(17)
+    h16 = lambda *shape, s=1.0: (torch.randn(*shape, device=dev, generator=gen) * s).to(torch.float16)
+    x, dy = h16(B, T, C), h16(B, T, C)
+    wqkv, wo = h16(C, 3 * C, s=C ** -0.5), h16(C, C, s=C ** -0.5)
+    cos, sin = (c.to(dev) for c in ops.precompute_rotary_embeddings(T, D, dtype=torch.float16))
+    ctx = ops.Context.current(dev)
+    ws = torch.empty(max(ops.workspace_bytes(torch.empty(B, H, T, D, dtype=torch.float16, device=dev)), 256),
+                     dtype=torch.uint8, device=dev)
+
+    def step():
+        lin_qkv = ops.Linear.new(x, wqkv)
+        qkv = lin_qkv.forward()
+        q4, k4, v4 = (qkv[..., i * C:(i + 1) * C].view(B, T, H, D) for i in range(3))
+        rq, rk = ops.RotaryPack.new(q4, cos, sin), ops.RotaryPack.new(k4, cos, sin)
+        qh, kh, vh = rq.forward(), rk.forward(), v4.permute(0, 2, 1, 3)
+        att = ops.CausalAttention.new(qh, kh, vh, token_major_out=True)
+        o = att.forward()
+        y_att = o.permute(0, 2, 1, 3).reshape(B, T, C)
+        lin_o = ops.Linear.new(y_att, wo)
+        lin_o.forward()
+        grads = ops.GradientStore()
+        lin_o.backward(grads, dy)
+        d_att = grads.get(y_att).view(B, T, H, D).permute(0, 2, 1, 3)
+        dqkv = torch.empty_like(qkv)
+        dq4, dk4, dv4 = (dqkv[..., i * C:(i + 1) * C].view(B, T, H, D) for i in range(3))
+        dqh, dkh, _ = ops.attention_bwd(qh, kh, vh, att.o, att.lse, d_att, att.scale, True, workspace=ws,
+                                        dv_out=dv4.permute(0, 2, 1, 3))
+        rq.backward(grads, dqh, dx_out=dq4)
+        rk.backward(grads, dkh, dx_out=dk4)
+        lin_qkv.backward(grads, dqkv)
+
+    sampler = ClockSampler(0)
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    ctx.kernel_timing(True)
+    launches0 = ctx.launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(args.steps):
+        step()
+    ev1.record()
+    torch.cuda.synchronize()
+    ms = ev0.elapsed_time(ev1) / args.steps
+    launches = ctx.launch_count() - launches0
+    kinds = (("gemm", _lib.K_GEMM), ("rope", _lib.K_ROPE), ("attn_fwd", _lib.K_FWD), ("attn_bwd_prep", _lib.K_BWD_PREP),
+             ("attn_bwd_dkdv", _lib.K_BWD_MAIN), ("attn_bwd_dq", _lib.K_BWD_DQ))
+    kernels = {name: ctx.kernel_time(kind)[0] / args.steps for name, kind in kinds}
+    ctx.kernel_timing(False)
+    ctx.sync()
+    clocks = sampler.stop()
+    tokens = B * T
+    gemm_flops = 3 * 2.0 * tokens * C * (3 * C + C)                 # forward, dgrad, wgrad of both projections
+    attn_flops = flops_fwd_bwd(B * H, T, D)
+    peaks = load_peaks()
+    achieved = (gemm_flops + attn_flops) / (sum(kernels.values()) * 1e-3) / 1e12
+    line = {"metric": "attention_block_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": f"{args.workload}: attention block forward + backward, f16, B={B} T={T} H={H} head_dim={D} "
+                                   f"(C={C}): fused qkv GEMM, rotary pack, causal attention, output projection",
+                       "flops_per_step": gemm_flops + attn_flops, "gemm_flops": gemm_flops, "attention_flops": attn_flops,
+                       "l2": "tensors larger than L2" if tokens * C * 2 > 126e6 else "tensors fit L2"},
+            "gpu_launches": int(launches), "clocks": clocks, "e2e": None, "kernels_ms_per_step": kernels,
+            "roofline": {"bound": "tensor", "kernel": "all kernels of the block", "achieved": achieved,
+                         "peak": peaks["tflops_sustained"], "unit": "TFLOP/s", "frac": achieved / peaks["tflops_sustained"],
+                         "traffic": None, "peak_source": peaks["source"] + " sustained bf16"},
+            "cpu_baseline": None}
+    print(json.dumps(line))
+
+
 def run_adamw(args):
     """One optimizer step of the reference's training loop: gradient norm, clip, AdamW over every parameter
     (src/optim.rs:214-297), fused into three kinds of launches."""
@@ -547,6 +626,9 @@ def main():
                          "workload's B, H, T, head_dim instead of the training step; 1 GPU")
     ap.add_argument("--gemm", default=None, metavar="M,N,K",
                     help="time the tcgen05 f16 GEMM y[M,N] = x[M,K] W[K,N] (Linear forward) instead of attention; 1 GPU")
+    ap.add_argument("--block", action="store_true",
+                    help="time the whole f16 attention block (fused qkv GEMM, rotary pack, attention, output projection) "
+                         "forward + backward on the workload's B, T, H, head_dim; 1 GPU")
     ap.add_argument("--adamw", action="store_true",
                     help="time the fused multi-tensor AdamW step with the gradient-norm clip on the parameter "
                          "shapes of the reference's GPT (22 M parameters in 38 tensors) instead of attention; 1 GPU")
@@ -572,6 +654,9 @@ def main():
         return
     if args.gemm:
         run_gemm(args)
+        return
+    if args.block:
+        run_block(args, B, T, H, D)
         return
     if args.impl == "reference":
         run_reference(args, dtype, B, T, H, D)
