@@ -614,6 +614,8 @@ def main():
                          "timed step.  Default none: gradients and O stay sharded, as a training step needs them; "
                          "the gather's cost is measured separately and reported under config.gather_probe")
     ap.add_argument("--e2e-steps", type=int, default=5)
+    ap.add_argument("--e2e-chunk-mb", type=int, default=128,
+                    help="input bytes (Q,K,V,dO together) per chunk of the pipelined host call, in MiB")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--rope", action="store_true",
@@ -777,7 +779,7 @@ def main():
         host_out = tuple(torch.empty(q.shape, dtype=tdtype, pin_memory=True) for _ in range(4)) + \
                    (torch.empty(q.shape[:3], dtype=torch.float32, pin_memory=True),)
         nbytes = q.numel() * esize
-        chunk = max(1, min(n_local, (128 << 20) // max(4 * T * D * esize, 1)))        # ~128 MB of inputs per chunk
+        chunk = max(1, min(n_local, (args.e2e_chunk_mb << 20) // max(4 * T * D * esize, 1)))
         dsc = _lib.AttnDesc()
         _lib.lib().deers_b200_attn_desc_compact(dsc, Bs, Hs, T, D, _lib.F16 if dtype == "f16" else _lib.F32, 1, scale)
         scratch = torch.empty(int(_lib.lib().deers_b200_attn_host_scratch_bytes(dsc, chunk)), dtype=torch.uint8, device=dev)
