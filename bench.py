@@ -458,7 +458,7 @@ def run_block(args, B, T, H, D):
     wqkv, wo = h16(C, 3 * C, s=C ** -0.5), h16(C, C, s=C ** -0.5)
     cos, sin = (c.to(dev) for c in ops.precompute_rotary_embeddings(T, D, dtype=torch.float16))
     ctx = ops.Context.current(dev)
-    ws = torch.empty(max(ops.workspace_bytes(torch.empty(B, H, T, D, dtype=torch.float16, device=dev)), 256),
+    ws = torch.empty(max(ops.workspace_bytes(torch.empty(B, H, T, D, dtype=torch.float16, device=dev), pass_=2), 256),
                      dtype=torch.uint8, device=dev)
 
     def step():
@@ -613,6 +613,9 @@ def main():
                     help="N>1: include an all-gather of O over NCCL (side stream, overlapping the backward) in the "
                          "timed step.  Default none: gradients and O stay sharded, as a training step needs them; "
                          "the gather's cost is measured separately and reported under config.gather_probe")
+    ap.add_argument("--bwd", default="keep-ds", choices=["keep-ds", "recompute"],
+                    help="f16 backward: keep the dS tiles in the workspace between its kernels (default), or "
+                         "recompute S and dP in the dQ kernel (workspace of a few MB)")
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--e2e-chunk-mb", type=int, default=128,
                     help="input bytes (Q,K,V,dO together) per chunk of the pipelined host call, in MiB")
@@ -699,7 +702,8 @@ def main():
     q, k, v, do = (torch.randn(Bs, Hs, T, D, device=dev, dtype=torch.float32, generator=gen).to(tdtype)
                    for _ in range(4))
     ctx = ops.Context.current(dev)
-    ws_bytes = ops.workspace_bytes(q, scale)
+    # The backward keeps its dS tiles when the workspace has room for them (pass 2), else recomputes S and dP.
+    ws_bytes = ops.workspace_bytes(q, scale, pass_=1 if args.bwd == "recompute" else 2)
     workspace = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=dev)
     gatherer = shard.OverlappedGather(n_total, T, D, tdtype, dev) if world > 1 else None
 
@@ -834,7 +838,8 @@ def main():
         fwd_ms, fwd_n = ktimes["fwd"]
         kernels = {name: {"launches": n_, "avg_ms": (ms_ / n_ if n_ else None)} for name, (ms_, n_) in ktimes.items()}
         if dtype == "f16":
-            for name, nprod in (("fwd", 2.0), ("bwd_main", 4.0), ("bwd_dq", 3.0)):     # causal products per kernel
+            # causal tile products per kernel
+            for name, nprod in (("fwd", 2.0), ("bwd_main", 4.0), ("bwd_dq", 3.0 if args.bwd == "recompute" else 1.0)):
                 ms_, n_ = ktimes[name]
                 if n_:
                     kernels[name]["tflops_executed"] = nprod * n_local * T * T * D / (ms_ / n_ * 1e-3) / 1e12
@@ -853,6 +858,9 @@ def main():
                            "flops_per_step": total_flops, "flop_convention": "7*B*H*T^2*D (causal fwd 2, bwd 5)",
                            "parallelism": f"(b x h) shards over {world} GPU(s), {n_local} slices on rank 0",
                            "gather": (args.gather if world > 1 else "n/a (1 GPU)"), "gather_probe": gather_probe,
+                           "backward": ("dS tiles kept in the workspace between the dK/dV and dQ kernels"
+                                        if args.bwd == "keep-ds" and dtype == "f16" else "dQ kernel recomputes S and dP"),
+                           "workspace_bytes": ws_bytes,
                            "l2": "inputs larger than L2 (no flush needed)" if 4 * q.numel() * esize > 126e6
                                  else "inputs fit in L2 (not flushed)",
                            "frac_of_dense_peak": value / world / peaks["tflops_sustained"],

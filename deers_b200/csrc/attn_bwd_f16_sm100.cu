@@ -74,7 +74,17 @@ struct BwdParams {
     unsigned int* err;
     const int4* sched;          // balanced schedule table[n * grid + cta] = {slot, slice, batch, head} (or nullptr: strided)
     int sched_rows;
+    // dS^T tiles kept between the two main kernels (nullptr: the dQ kernel recomputes S and dP instead).
+    // Tile (slice, query tile i, KV tile j) is 32 KB at ((slice * ds_pairs + pair(i, j)) << 15): two blocks of
+    // 128 KV rows x 64 query columns in the 128-byte-swizzled shared-memory image the tensor core reads.
+    __half* ds;
+    long long ds_pairs;         // tiles per slice: nq (nq + 1) / 2 causal, nq * nq otherwise
 };
+
+// Index of tile (query tile i, KV tile j) among its slice's dS^T tiles: all KV tiles of a query tile are adjacent.
+__device__ __forceinline__ long long ds_pair(const BwdParams& p, int i, int j, int nq) {
+    return p.causal ? (long long)i * (i + 1) / 2 + j : (long long)i * nq + j;
+}
 
 __device__ __forceinline__ float ex2(float x) {
     float y;
@@ -422,6 +432,22 @@ attn_bwd_dkdv_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
 #if defined(DEERS_TRACE) && DEERS_TRACE == 1
                 if (tr) TRACE_A(1 + g, 4);
 #endif
+                if (p.ds) {
+                    // The same dS^T row also goes to global memory, already swizzled, for the dQ kernel (off the
+                    // critical path: the tensor core has what it needs).  The row's eight 16-byte chunks are
+                    // transposed within 8-lane groups first, so that one store instruction writes four whole
+                    // 128-byte rows instead of 16 bytes in each of 32 rows.
+                    uint8_t* tile = reinterpret_cast<uint8_t*>(p.ds) + (((long long)bh * p.ds_pairs + ds_pair(p, i, kt, nq)) << 15) +
+                                    g * (int)BLOCK_BYTES;
+                    uint4 pc[8];
+#pragma unroll
+                    for (int ch = 0; ch < 8; ++ch) pc[ch] = make_uint4(dd[4 * ch], dd[4 * ch + 1], dd[4 * ch + 2], dd[4 * ch + 3]);
+                    transpose_pieces<8>(pc, (uint32_t)lane);
+                    const int rbase = lane_base + (lane & ~7);  // pc[c] is now chunk (lane & 7) of row rbase + c
+#pragma unroll
+                    for (int c = 0; c < 8; ++c)
+                        *reinterpret_cast<uint4*>(tile + sw128_chunk_offset(rbase + c, lane & 7)) = pc[c];
+                }
             }
             if (!alive) break;
 
@@ -804,6 +830,159 @@ attn_bwd_dq_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     if (warp == 1) tmem_dealloc(tmem, TMEM_COLS);
 }
 
+// ---------------------------------------------------------------------------------------------
+// dQ from stored dS^T tiles (persistent; used when the caller's workspace has room for them)
+// ---------------------------------------------------------------------------------------------
+// dQ tile i = scale * sum_j dS(i, j) K(j): a streaming product.  Warp 0 brings, per KV tile, the 32 KB dS^T tile
+// (two bulk copies: it is already in shared-memory order) and the K tile (TMA) into a 3-stage ring; warp 1
+// issues 8 tcgen05.mma per stage (A = dS^T read MN-major, B = K read MN-major) into one of two TMEM
+// accumulators; warps 2-5 convert a finished accumulator to f16 and store it.  No exponentials, no second
+// pass over Q, V, dO: the kernel is bound by reading the dS^T tiles once.
+template <int D>
+struct DqsSmem {
+    static constexpr uint32_t DS = 128u * 128u * 2u;
+    static constexpr uint32_t KT = 128u * D * 2u;
+    static constexpr uint32_t STAGE = DS + KT;
+    static constexpr int STAGES = 3;
+    static constexpr uint32_t BARS = STAGES * STAGE;
+    static constexpr uint32_t TOTAL = BARS + 256;
+};
+
+enum DqsBar { R_FULL = 0, R_EMPTY = 3, R_ACC_FULL = 6, R_ACC_EMPTY = 8, R_COUNT = 10 };
+
+template <int D>
+__global__ void __launch_bounds__(192, 1)
+attn_bwd_dq_from_ds_f16_kernel(const __grid_constant__ CUtensorMap tmap_k, const BwdParams p) {
+    using L = DqsSmem<D>;
+    constexpr int DBLK = D / 64;
+    constexpr uint32_t TMEM_COLS = 2 * D;                    // 128 or 256: a power of two
+
+    extern __shared__ __align__(1024) uint8_t smem[];
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BARS);
+    uint32_t* tmem_base_s = reinterpret_cast<uint32_t*>(bars + R_COUNT);
+    volatile uint32_t* abort_s = tmem_base_s + 1;
+    uint32_t* skip_s = tmem_base_s + 2;
+
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const int nq = (p.T + BT - 1) / BT;
+    const int n_items = p.B * p.H * nq;
+
+    if (threadIdx.x == 0) {
+        *abort_s = 0;
+        uint32_t skip = (*(volatile unsigned int*)p.err != 0) ? 1u : 0u;
+        if ((smem_u32(smem) & 1023u) != 0) {
+            atomicCAS(p.err, 0u, DEERS_KERR_BWD_F16 | 0x20);
+            skip = 1;
+        }
+        *skip_s = skip;
+        for (int s = 0; s < L::STAGES; ++s) { mbar_init(&bars[R_FULL + s], 1); mbar_init(&bars[R_EMPTY + s], 1); }
+        for (int s = 0; s < 2; ++s) { mbar_init(&bars[R_ACC_FULL + s], 1); mbar_init(&bars[R_ACC_EMPTY + s], 128); }
+        fence_barrier_init();
+        tma_prefetch_desc(&tmap_k);
+    }
+    __syncthreads();
+    if (*skip_s) return;
+    if (warp == 1) {
+        tmem_alloc(tmem_base_s, TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = *tmem_base_s;
+    WaitState ws{abort_s, p.err};
+
+    if (warp == 0) {
+        // ------------------------------ producer ------------------------------
+        if (lane == 0) {
+            uint32_t gi = 0;                                    // KV steps so far (ring position)
+            bool ok = true;
+            for (int4 cur = next_item(p, 0, n_items, nq), nxt = next_item(p, 1, n_items, nq), n4 = make_int4(0, 0, 0, 0); ok && cur.x >= 0;
+                     ++n4.x, cur = nxt, nxt = next_item(p, n4.x + 1, n_items, nq)) {
+                const int qt = nq - 1 - cur.x, bh = cur.y, b = cur.z, h = cur.w;
+                const int ntiles = p.causal ? qt + 1 : nq;
+                const uint8_t* ds_src = reinterpret_cast<const uint8_t*>(p.ds) + (((long long)bh * p.ds_pairs + ds_pair(p, qt, 0, nq)) << 15);
+                for (int j = 0; j < ntiles; ++j, ++gi) {
+                    const uint32_t s = gi % (uint32_t)L::STAGES;
+                    if (!mbar_wait(ws, &bars[R_EMPTY + s], ((gi / (uint32_t)L::STAGES) & 1u) ^ 1u, DEERS_KERR_BWD_F16 | 0x30)) { ok = false; break; }
+                    mbar_arrive_expect_tx(&bars[R_FULL + s], L::STAGE);
+                    uint8_t* stage = smem + s * L::STAGE;
+                    bulk_load(stage, ds_src + ((long long)j << 15), BLOCK_BYTES, &bars[R_FULL + s]);
+                    bulk_load(stage + BLOCK_BYTES, ds_src + ((long long)j << 15) + BLOCK_BYTES, BLOCK_BYTES, &bars[R_FULL + s]);
+#pragma unroll
+                    for (int blk = 0; blk < DBLK; ++blk)
+                        tma_load_4d(stage + L::DS + blk * BLOCK_BYTES, &tmap_k, &bars[R_FULL + s], blk * 64, j * BT, h, b);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer ------------------------------
+        if (lane == 0) {
+            constexpr uint32_t IDESC = idesc_f16(128, D, 1, 1);        // both operands MN-major
+            constexpr uint64_t STAGE_STEP = L::STAGE >> 4;
+            const uint64_t a0 = desc_mnmajor(smem_u32(smem), 0, BLOCK_BYTES);
+            const uint64_t b0 = desc_mnmajor(smem_u32(smem + L::DS), 0, BLOCK_BYTES);
+            uint32_t gi = 0;
+            bool ok = true;
+            for (int4 cur = next_item(p, 0, n_items, nq), nxt = next_item(p, 1, n_items, nq), n4 = make_int4(0, 0, 0, 0); ok && cur.x >= 0;
+                     ++n4.x, cur = nxt, nxt = next_item(p, n4.x + 1, n_items, nq)) {
+                const uint32_t n = (uint32_t)n4.x, buf = n & 1u;
+                const int qt = nq - 1 - cur.x;
+                const int ntiles = p.causal ? qt + 1 : nq;
+                if (!mbar_wait(ws, &bars[R_ACC_EMPTY + buf], ((n >> 1) & 1u) ^ 1u, DEERS_KERR_BWD_F16 | 0x31)) break;
+                for (int j = 0; j < ntiles; ++j, ++gi) {
+                    const uint32_t s = gi % (uint32_t)L::STAGES;
+                    if (!mbar_wait(ws, &bars[R_FULL + s], (gi / (uint32_t)L::STAGES) & 1u, DEERS_KERR_BWD_F16 | 0x32)) { ok = false; break; }
+                    tc_fence_after_sync();
+                    const uint64_t a = a0 + (uint64_t)s * STAGE_STEP, bd = b0 + (uint64_t)s * STAGE_STEP;
+#pragma unroll
+                    for (int ks = 0; ks < BT / 16; ++ks)
+                        umma_ss(tmem + buf * (uint32_t)D, a + mnmajor_step(ks), bd + mnmajor_step(ks), IDESC, (j > 0 || ks > 0));
+                    umma_commit(&bars[R_EMPTY + s]);
+                }
+                if (ok) umma_commit(&bars[R_ACC_FULL + buf]);
+            }
+        }
+    } else {
+        // ------------------------------ epilogue ------------------------------
+        const int lane_base = (warp & 3) * 32;
+        const uint32_t t_lane = (uint32_t)lane_base << 16;
+        for (int4 cur = next_item(p, 0, n_items, nq), nxt = next_item(p, 1, n_items, nq), n4 = make_int4(0, 0, 0, 0); cur.x >= 0;
+                 ++n4.x, cur = nxt, nxt = next_item(p, n4.x + 1, n_items, nq)) {
+            const uint32_t n = (uint32_t)n4.x, buf = n & 1u;
+            const int qt = nq - 1 - cur.x, b = cur.z, h = cur.w;
+            if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[R_ACC_FULL + buf], (n >> 1) & 1u, DEERS_KERR_BWD_F16 | 0x33))) break;
+            tc_fence_after_sync();
+            const int row0 = qt * BT + lane_base + (lane & ~7);
+            __half* qb = p.dq + b * p.sdq_b + h * p.sdq_h + (lane & 7) * 8;
+#pragma unroll 1
+            for (int part = 0; part < D / 64; ++part) {          // 64 columns at a time
+                uint32_t r[64];
+                uint4 pc[8];
+                tmem_ld_x32(tmem + buf * (uint32_t)D + t_lane + part * 64, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+                tmem_ld_x32(tmem + buf * (uint32_t)D + t_lane + part * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+                tmem_wait_ld();
+                if (part == D / 64 - 1) {                        // accumulator is in registers: the next item may use it
+                    tc_fence_before_sync();
+                    mbar_arrive(&bars[R_ACC_EMPTY + buf]);
+                }
+#pragma unroll
+                for (int q8 = 0; q8 < 8; ++q8) pc[q8] = pack8_f16(r + q8 * 8, p.scale);
+                transpose_pieces<8>(pc, (uint32_t)lane);
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const int row = row0 + c;
+                    if (row < p.T) *reinterpret_cast<uint4*>(qb + (long long)row * p.sdq_t + part * 64) = pc[c];
+                }
+            }
+        }
+    }
+    __syncwarp();
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem, TMEM_COLS);
+}
+
 // delta[row] = sum_d dO[row][d] * O[row][d] and lse2[row] = lse[row] * log2(e) on the padded
 // [B*H][Tpad] grid (0 beyond T).  D/8 lanes share a row (16-byte loads); a warp takes 4 * 256 / D
 // consecutive rows per step with all eight loads of a lane in flight before the first is used;
@@ -869,7 +1048,7 @@ size_t bwd_stat_bytes(const deers_attn_desc* d) {
 
 template <int D>
 int bwd_launch(deers_ctx* ctx, const deers_attn_desc* d, const void* q, const void* k, const void* v, const void* o,
-               const float* lse, const void* d_o, void* dq, void* dk, void* dv, void* workspace) {
+               const float* lse, const void* d_o, void* dq, void* dk, void* dv, void* workspace, bool keep_ds) {
     CUtensorMap tq, tk, tv, tdo;
     int rc;
     if ((rc = make_tmap_bhtd_f16(ctx, &tq, q, d->B, d->H, d->T, D, d->q_strides, BT))) return rc;
@@ -904,6 +1083,8 @@ int bwd_launch(deers_ctx* ctx, const deers_attn_desc* d, const void* q, const vo
     p.sdv_b = d->dv_strides[0]; p.sdv_h = d->dv_strides[1]; p.sdv_t = d->dv_strides[2];
     p.B = d->B; p.H = d->H; p.T = d->T; p.Tpad = Tpad; p.causal = d->causal; p.scale = d->scale;
     p.err = ctx->dev_err;
+    p.ds_pairs = d->causal ? (long long)nq * (nq + 1) / 2 : (long long)nq * nq;
+    p.ds = keep_ds ? (__half*)((char*)workspace + 2 * stat_bytes) : nullptr;
     const long long grid = BH * nq;
     if (grid > 0x7fffffffLL) return DEERS_ERR_SHAPE;
 
@@ -917,7 +1098,12 @@ int bwd_launch(deers_ctx* ctx, const deers_attn_desc* d, const void* q, const vo
         attn_bwd_dkdv_f16_kernel<D><<<persistent, 320, smem_a, ctx->stream>>>(tq, tk, tv, tdo, p);
     }
     DEERS_CUDA_TRY(ctx, cudaGetLastError());
-    {
+    if (keep_ds) {
+        const size_t smem_c = DqsSmem<D>::TOTAL;
+        DEERS_CUDA_TRY(ctx, cudaFuncSetAttribute(attn_bwd_dq_from_ds_f16_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_c));
+        KernelTimerScope ts(ctx, DEERS_K_BWD_DQ);
+        attn_bwd_dq_from_ds_f16_kernel<D><<<persistent, 192, smem_c, ctx->stream>>>(tk, p);
+    } else {
         KernelTimerScope ts(ctx, DEERS_K_BWD_DQ);
         attn_bwd_dq_f16_kernel<D><<<persistent, 320, smem_b, ctx->stream>>>(tq, tk, tv, tdo, p);
     }
@@ -928,14 +1114,22 @@ int bwd_launch(deers_ctx* ctx, const deers_attn_desc* d, const void* q, const vo
 
 }  // namespace
 
-// Workspace: delta [B*H][Tpad] | lse*log2e [B*H][Tpad], float32, Tpad = T rounded up to 128.
-size_t attn_bwd_f16_workspace_bytes(const deers_attn_desc* d) { return 2 * bwd_stat_bytes(d); }
+// Workspace: delta [B*H][Tpad] | lse*log2e [B*H][Tpad], float32, Tpad = T rounded up to 128; with keep_ds
+// also one 32 KB dS^T tile per (slice, query tile, KV tile) pair the mask leaves.
+size_t attn_bwd_f16_workspace_bytes(const deers_attn_desc* d, bool keep_ds) {
+    size_t bytes = 2 * bwd_stat_bytes(d);
+    if (keep_ds) {
+        const size_t nq = (size_t)((d->T + BT - 1) / BT);
+        bytes += (size_t)d->B * d->H * (d->causal ? nq * (nq + 1) / 2 : nq * nq) * 32768u;
+    }
+    return bytes;
+}
 
 int launch_attn_bwd_f16(deers_ctx* ctx, const deers_attn_desc* d, const void* q, const void* k, const void* v,
                         const void* o, const float* lse, const void* d_o, void* dq, void* dk, void* dv,
-                        void* workspace) {
-    if (d->D == 64) return bwd_launch<64>(ctx, d, q, k, v, o, lse, d_o, dq, dk, dv, workspace);
-    if (d->D == 128) return bwd_launch<128>(ctx, d, q, k, v, o, lse, d_o, dq, dk, dv, workspace);
+                        void* workspace, bool keep_ds) {
+    if (d->D == 64) return bwd_launch<64>(ctx, d, q, k, v, o, lse, d_o, dq, dk, dv, workspace, keep_ds);
+    if (d->D == 128) return bwd_launch<128>(ctx, d, q, k, v, o, lse, d_o, dq, dk, dv, workspace, keep_ds);
     return DEERS_ERR_UNSUPPORTED;
 }
 
@@ -970,7 +1164,7 @@ int deers_b200_attn_bwd_f16_static(deers_ctx* ctx, const deers_attn_desc* d, con
         for (int a = 0; a < 3; ++a)
             if (strides[i][a] < 0 || ((strides[i][a] * 2) & 15) != 0) return DEERS_ERR_LAYOUT;
     }
-    const size_t need = attn_bwd_f16_workspace_bytes(d);
+    const size_t need = attn_bwd_f16_workspace_bytes(d, false);
     if (need > sizeof(float) * kStaticScratchFloats) {
         snprintf(ctx->last_error, sizeof(ctx->last_error),
                  "deers_b200_attn_bwd_f16_static: needs %zu bytes of scratch, the built-in array holds %zu "
@@ -987,6 +1181,6 @@ int deers_b200_attn_bwd_f16_static(deers_ctx* ctx, const deers_attn_desc* d, con
     void* scratch = g_static_scratch_addr[ctx->device];
     // Nothing needs clearing: the first kernel of the backward writes every element of both arrays
     // (zeros beyond T included) before the other two read them.
-    if (d->D == 64) return bwd_launch<64>(ctx, d, q, k, v, o, lse, d_o, dq, dk, dv, scratch);
-    return bwd_launch<128>(ctx, d, q, k, v, o, lse, d_o, dq, dk, dv, scratch);
+    if (d->D == 64) return bwd_launch<64>(ctx, d, q, k, v, o, lse, d_o, dq, dk, dv, scratch, false);
+    return bwd_launch<128>(ctx, d, q, k, v, o, lse, d_o, dq, dk, dv, scratch, false);
 }

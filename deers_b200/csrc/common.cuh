@@ -102,6 +102,6 @@ int launch_attn_fwd_f16(deers_ctx* ctx, const deers_attn_desc* d, const void* q,
                         const void* v, void* o, float* lse);
 int launch_attn_bwd_f16(deers_ctx* ctx, const deers_attn_desc* d, const void* q, const void* k,
                         const void* v, const void* o, const float* lse, const void* d_o, void* dq,
-                        void* dk, void* dv, void* workspace);
-size_t attn_bwd_f16_workspace_bytes(const deers_attn_desc* d);
+                        void* dk, void* dv, void* workspace, bool keep_ds);
+size_t attn_bwd_f16_workspace_bytes(const deers_attn_desc* d, bool keep_ds);
 int run_selftest_umma(deers_ctx* ctx, float* max_abs_err);

@@ -275,7 +275,8 @@ static size_t delta_bytes(const deers_attn_desc* d) {
 
 extern "C" size_t deers_b200_attn_workspace_bytes(const deers_attn_desc* d, int pass) {
     if (check_desc(d) != DEERS_OK || pass == 0) return 0;
-    return d->dtype == DEERS_F16 ? attn_bwd_f16_workspace_bytes(d) : delta_bytes(d);
+    // pass 1: the least the backward needs; pass 2: what lets the f16 backward keep its dS tiles
+    return d->dtype == DEERS_F16 ? attn_bwd_f16_workspace_bytes(d, pass >= 2) : delta_bytes(d);
 }
 
 extern "C" int deers_b200_attn_fwd(deers_ctx* ctx, const deers_attn_desc* d, const void* q,
@@ -322,7 +323,8 @@ extern "C" int deers_b200_attn_bwd(deers_ctx* ctx, const deers_attn_desc* d, con
         return launch_attn_bwd_f32(ctx, d, (const float*)q, (const float*)k, (const float*)v,
                                    (const float*)o, lse, (const float*)d_o, (float*)dq, (float*)dk,
                                    (float*)dv, (float*)workspace);
-    return launch_attn_bwd_f16(ctx, d, q, k, v, o, lse, d_o, dq, dk, dv, workspace);
+    const bool keep_ds = workspace_bytes >= deers_b200_attn_workspace_bytes(d, 2);
+    return launch_attn_bwd_f16(ctx, d, q, k, v, o, lse, d_o, dq, dk, dv, workspace, keep_ds);
 }
 
 static int drain_timer(deers_ctx* ctx, deers_ktimer* t) {

@@ -156,7 +156,9 @@ def workspace_bytes(q, scale: float = 1.0, causal: bool = True, pass_: int = 1) 
 
 def attention_bwd(q, k, v, o, lse, d_o, scale: float, causal: bool = True, workspace: Optional[torch.Tensor] = None,
                   dv_out: Optional[torch.Tensor] = None):
-    """Storage-level backward: returns (dq, dk, dv), each compact [B,H,T,D].  `dv_out` (a [B,H,T,D] view
+    """Storage-level backward: returns (dq, dk, dv), each compact [B,H,T,D].  `workspace` (uint8, 256-byte
+    aligned) of `workspace_bytes(q, pass_=2)` bytes selects the f16 backward that keeps dS tiles, of
+    `pass_=1` bytes the recomputing one; without it the function allocates.  `dv_out` (a [B,H,T,D] view
     with inner stride 1, e.g. the v slice of a fused dqkv buffer seen head-major) receives dV in place
     instead: the kernels write through its strides."""
     _check_inputs("attention_bwd", (q, k, v, o, d_o))
@@ -172,6 +174,11 @@ def attention_bwd(q, k, v, o, lse, d_o, scale: float, causal: bool = True, works
     d = _desc(q, k, v, o, d_o, dq, dk, dv, scale=scale, causal=causal)
     need = int(_lib.lib().deers_b200_attn_workspace_bytes(ctypes.byref(d), 1))
     if workspace is None or workspace.numel() * workspace.element_size() < need:
+        # The larger size lets the f16 backward keep its dS tiles (two tile products fewer); taken when it is
+        # a small part of what the device has free, else the backward recomputes.
+        fast = int(_lib.lib().deers_b200_attn_workspace_bytes(ctypes.byref(d), 2))
+        if fast > need and fast <= torch.cuda.mem_get_info(q.device)[0] // 4:
+            need = fast
         workspace = torch.empty(max(need, 256), dtype=torch.uint8, device=q.device)
     _lib.check(_lib.lib().deers_b200_attn_bwd(ctx.handle, ctypes.byref(d), q.data_ptr(), k.data_ptr(),
                                               v.data_ptr(), o.data_ptr(), lse.data_ptr(), d_o.data_ptr(),

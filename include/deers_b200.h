@@ -115,10 +115,17 @@ int deers_b200_memcpy_d2d(deers_ctx* ctx, void* dst, const void* src, size_t byt
 int deers_b200_sync(deers_ctx* ctx);
 
 /*
- * Scratch memory a pass needs (pass 0 = forward, 1 = backward), in bytes.
+ * Scratch memory a pass needs (pass 0 = forward, 1 = backward, 2 = fast backward), in bytes.
  * Forward needs none.  Backward keeps rowsum(dO * O) per row (and, for f16, the
  * row lse in log2 units), padded to whole tiles.  The reference allocates the equivalent temporaries
- * inside each op (`src/storage/cuda.rs:637-644`).
+ * inside each op (`src/storage/cuda.rs:637-644`; its backward also keeps the whole [B,H,T,T]
+ * probability tensor alive from the forward, `src/ops.rs:1162-1175`).
+ * Pass 2 (f16; for f32 it equals pass 1) adds room for the dS tiles the mask leaves, 32 KB per
+ * (slice, 128-row query tile, 128-row key tile): B*H*nq*(nq+1)/2 tiles causal, nq = ceil(T/128).
+ * deers_b200_attn_bwd given at least that much keeps dS between its two main kernels, so dQ is one
+ * streaming product instead of a second recomputation of S and dP (7 tile products become 5);
+ * given less (but at least the pass-1 size) it recomputes.  Both give the same results up to
+ * f16 rounding of the same dS values and both are bitwise reproducible.
  */
 size_t deers_b200_attn_workspace_bytes(const deers_attn_desc* desc, int pass);
 

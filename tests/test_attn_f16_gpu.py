@@ -108,8 +108,13 @@ def _sampled_slices(B, H, T, D, n_random, seed):
     op = ops.CausalAttention.new(q, k, v)
     o = op.forward()
     grads = ops.GradientStore()
-    op.backward(grads, do)
+    # The backward with room for its dS tiles; the workspace starts as all-ones bytes (NaN patterns), so a
+    # tile that were read without having been written would show.
+    ws = torch.full((ops.workspace_bytes(q, op.scale, True, pass_=2),), 0xFF, dtype=torch.uint8, device="cuda")
+    for t, g in zip((q, k, v), ops.attention_bwd(q, k, v, o, op.lse, do, op.scale, True, workspace=ws)):
+        grads.accumulate(t, g)
     ops.Context.current(q.device).sync()
+    del ws
     rng = np.random.default_rng(seed)
     picks = {(0, 0), (B - 1, H - 1)} | {(int(rng.integers(B)), int(rng.integers(H))) for _ in range(n_random)}
     for b, h in sorted(picks):
@@ -132,3 +137,33 @@ def test_cfg4_long_context_sampled_slices():
 def test_cfg5_shape_sampled_slices():
     # BASELINE config 5 at full size on one GPU: B=64, T=2048, H=32, head_dim=128.
     _sampled_slices(64, 32, 2048, 128, n_random=6, seed=5)
+
+
+@pytest.mark.parametrize("shape,causal", [((1, 2, 256, 128), True), ((2, 2, 384, 64), True), ((1, 2, 130, 64), True),
+                                          ((1, 1, 777, 128), True), ((1, 2, 300, 64), False), ((1, 1, 1, 64), True),
+                                          ((3, 8, 1100, 128), True), ((2, 5, 900, 64), False)])
+def test_backward_workspace_selects_kept_ds_or_recompute(shape, causal):
+    # The workspace size picks the backward: pass-2 bytes keep the dS tiles between the two main kernels,
+    # pass-1 bytes make the dQ kernel recompute S and dP.  Both against the oracle, and against each other.
+    from deers_b200 import ops
+    from oracle import ref
+    from tests.gpu_util import make_inputs, to_dev
+    q, k, v, do = make_inputs(*shape, torch.float16, seed=sum(shape) + 31)
+    want = ref.attn_fwd_bwd(q, k, v, do, causal=causal)
+    tq, tk, tv, tdo = (to_dev(a, torch.float16) for a in (q, k, v, do))
+    scale = ops.default_scale(shape[3])
+    o, lse = ops.attention_fwd(tq, tk, tv, scale, causal)
+    small, large = (ops.workspace_bytes(tq, scale, causal, pass_=p) for p in (1, 2))
+    assert large > small
+    got = {}
+    for name, nbytes in (("recompute", small), ("kept", large)):
+        ws = torch.full((nbytes,), 0xFF, dtype=torch.uint8, device="cuda")      # NaN patterns: nothing may be read unwritten
+        got[name] = [t.float().cpu().numpy() for t in ops.attention_bwd(tq, tk, tv, o, lse, tdo, scale, causal, workspace=ws)]
+        ops.Context.current(tq.device).sync()
+        for label, g, w in zip(("dq", "dk", "dv"), got[name], want[2:]):
+            assert_close(g, w, TOL_F16, f"{name}/{shape}/{label}")
+    # dK and dV come from the same kernel and the same arithmetic either way
+    assert np.array_equal(got["recompute"][1], got["kept"][1]) and np.array_equal(got["recompute"][2], got["kept"][2])
+    again = [t.float().cpu().numpy() for t in ops.attention_bwd(tq, tk, tv, o, lse, tdo, scale, causal,
+                                                                 workspace=torch.zeros(large, dtype=torch.uint8, device="cuda"))]
+    assert np.array_equal(again[0], got["kept"][0])          # no atomics: bitwise repeatable

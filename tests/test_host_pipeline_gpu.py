@@ -29,13 +29,13 @@ def test_host_call_matches_oracle_and_device_path(dtype, shape, chunk, tol):
         assert_close(g.float().numpy(), w, tol, f"{shape}/{name}")
     # Bitwise equal to the device-resident path (same kernels, slices are independent).
     dev = [t.cuda() for t in pinned]
-    op = ops.CausalAttention.new(dev[0], dev[1], dev[2], scale)
-    o_dev = op.forward()
-    grads = ops.GradientStore()
-    op.backward(grads, dev[3])
+    o_dev, lse_dev = ops.attention_fwd(dev[0], dev[1], dev[2], scale, True)
+    # the host call gives each chunk the small workspace (its dQ kernel recomputes): same choice here
+    ws = torch.empty(max(ops.workspace_bytes(dev[0], scale, True, pass_=1), 256), dtype=torch.uint8, device="cuda")
+    grads_dev = ops.attention_bwd(dev[0], dev[1], dev[2], o_dev, lse_dev, dev[3], scale, True, workspace=ws)
     assert torch.equal(o_dev.cpu(), o)
-    for t, g in zip(op.dependencies(), (dq, dk, dv)):
-        assert torch.equal(grads.get(t).cpu(), g)
+    for gd, g in zip(grads_dev, (dq, dk, dv)):
+        assert torch.equal(gd.cpu(), g)
 
 
 def test_host_call_rejects_small_scratch():
