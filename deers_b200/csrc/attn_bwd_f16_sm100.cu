@@ -99,6 +99,18 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
                  : "memory");
 }
 
+// The same with an L2 eviction-priority hint (a createpolicy value) for data that is read exactly once.
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ void bulk_load_hint(void* dst, const void* src, uint32_t bytes, uint64_t* bar, uint64_t pol) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(pol)
+                 : "memory");
+}
+
 // Work order shared by both kernels: groups of 16 slices; inside a group the heaviest tiles
 // of all its slices come first (balance) and the group's tensors (a few MB) stay in L2.
 // Work item w -> (slot, slice); slot 0 is the heaviest tile of the slice.
@@ -445,8 +457,8 @@ attn_bwd_dkdv_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
                     transpose_pieces<8>(pc, (uint32_t)lane);
                     const int rbase = lane_base + (lane & ~7);  // pc[c] is now chunk (lane & 7) of row rbase + c
 #pragma unroll
-                    for (int c = 0; c < 8; ++c)
-                        *reinterpret_cast<uint4*>(tile + sw128_chunk_offset(rbase + c, lane & 7)) = pc[c];
+                    for (int c = 0; c < 8; ++c)       // streaming stores: the tiles are read once, by the next kernel
+                        __stcs(reinterpret_cast<uint4*>(tile + sw128_chunk_offset(rbase + c, lane & 7)), pc[c]);
                 }
             }
             if (!alive) break;
@@ -897,6 +909,7 @@ attn_bwd_dq_from_ds_f16_kernel(const __grid_constant__ CUtensorMap tmap_k, const
         if (lane == 0) {
             uint32_t gi = 0;                                    // KV steps so far (ring position)
             bool ok = true;
+            const uint64_t pol = l2_policy_evict_first();
             for (int4 cur = next_item(p, 0, n_items, nq), nxt = next_item(p, 1, n_items, nq), n4 = make_int4(0, 0, 0, 0); ok && cur.x >= 0;
                      ++n4.x, cur = nxt, nxt = next_item(p, n4.x + 1, n_items, nq)) {
                 const int qt = nq - 1 - cur.x, bh = cur.y, b = cur.z, h = cur.w;
@@ -907,8 +920,10 @@ attn_bwd_dq_from_ds_f16_kernel(const __grid_constant__ CUtensorMap tmap_k, const
                     if (!mbar_wait(ws, &bars[R_EMPTY + s], ((gi / (uint32_t)L::STAGES) & 1u) ^ 1u, DEERS_KERR_BWD_F16 | 0x30)) { ok = false; break; }
                     mbar_arrive_expect_tx(&bars[R_FULL + s], L::STAGE);
                     uint8_t* stage = smem + s * L::STAGE;
-                    bulk_load(stage, ds_src + ((long long)j << 15), BLOCK_BYTES, &bars[R_FULL + s]);
-                    bulk_load(stage + BLOCK_BYTES, ds_src + ((long long)j << 15) + BLOCK_BYTES, BLOCK_BYTES, &bars[R_FULL + s]);
+                    // dS^T tiles are read exactly once: first to leave L2, so that the K tiles the slice's other
+                    // query tiles share stay there
+                    bulk_load_hint(stage, ds_src + ((long long)j << 15), BLOCK_BYTES, &bars[R_FULL + s], pol);
+                    bulk_load_hint(stage + BLOCK_BYTES, ds_src + ((long long)j << 15) + BLOCK_BYTES, BLOCK_BYTES, &bars[R_FULL + s], pol);
 #pragma unroll
                     for (int blk = 0; blk < DBLK; ++blk)
                         tma_load_4d(stage + L::DS + blk * BLOCK_BYTES, &tmap_k, &bars[R_FULL + s], blk * 64, j * BT, h, b);
