@@ -818,10 +818,12 @@ def main():
         roofline = None
         if dtype == "f16":
             achieved = dkdv_flops / (bwd_avg * 1e-3) / 1e12
-            # DRAM traffic of this kernel from an ncu capture of a small case (376.0 MB for the 128 slices of
-            # B=8, H=16 at T=2048, D=128; summary under profiles/), scaled by the slices one launch
-            # processes; traffic is proportional to the slice count.
-            traffic = 376.0e6 / 128 * n_local if (T == 2048 and D == 128) else None
+            # DRAM traffic of this kernel from an ncu capture of a small case (the 128 slices of B=8, H=16 at
+            # T=2048, D=128: 914.2 MB when it also writes the dS tiles, 376.0 MB when it does not; summaries
+            # under profiles/), scaled by the slices one launch processes; traffic is proportional to the
+            # slice count.
+            per128 = 376.0e6 if args.bwd == "recompute" else 914.2e6
+            traffic = per128 / 128 * n_local if (T == 2048 and D == 128) else None
             roofline = {"bound": "tensor", "kernel": "attn_bwd_dkdv_f16_kernel", "achieved": achieved, "peak": peak,
                         "unit": UNIT, "frac": achieved / peak, "traffic": traffic,
                         "flops_per_launch": dkdv_flops,
