@@ -16,7 +16,7 @@ F16, F32 = 0, 1
 SYMBOLS = [
     "deers_b200_attn_desc_compact", "deers_b200_init", "deers_b200_destroy", "deers_b200_set_stream",
     "deers_b200_stream", "deers_b200_alloc", "deers_b200_free", "deers_b200_memcpy_h2d",
-    "deers_b200_memcpy_d2h", "deers_b200_memcpy_d2d", "deers_b200_sync", "deers_b200_attn_workspace_bytes",
+    "deers_b200_memcpy_d2h", "deers_b200_memcpy_d2d", "deers_b200_mem_info", "deers_b200_sync", "deers_b200_attn_workspace_bytes",
     "deers_b200_attn_fwd", "deers_b200_attn_bwd", "deers_b200_status_string", "deers_b200_last_error",
     "deers_b200_launch_count", "deers_b200_selftest_umma", "deers_b200_kernel_timing",
     "deers_b200_kernel_time", "deers_b200_attn_bwd_f16_static", "deers_b200_attn_host_scratch_bytes",
@@ -88,6 +88,7 @@ def lib() -> ctypes.CDLL:
     for n in ("h2d", "d2h", "d2d"):
         getattr(L, f"deers_b200_memcpy_{n}").argtypes = [vp, vp, vp, sz]
     L.deers_b200_sync.argtypes = [vp]
+    L.deers_b200_mem_info.argtypes = [vp, ctypes.POINTER(sz), ctypes.POINTER(sz)]
     L.deers_b200_attn_workspace_bytes.argtypes = [dp, i32]
     L.deers_b200_attn_workspace_bytes.restype = sz
     L.deers_b200_attn_fwd.argtypes = [vp, dp, vp, vp, vp, vp, vp, vp, sz]

@@ -143,6 +143,13 @@ extern "C" int deers_b200_free(deers_ctx* ctx, void* dptr) {
     return DEERS_OK;
 }
 
+extern "C" int deers_b200_mem_info(deers_ctx* ctx, size_t* free_bytes, size_t* total_bytes) {
+    if (!ctx || !free_bytes || !total_bytes) return DEERS_ERR_NULL;
+    DEERS_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    DEERS_CUDA_TRY(ctx, cudaMemGetInfo(free_bytes, total_bytes));
+    return DEERS_OK;
+}
+
 extern "C" int deers_b200_memcpy_h2d(deers_ctx* ctx, void* dst, const void* src, size_t bytes) {
     if (!ctx || (bytes && (!dst || !src))) return DEERS_ERR_NULL;
     DEERS_CUDA_TRY(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, ctx->stream));

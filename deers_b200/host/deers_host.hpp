@@ -217,7 +217,12 @@ public:
         deers_attn_desc d = desc(o_.layout());
         fill_strides(d.do_strides, out_grad.layout());
         fill_strides(d.dq_strides, gl); fill_strides(d.dk_strides, gl); fill_strides(d.dv_strides, gl);
-        const size_t ws_bytes = deers_b200_attn_workspace_bytes(&d, 1);
+        // The larger (pass 2) workspace lets the f16 backward keep its dS tiles between its kernels; taken when
+        // it is a small part of what the device has free, else the backward recomputes (pass 1).
+        size_t ws_bytes = deers_b200_attn_workspace_bytes(&d, 1);
+        const size_t fast = deers_b200_attn_workspace_bytes(&d, 2);
+        size_t free_b = 0, total_b = 0;
+        if (fast > ws_bytes && deers_b200_mem_info(rt.ctx(), &free_b, &total_b) == DEERS_OK && fast <= free_b / 4) ws_bytes = fast;
         CudaStorage ws(ws_bytes ? ws_bytes : 256, DType::F32);
         rt.check(deers_b200_attn_bwd(rt.ctx(), &d, q_.storage().ptr(), k_.storage().ptr(), v_.storage().ptr(),
                                      o_.storage().ptr(), (const float*)lse_->ptr(), out_grad.storage().ptr(), dq->ptr(),

@@ -103,6 +103,8 @@ void* deers_b200_stream(deers_ctx* ctx);
  */
 int deers_b200_alloc(deers_ctx* ctx, size_t bytes, void** dptr);
 int deers_b200_free(deers_ctx* ctx, void* dptr);
+/* Free and total device memory in bytes (what a caller weighs the larger backward workspace against). */
+int deers_b200_mem_info(deers_ctx* ctx, size_t* free_bytes, size_t* total_bytes);
 int deers_b200_memcpy_h2d(deers_ctx* ctx, void* dst, const void* src, size_t bytes);
 int deers_b200_memcpy_d2h(deers_ctx* ctx, void* dst, const void* src, size_t bytes);
 int deers_b200_memcpy_d2d(deers_ctx* ctx, void* dst, const void* src, size_t bytes);
