@@ -109,6 +109,7 @@ def cpu_baseline(T: int, D: int, n_slices: int, repeats: int):
     """Times the CPU oracle (fwd + bwd, materialising, OpenMP over slices) on `n_slices` slices."""
     import numpy as np
     from oracle import ref
+    ref.set_num_threads()                                   # every host core, whatever OMP_NUM_THREADS says
     rng = np.random.default_rng(0)
     base = min(n_slices, 32)
     q, k, v, do = (np.tile(rng.standard_normal((base, 1, T, D), dtype=np.float32), (n_slices // base, 1, 1, 1))
@@ -140,7 +141,7 @@ def run_reference(args, dtype, B, T, H, D):
     if rank != 0:
         return
     from oracle import ref
-    threads = ref.num_threads()
+    threads = ref.set_num_threads()                         # launchers such as torchrun export OMP_NUM_THREADS=1
     total_budget = 100.0                                    # seconds for the whole run
     n = cpu_sample_size(T, D, threads, total_budget / (args.steps + args.warmup))
     n = max(1, min(n, B * H))
@@ -600,12 +601,226 @@ def run_adamw(args):
     print(json.dumps(line))
 
 
+GPT_CFG3 = {"vocab": 50257, "n_layer": 6, "n_head": 6, "n_embd": 192, "mlp": 768, "B": 4, "T": 256,
+            "eps": 1e-5, "rope_base": 10000.0, "lr": 5e-4, "wd": 0.1, "max_grad_norm": 1.0}
+
+
+def gpt_workload_name():
+    c = GPT_CFG3
+    return (f"cfg3: GPT training step, f32, {c['n_layer']} layers, {c['n_head']} heads, n_embd {c['n_embd']}, mlp "
+            f"{c['mlp']}, vocab {c['vocab']}, RMSNorm eps {c['eps']}, RoPE base {c['rope_base']:g}; B={c['B']} "
+            f"T={c['T']}, ids uniform in [0, vocab); cross_entropy + clip_grad_norm({c['max_grad_norm']}) + "
+            f"AdamW(lr={c['lr']}, wd={c['wd']})")
+
+
+def gpt_gemm_flops():
+    c = GPT_CFG3
+    n, C, Hm, V = c["B"] * c["T"], c["n_embd"], c["mlp"], c["vocab"]
+    linear = c["n_layer"] * (4 * C * C + 2 * C * Hm) + C * V
+    return 6.0 * n * linear                                 # forward + two backward products per Linear
+
+
+def gpt_cpu_step(params, ids, tgt, moments, step):
+    """One whole training step on the CPU oracle: forward, loss, backward, clip, AdamW.  Returns seconds."""
+    from oracle import ref
+    c = GPT_CFG3
+    t0 = time.perf_counter()
+    r = ref.gpt_step((c["vocab"], c["n_layer"], c["n_head"], c["n_embd"], c["mlp"]), params, ids, tgt,
+                     eps=c["eps"], rope_base=c["rope_base"], want_logits=False)
+    ref.clip_grad_norm(r["grads"], c["max_grad_norm"])
+    for p, g, (m, v) in zip(params, r["grads"], moments):
+        ref.adamw_step(p, g, m, v, step, c["lr"], weight_decay=c["wd"])
+    return time.perf_counter() - t0, r["loss"]
+
+
+def run_gpt_reference(args):
+    """--impl reference --workload cfg3: the CPU restatement of the whole step, all host threads."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    import numpy as np
+    from oracle import ref
+    threads = ref.set_num_threads()
+    c = GPT_CFG3
+    cfg = (c["vocab"], c["n_layer"], c["n_head"], c["n_embd"], c["mlp"])
+    params = ref.gpt_init_params(cfg, seed=0)
+    moments = [(np.zeros_like(p), np.zeros_like(p)) for p in params]
+    rng = np.random.default_rng(1)
+    ids = rng.integers(0, c["vocab"], (c["B"], c["T"]))
+    tgt = rng.integers(0, c["vocab"], c["B"] * c["T"])
+    steps = max(1, min(args.steps, 5))                      # a step takes seconds on the host: bounded
+    warm = min(args.warmup, 1)
+    for i in range(warm):
+        gpt_cpu_step(params, ids, tgt, moments, i + 1)
+    total = 0.0
+    for i in range(steps):
+        dt, _ = gpt_cpu_step(params, ids, tgt, moments, warm + i + 1)
+        total += dt
+    dt = total / steps
+    val = c["B"] * c["T"] / dt
+    sample = (f"the whole step (B*T = {c['B'] * c['T']} tokens) {steps} time(s) after {warm} warm-up: f32 C restatement "
+              f"of the reference CPU path (forward, cross-entropy, backward, clip, AdamW), {threads} threads")
+    line = {"impl": "reference", "metric": "gpt_step_tok_per_s", "value": val, "unit": "tok/s", "n_gpus": args.gpus,
+            "steps": steps, "warmup": warm, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": gpt_workload_name(), "sample": sample},
+            "cpu_baseline": {"value": val, "unit": "tok/s", "cores": threads, "kind": "port", "sample": sample},
+            "e2e": {"value": val, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def run_gpt_step(args):
+    """--workload cfg3: the f32 GPT training step of BASELINE cfg 3 on one GPU (N > 1: one independent replica
+    per rank, weak scaling, no collective: the reference has no data-parallel training)."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from deers_b200 import _lib, gpt
+    from oracle import ref
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a B200: there is no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    c = GPT_CFG3
+    cfg = (c["vocab"], c["n_layer"], c["n_head"], c["n_embd"], c["mlp"])
+    B, T = c["B"], c["T"]
+    params = ref.gpt_init_params(cfg, seed=0)               # numpy draws from the reference's init distributions
+    model = gpt.GPT(gpt.GPTConfig(c["vocab"], T, c["n_layer"], c["n_head"], c["n_embd"], c["mlp"], c["eps"],
+                                  c["rope_base"]), dev, B)
+    model.load_parameters(params)
+    rng = np.random.default_rng(1 + rank)
+    n_batches = 8                                            # rotate batches so no step repeats the previous one's ids
+    ids_h = [rng.integers(0, c["vocab"], (B, T)) for _ in range(n_batches)]
+    tgt_h = [rng.integers(0, c["vocab"], B * T) for _ in range(n_batches)]
+    ids_d = [torch.from_numpy(a).to(dev) for a in ids_h]
+    tgt_d = [torch.from_numpy(a).to(dev) for a in tgt_h]
+    kw = dict(lr=c["lr"], weight_decay=c["wd"], max_grad_norm=c["max_grad_norm"])
+    ctx = model.ctx
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local) if rank == 0 else None
+    for i in range(max(args.warmup, 3)):
+        model.train_step(ids_d[i % n_batches], tgt_d[i % n_batches], **kw)
+    barrier()
+    # The driver fixes --steps; a block of K steps lasts milliseconds here, so the block is repeated until two
+    # seconds of device time have passed and the median block is reported.
+    blocks = []
+    launches0 = ctx.launch_count()
+    while sum(blocks) < 2000.0 and len(blocks) < 2000:
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        for i in range(args.steps):
+            loss_d, norm_d = model.train_step(ids_d[i % n_batches], tgt_d[i % n_batches], **kw)
+        ev1.record()
+        torch.cuda.synchronize()
+        blocks.append(ev0.elapsed_time(ev1))
+    barrier()
+    launches = (ctx.launch_count() - launches0) / len(blocks)
+    clocks = sampler.stop() if sampler else None
+    ms = statistics.median(blocks) / args.steps
+    ms_t = torch.tensor([ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(ms_t, op=dist.ReduceOp.MAX)
+    ms_max = float(ms_t.item())
+    final_loss = float(loss_d.item())
+
+    # ---- e2e: ids and targets from host memory, the loss read back, every step
+    e_steps = max(args.e2e_steps, 5)
+    model.train_step_host(ids_h[0], tgt_h[0], **kw)
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(e_steps):
+        model.train_step_host(ids_h[i % n_batches], tgt_h[i % n_batches], **kw)
+    e_ms = torch.tensor([(time.perf_counter() - t0) * 1e3 / e_steps], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(e_ms, op=dist.ReduceOp.MAX)
+    e2e = {"value": world * B * T / (float(e_ms.item()) * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": 2 * B * T * 8,
+           "d2h_bytes_per_step": 8, "ms_per_step": float(e_ms.item()), "steps": e_steps,
+           "api": "deers_b200_gpt_train_step_host: int64 ids and targets from host memory, loss and gradient norm read "
+                  "back, one blocking call per step (host clock)"}
+
+    # ---- per-kernel-family device times: a few eager steps (no graph) bracketed by events
+    model.set_graph(False)
+    model.train_step(ids_d[0], tgt_d[0], **kw)
+    torch.cuda.synchronize()
+    ctx.kernel_timing(True)
+    k_steps = 3
+    l0 = ctx.launch_count()
+    for i in range(k_steps):
+        model.train_step(ids_d[i % n_batches], tgt_d[i % n_batches], **kw)
+    eager_launches = (ctx.launch_count() - l0) / k_steps
+    fams = {"gemm_f32": _lib.K_GEMM, "attn_fwd_f32": _lib.K_FWD, "attn_bwd_delta_f32": _lib.K_BWD_PREP,
+            "attn_bwd_dkdv_f32": _lib.K_BWD_MAIN, "attn_bwd_dq_f32": _lib.K_BWD_DQ, "rope_pack": _lib.K_ROPE,
+            "rmsnorm": _lib.K_NORM, "embedding_cross_entropy": _lib.K_GPT, "grad_norm_adamw": _lib.K_OPTIM}
+    kernels = {}
+    for name, kind in fams.items():
+        t_ms, n = ctx.kernel_time(kind)
+        kernels[name] = {"launches_per_step": n / k_steps, "ms_per_step": t_ms / k_steps}
+    ctx.kernel_timing(False)
+    ctx.sync()
+    model.set_graph(True)
+
+    if rank == 0:
+        peaks = load_peaks()
+        gemm_ms = kernels["gemm_f32"]["ms_per_step"]
+        flops = gpt_gemm_flops()
+        achieved = flops / (gemm_ms * 1e-3) / 1e12
+        sm_max = (clocks or {}).get("sm_max_mhz") or 1965.0
+        ffma_peak = 148 * 128 * 2 * sm_max * 1e6 / 1e12      # FFMA lanes x 2 flops x clock
+        roofline = {"bound": "fp32 FFMA pipe (the reference computes these products in full f32, CUBLAS_COMPUTE_32F)",
+                    "kernel": "gemm_f32_kernel (all Linear forward / dgrad / wgrad products of the step)",
+                    "achieved": achieved, "peak": ffma_peak, "unit": "TFLOP/s", "frac": achieved / ffma_peak,
+                    "traffic": None, "flops_per_step": flops, "kernel_ms_per_step": gemm_ms,
+                    "peak_source": f"148 SMs x 128 FFMA lanes x 2 x {sm_max:.0f} MHz (nominal; MEASURED_PEAKS.json holds no f32 figure)"}
+        cb = None
+        if not args.no_cpu_baseline:
+            threads = ref.set_num_threads()
+            cpu_params = [p.copy() for p in params]
+            moments = [(np.zeros_like(p), np.zeros_like(p)) for p in cpu_params]
+            dt, _ = gpt_cpu_step(cpu_params, ids_h[0], tgt_h[0], moments, 1)
+            dt2, _ = gpt_cpu_step(cpu_params, ids_h[1], tgt_h[1], moments, 2)
+            dt = min(dt, dt2)
+            cb = {"value": B * T / dt, "unit": "tok/s", "cores": threads, "kind": "port", "seconds": dt,
+                  "sample": "the whole step (1024 tokens) twice, best taken: f32 C restatement of the reference CPU path "
+                            "(forward, cross-entropy, backward, clip, AdamW)"}
+        line = {"metric": "gpt_step_tok_per_s", "value": world * B * T / (ms_max * 1e-3), "unit": "tok/s", "n_gpus": world,
+                "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_max, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": gpt_workload_name(), "parameters": 21952896,
+                           "weights": "seeded draws from the reference's init distributions (uniform +-1/sqrt(in), normal embedding)",
+                           "parallelism": "1 GPU" if world == 1 else f"{world} independent replicas (replicas only)",
+                           "timing": f"median of {len(blocks)} blocks of {args.steps} steps ({sum(blocks) / 1e3:.2f} s of device time)",
+                           "l2": "weights, moments, gradients and logits (560 MB) exceed L2: no flush needed",
+                           "final_loss": final_loss, "graph": "forward + loss + backward + gradient norm replayed from a CUDA graph, AdamW launched after it",
+                           "ms_x_median_sm_mhz": (ms_max * clocks["sm_mhz"]) if clocks and clocks.get("sm_mhz") else None},
+                "e2e": e2e, "gpu_launches": int(round(eager_launches * args.steps)),
+                "launches_per_step": {"kernels": eager_launches, "host_calls_with_graph": launches / args.steps},
+                "clocks": clocks, "roofline": roofline, "kernels": kernels, "cpu_baseline": cb}
+        sys.stdout.flush()
+        os.write(real_stdout, (json.dumps(line) + "\n").encode())
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", default="cfg5", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="cfg5", choices=sorted(WORKLOADS) + ["cfg3"],
+                    help="cfg1/2/4/5: attention forward + backward (TFLOP/s); cfg3: the f32 GPT training step (tok/s)")
     ap.add_argument("--shape", default=None, help="B,T,H,D: a custom shape (profiling captures on a small case)")
     ap.add_argument("--dtype", default=None, choices=["f16", "f32"], help="dtype for --shape")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
@@ -640,6 +855,12 @@ def main():
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
+    if args.workload == "cfg3":
+        if args.impl == "reference":
+            run_gpt_reference(args)
+        else:
+            run_gpt_step(args)
+        return
     dtype, B, T, H, D = WORKLOADS[args.workload]
     if args.shape:
         B, T, H, D = (int(x) for x in args.shape.split(","))
@@ -848,7 +1069,7 @@ def main():
         cb = None
         if not args.no_cpu_baseline:
             from oracle import ref
-            threads = ref.num_threads()
+            threads = ref.set_num_threads()
             n_cpu = cpu_sample_size(T, D, threads, 12.0)
             n_cpu = max(1, min(n_cpu, n_total))
             n_cpu = max(32, n_cpu // 32 * 32) if n_cpu >= 32 else n_cpu

@@ -24,8 +24,15 @@ SYMBOLS = [
     "deers_b200_optim_scratch_bytes", "deers_b200_grad_norm", "deers_b200_grad_clip", "deers_b200_adamw_step",
     "deers_b200_rmsnorm_fwd", "deers_b200_rmsnorm_bwd",
     "deers_b200_attn_decode_workspace_bytes", "deers_b200_attn_decode", "deers_b200_gemm_f16",
+    "deers_b200_gemm_f32_workspace_bytes", "deers_b200_gemm_f32", "deers_b200_rmsnorm_bwd_add",
+    "deers_b200_embedding_fwd", "deers_b200_embedding_bwd", "deers_b200_cross_entropy_scratch_bytes",
+    "deers_b200_cross_entropy_fwd", "deers_b200_cross_entropy_bwd",
+    "deers_b200_gpt_create", "deers_b200_gpt_destroy", "deers_b200_gpt_num_params", "deers_b200_gpt_param_info",
+    "deers_b200_gpt_param_set", "deers_b200_gpt_param_get", "deers_b200_gpt_set_graph", "deers_b200_gpt_forward",
+    "deers_b200_gpt_forward_backward", "deers_b200_gpt_train_step", "deers_b200_gpt_train_step_host",
 ]
-K_FWD, K_BWD_PREP, K_BWD_MAIN, K_BWD_DQ, K_ROPE, K_OPTIM, K_NORM, K_DECODE, K_GEMM = range(9)
+K_FWD, K_BWD_PREP, K_BWD_MAIN, K_BWD_DQ, K_ROPE, K_OPTIM, K_NORM, K_DECODE, K_GEMM, K_GPT = range(10)
+EPI_NONE, EPI_ADD, EPI_RELU_SQ, EPI_MUL_AUX2 = range(4)
 
 
 class AttnDesc(ctypes.Structure):
@@ -58,6 +65,17 @@ class DecodeDesc(ctypes.Structure):
                 ("D", ctypes.c_int32), ("dtype", ctypes.c_int32), ("causal", ctypes.c_int32), ("scale", ctypes.c_float),
                 ("q_strides", ctypes.c_int64 * 4), ("k_strides", ctypes.c_int64 * 4),
                 ("v_strides", ctypes.c_int64 * 4), ("o_strides", ctypes.c_int64 * 4)]
+
+
+class GemmEpilogue(ctypes.Structure):
+    _fields_ = [("kind", ctypes.c_int32), ("residual", ctypes.c_void_p), ("ld_residual", ctypes.c_int64),
+                ("aux", ctypes.c_void_p)]
+
+
+class GptConfig(ctypes.Structure):
+    _fields_ = [("vocab_size", ctypes.c_int32), ("sequence_len", ctypes.c_int32), ("n_layer", ctypes.c_int32),
+                ("n_head", ctypes.c_int32), ("n_embd", ctypes.c_int32), ("mlp_hidden_dim", ctypes.c_int32),
+                ("rms_norm_eps", ctypes.c_double), ("rope_base", ctypes.c_float)]
 
 
 _lib = None
@@ -112,6 +130,31 @@ def lib() -> ctypes.CDLL:
     L.deers_b200_attn_decode.argtypes = [vp, ddp, vp, vp, vp, vp, vp, vp, sz]
     i64 = ctypes.c_int64
     L.deers_b200_gemm_f16.argtypes = [vp, i32, i32, i32, vp, i64, i32, vp, i64, i32, vp, i64]
+    L.deers_b200_gemm_f32_workspace_bytes.argtypes = [vp, i32, i32, i32]
+    L.deers_b200_gemm_f32_workspace_bytes.restype = sz
+    L.deers_b200_gemm_f32.argtypes = [vp, i32, i32, i32, vp, i64, i32, vp, i64, i32, vp, i64,
+                                      ctypes.POINTER(GemmEpilogue), vp, sz]
+    L.deers_b200_rmsnorm_bwd_add.argtypes = [vp, i64, ctypes.c_int32, vp, vp, vp, vp, vp]
+    L.deers_b200_embedding_fwd.argtypes = [vp, vp, vp, i64, ctypes.c_int32, i64, vp]
+    L.deers_b200_embedding_bwd.argtypes = [vp, vp, vp, i64, ctypes.c_int32, i64, vp]
+    L.deers_b200_cross_entropy_scratch_bytes.argtypes = [i64]
+    L.deers_b200_cross_entropy_scratch_bytes.restype = sz
+    L.deers_b200_cross_entropy_fwd.argtypes = [vp, i64, i64, vp, i64, vp, vp, vp, vp, sz]
+    L.deers_b200_cross_entropy_bwd.argtypes = [vp, i64, i64, vp, i64, vp, vp, ctypes.c_float, vp, i64]
+    gcp, hp = ctypes.POINTER(GptConfig), ctypes.POINTER(AdamWHyper)
+    L.deers_b200_gpt_create.argtypes = [vp, gcp, ctypes.c_int32, ctypes.POINTER(vp)]
+    L.deers_b200_gpt_destroy.argtypes = [vp]
+    L.deers_b200_gpt_destroy.restype = None
+    L.deers_b200_gpt_num_params.argtypes = [vp]
+    L.deers_b200_gpt_param_info.argtypes = [vp, i32, ctypes.c_char_p, sz, ctypes.POINTER(i64), ctypes.POINTER(i64)]
+    L.deers_b200_gpt_param_set.argtypes = [vp, i32, i32, vp]
+    L.deers_b200_gpt_param_get.argtypes = [vp, i32, i32, vp]
+    L.deers_b200_gpt_set_graph.argtypes = [vp, i32]
+    L.deers_b200_gpt_forward.argtypes = [vp, vp, ctypes.c_int32, ctypes.c_int32, vp]
+    L.deers_b200_gpt_forward_backward.argtypes = [vp, vp, vp, ctypes.c_int32, ctypes.c_int32, vp]
+    L.deers_b200_gpt_train_step.argtypes = [vp, vp, vp, ctypes.c_int32, ctypes.c_int32, hp, ctypes.c_double, vp, vp]
+    L.deers_b200_gpt_train_step_host.argtypes = [vp, vp, vp, ctypes.c_int32, ctypes.c_int32, hp, ctypes.c_double,
+                                                 ctypes.POINTER(ctypes.c_float), ctypes.POINTER(ctypes.c_float)]
     L.deers_b200_status_string.argtypes = [i32]
     L.deers_b200_status_string.restype = ctypes.c_char_p
     L.deers_b200_last_error.argtypes = [vp]

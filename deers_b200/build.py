@@ -13,7 +13,8 @@ CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB = os.path.join(LIB_DIR, "libdeers_b200.so")
 SOURCES = ["ctx.cu", "attn_f32.cu", "umma_selftest.cu", "attn_fwd_f16_sm100.cu", "attn_bwd_f16_sm100.cu",
-           "rope_pack.cu", "optim.cu", "rmsnorm.cu", "attn_decode.cu", "gemm_f16_sm100.cu"]
+           "rope_pack.cu", "optim.cu", "rmsnorm.cu", "attn_decode.cu", "gemm_f16_sm100.cu", "gemm_f32.cu",
+           "gpt_ops.cu", "gpt_model.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC,-fvisibility=hidden", "--use_fast_math=false"]
 
@@ -43,11 +44,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         o = os.path.join(LIB_DIR, src.replace(".cu", ".o"))
         objs.append(o)
         if force or _stale(o, [s] + headers):
-            trace = os.environ.get("DEERS_TRACE")      # development aid: per-iteration clock stamps
-            # DEERS_NVCC_EXTRA: extra nvcc flags (development aid: -D switches of the kernels)
             cmd = [_nvcc()] + [f for f in NVCC_FLAGS if not f.startswith("--use_fast_math")] + \
-                  ([f"-DDEERS_TRACE={trace}"] if trace else []) + \
-                  os.environ.get("DEERS_NVCC_EXTRA", "").split() + \
                   (["-Xptxas", "-v"] if verbose else []) + ["-c", s, "-o", o]
             procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
     failed = False

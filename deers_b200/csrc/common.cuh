@@ -80,6 +80,7 @@ enum {
     DEERS_KERR_BWD_F16 = 0x200,
     DEERS_KERR_SELFTEST = 0x300,
     DEERS_KERR_GEMM = 0x400,
+    DEERS_KERR_GPT = 0x500,      // token id / target out of range
 };
 
 // Work schedule shared by the persistent f16 kernels (ctx.cu).  Work items are ordered in groups
@@ -105,3 +106,25 @@ int launch_attn_bwd_f16(deers_ctx* ctx, const deers_attn_desc* d, const void* q,
                         void* dk, void* dv, void* workspace, bool keep_ds);
 size_t attn_bwd_f16_workspace_bytes(const deers_attn_desc* d, bool keep_ds);
 int run_selftest_umma(deers_ctx* ctx, float* max_abs_err);
+
+// f32 GEMM (gemm_f32.cu)
+size_t gemm_f32_workspace_bytes(const deers_ctx* ctx, int M, int N, int K);
+int launch_gemm_f32(deers_ctx* ctx, int M, int N, int K, const float* a, long long lda, int a_mn, const float* b,
+                    long long ldb, int b_mn, float* c, long long ldc, int epi, const float* r, long long ldr, float* aux,
+                    void* workspace, size_t ws_bytes, bool counters_zero);
+// RMSNorm (rmsnorm.cu)
+int launch_rmsnorm_fwd(deers_ctx* ctx, long long rows, int C, double eps, const float* x, float* y, float* inv_norm);
+int launch_rmsnorm_bwd(deers_ctx* ctx, long long rows, int C, const float* x, const float* inv_norm, const float* dy,
+                       const float* add, float* dx);
+// embedding and cross-entropy (gpt_ops.cu)
+int launch_embedding_fwd(deers_ctx* ctx, const float* weight, const long long* ids, long long n_ids, int C, long long V,
+                         float* out);
+int launch_embedding_bwd(deers_ctx* ctx, const float* dout, const long long* ids, long long n_ids, int C, long long V,
+                         float* dweight);
+int launch_cross_entropy_fwd(deers_ctx* ctx, const float* logits, long long ld, const long long* targets, long long rows,
+                             long long V, float* lse, float* picked, float* loss);
+int launch_cross_entropy_bwd(deers_ctx* ctx, const float* logits, long long ld, const long long* targets, const float* lse,
+                             long long rows, long long V, float upstream, float* dlogits, long long ldd);
+// AdamW with the trainer's rule "no update when the gradient norm is not finite" (optim.cu)
+int launch_adamw(deers_ctx* ctx, int n_tensors, const deers_optim_tensor* tensors, const deers_adamw_hyper* h,
+                 const float* norm_dev, double max_norm, bool skip_nonfinite);

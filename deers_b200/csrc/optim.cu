@@ -42,6 +42,7 @@ struct OptScalars {                     // f64 hyper-parameters rounded to f32 w
     float lr, eps;
     int has_decay;
     int use_clip;
+    int skip_nonfinite;                 // leave w, m, v untouched when the norm is not finite
     double max_norm;
 };
 
@@ -139,6 +140,7 @@ __global__ void __launch_bounds__(256) adamw_kernel(const __grid_constant__ OptT
     float scale;
     const bool clip = clip_scale(s, norm, scale);
     if (MODE == MODE_CLIP && !clip) return;
+    if (MODE == MODE_STEP && s.skip_nonfinite && !isfinite(*norm)) return;
     const int total_chunks = t.chunk_start[t.count];
     for (int chunk = blockIdx.x; chunk < total_chunks; chunk += gridDim.x) {
         const int ti = find_tensor(t, chunk);
@@ -313,9 +315,14 @@ extern "C" int deers_b200_grad_clip(deers_ctx* ctx, int n_tensors, const deers_o
 
 extern "C" int deers_b200_adamw_step(deers_ctx* ctx, int n_tensors, const deers_optim_tensor* tensors,
                                      const deers_adamw_hyper* h, const float* norm_dev, double max_norm) {
+    return launch_adamw(ctx, n_tensors, tensors, h, norm_dev, max_norm, false);
+}
+
+int launch_adamw(deers_ctx* ctx, int n_tensors, const deers_optim_tensor* tensors, const deers_adamw_hyper* h,
+                 const float* norm_dev, double max_norm, bool skip_nonfinite) {
     if (!ctx || !h) return DEERS_ERR_NULL;
     if (h->step < 1) return DEERS_ERR_SHAPE;
-    if (norm_dev && !(max_norm > 0.0)) return DEERS_ERR_SHAPE;
+    if (norm_dev && !(max_norm > 0.0) && !skip_nonfinite) return DEERS_ERR_SHAPE;
     int rc = check_tensors(tensors, n_tensors, true);
     if (rc) return rc;
     DEERS_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
@@ -330,7 +337,8 @@ extern "C" int deers_b200_adamw_step(deers_ctx* ctx, int n_tensors, const deers_
     s.has_decay = h->weight_decay > 0.0 ? 1 : 0;
     s.decay = (float)(1.0 - h->lr * h->weight_decay);
     s.lr = (float)h->lr; s.eps = (float)h->eps;
-    s.use_clip = norm_dev ? 1 : 0;
+    s.use_clip = (norm_dev && max_norm > 0.0) ? 1 : 0;
+    s.skip_nonfinite = (skip_nonfinite && norm_dev) ? 1 : 0;
     s.max_norm = max_norm;
     return optim_apply(ctx, n_tensors, tensors, s, norm_dev, MODE_STEP);
 }

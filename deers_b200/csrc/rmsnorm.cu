@@ -28,8 +28,9 @@ __device__ __forceinline__ float warp_sum(float v) {
 // BWD = false: y = x * inv, inv_out[row] = inv.   BWD = true: dx from x, dy and the saved inv.
 template <bool BWD, bool VEC, bool VEC2 = false>
 __global__ void __launch_bounds__(256) rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ dy,
-                                                      float* __restrict__ out, float* __restrict__ inv_io, long long rows,
-                                                      int C, float eps, float inv_n) {
+                                                      const float* __restrict__ add, float* __restrict__ out,
+                                                      float* __restrict__ inv_io, long long rows, int C, float eps,
+                                                      float inv_n) {
     const int lane = threadIdx.x & 31;
     const long long warp = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
     const long long nwarps = (long long)gridDim.x * 8;
@@ -70,6 +71,10 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const float* __restrict__ 
                     if (BWD) {
                         o.x = gv[i].x * inv - xv[i].x * k; o.y = gv[i].y * inv - xv[i].y * k;
                         o.z = gv[i].z * inv - xv[i].z * k; o.w = gv[i].w * inv - xv[i].w * k;
+                        if (add) {
+                            const float4 r = reinterpret_cast<const float4*>(add + row * C)[p];
+                            o.x = r.x + o.x; o.y = r.y + o.y; o.z = r.z + o.z; o.w = r.w + o.w;
+                        }
                     } else {
                         o.x = xv[i].x * inv; o.y = xv[i].y * inv; o.z = xv[i].z * inv; o.w = xv[i].w * inv;
                     }
@@ -105,6 +110,10 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const float* __restrict__ 
                 if (BWD) {
                     const float4 b = g4[p];
                     o.x = b.x * inv - a.x * k; o.y = b.y * inv - a.y * k; o.z = b.z * inv - a.z * k; o.w = b.w * inv - a.w * k;
+                    if (add) {
+                        const float4 r = reinterpret_cast<const float4*>(add + row * C)[p];
+                        o.x = r.x + o.x; o.y = r.y + o.y; o.z = r.z + o.z; o.w = r.w + o.w;
+                    }
                 } else {
                     o.x = a.x * inv; o.y = a.y * inv; o.z = a.z * inv; o.w = a.w * inv;
                 }
@@ -123,7 +132,11 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const float* __restrict__ 
                 inv = 1.0f / sqrtf(acc * inv_n + eps);
                 if (lane == 0) inv_io[row] = inv;
             }
-            for (int c = lane; c < C; c += 32) orow[c] = BWD ? gr[c] * inv - xr[c] * k : xr[c] * inv;
+            for (int c = lane; c < C; c += 32) {
+                float o = BWD ? gr[c] * inv - xr[c] * k : xr[c] * inv;
+                if (BWD && add) o = add[row * C + c] + o;
+                orow[c] = o;
+            }
         }
     }
 }
@@ -131,8 +144,9 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const float* __restrict__ 
 // Rows of 1025 .. 8192 elements: a whole block owns a row, which still stays in registers (one pass over HBM).
 template <bool BWD>
 __global__ void __launch_bounds__(256) rmsnorm_block_kernel(const float* __restrict__ x, const float* __restrict__ dy,
-                                                            float* __restrict__ out, float* __restrict__ inv_io, long long rows,
-                                                            int C, float eps, float inv_n) {
+                                                            const float* __restrict__ add, float* __restrict__ out,
+                                                            float* __restrict__ inv_io, long long rows, int C, float eps,
+                                                            float inv_n) {
     __shared__ float part[8];
     const int nv = C / 4;                                       // <= 256 * RN_MAXV
     for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
@@ -177,6 +191,10 @@ __global__ void __launch_bounds__(256) rmsnorm_block_kernel(const float* __restr
                 if (BWD) {
                     o.x = gv[i].x * inv - xv[i].x * k; o.y = gv[i].y * inv - xv[i].y * k;
                     o.z = gv[i].z * inv - xv[i].z * k; o.w = gv[i].w * inv - xv[i].w * k;
+                    if (add) {
+                        const float4 r = reinterpret_cast<const float4*>(add + row * C)[p];
+                        o.x = r.x + o.x; o.y = r.y + o.y; o.z = r.z + o.z; o.w = r.w + o.w;
+                    }
                 } else {
                     o.x = xv[i].x * inv; o.y = xv[i].y * inv; o.z = xv[i].z * inv; o.w = xv[i].w * inv;
                 }
@@ -187,9 +205,10 @@ __global__ void __launch_bounds__(256) rmsnorm_block_kernel(const float* __restr
 }
 
 template <bool BWD>
-int rms_launch(deers_ctx* ctx, long long rows, int C, float eps, const float* x, const float* dy, float* out, float* inv) {
+int rms_launch(deers_ctx* ctx, long long rows, int C, float eps, const float* x, const float* dy, float* out, float* inv,
+               const float* add = nullptr) {
     if (rows == 0) return DEERS_OK;
-    uintptr_t bits = (uintptr_t)x | (uintptr_t)out | (BWD ? (uintptr_t)dy : 0);
+    uintptr_t bits = (uintptr_t)x | (uintptr_t)out | (BWD ? (uintptr_t)dy : 0) | (uintptr_t)add;
     const bool aligned = (C % 4) == 0 && (bits & 15u) == 0;
     const bool vec = aligned && C <= 32 * RN_MAXV * 4;
     const long long want = (rows + 7) / 8;
@@ -198,12 +217,12 @@ int rms_launch(deers_ctx* ctx, long long rows, int C, float eps, const float* x,
     const float inv_n = (float)(1.0 / (double)C);               // mean = sum * (1/n as f64 -> f32), src/tensor.rs:461-465
     {
         KernelTimerScope ts(ctx, DEERS_K_NORM);
-        if (vec) rmsnorm_kernel<BWD, true><<<grid, 256, 0, ctx->stream>>>(x, dy, out, inv, rows, C, eps, inv_n);
+        if (vec) rmsnorm_kernel<BWD, true><<<grid, 256, 0, ctx->stream>>>(x, dy, add, out, inv, rows, C, eps, inv_n);
         else if (aligned && C <= 256 * RN_MAXV * 4) {
             const unsigned bgrid = (unsigned)(rows < cap ? rows : cap);
-            rmsnorm_block_kernel<BWD><<<bgrid, 256, 0, ctx->stream>>>(x, dy, out, inv, rows, C, eps, inv_n);
-        } else if (aligned) rmsnorm_kernel<BWD, false, true><<<grid, 256, 0, ctx->stream>>>(x, dy, out, inv, rows, C, eps, inv_n);
-        else rmsnorm_kernel<BWD, false><<<grid, 256, 0, ctx->stream>>>(x, dy, out, inv, rows, C, eps, inv_n);
+            rmsnorm_block_kernel<BWD><<<bgrid, 256, 0, ctx->stream>>>(x, dy, add, out, inv, rows, C, eps, inv_n);
+        } else if (aligned) rmsnorm_kernel<BWD, false, true><<<grid, 256, 0, ctx->stream>>>(x, dy, add, out, inv, rows, C, eps, inv_n);
+        else rmsnorm_kernel<BWD, false><<<grid, 256, 0, ctx->stream>>>(x, dy, add, out, inv, rows, C, eps, inv_n);
     }
     ctx->launches += 1;
     DEERS_CUDA_TRY(ctx, cudaGetLastError());
@@ -225,6 +244,25 @@ extern "C" int deers_b200_rmsnorm_fwd(deers_ctx* ctx, int64_t rows, int32_t C, d
     if (rc) return rc;
     DEERS_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
     return rms_launch<false>(ctx, rows, C, (float)eps, x, nullptr, y, inv_norm);
+}
+
+// Internal launchers for the model step (gpt_model.cu).
+int launch_rmsnorm_fwd(deers_ctx* ctx, long long rows, int C, double eps, const float* x, float* y, float* inv_norm) {
+    return rms_launch<false>(ctx, rows, C, (float)eps, x, nullptr, y, inv_norm);
+}
+int launch_rmsnorm_bwd(deers_ctx* ctx, long long rows, int C, const float* x, const float* inv_norm, const float* dy,
+                       const float* add, float* dx) {
+    return rms_launch<true>(ctx, rows, C, 0.f, x, dy, dx, const_cast<float*>(inv_norm), add);
+}
+
+extern "C" int deers_b200_rmsnorm_bwd_add(deers_ctx* ctx, int64_t rows, int32_t C, const float* x, const float* inv_norm,
+                                          const float* dy, const float* residual_grad, float* dx) {
+    int rc = rms_check(ctx, rows, C, x, inv_norm, dy, dx);
+    if (rc) return rc;
+    if (!residual_grad) return DEERS_ERR_NULL;
+    if ((uintptr_t)residual_grad & 3u) return DEERS_ERR_LAYOUT;
+    DEERS_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    return rms_launch<true>(ctx, rows, C, 0.f, x, dy, dx, const_cast<float*>(inv_norm), residual_grad);
 }
 
 extern "C" int deers_b200_rmsnorm_bwd(deers_ctx* ctx, int64_t rows, int32_t C, const float* x, const float* inv_norm,

@@ -329,6 +329,128 @@ int deers_b200_gemm_f16(deers_ctx* ctx, int32_t M, int32_t N, int32_t K, const v
                         const void* b, int64_t ldb, int32_t b_mn_major, void* c, int64_t ldc);
 
 /*
+ * f32 GEMM in full f32 arithmetic (FFMA; no TF32) for the projections of the f32 model: C[M,N] = A * B,
+ * C row-major with leading dimension ldc.  Replaces the `cublasGemmStridedBatchedEx` call with
+ * CUBLAS_COMPUTE_32F behind `Tensor::matmul` for f32 operands (`src/storage/cuda.rs:1098-1128`) as
+ * `Linear::forward` uses it (`src/nn.rs:184-190`, weight stored [in_features, out_features]) and as the
+ * matmul backward does (`src/ops.rs:1089-1101`); operand orders as for deers_b200_gemm_f16:
+ *     a_mn_major = 0: A is stored [M][K] (K contiguous);   1: A is stored [K][M] (M contiguous)
+ *     b_mn_major = 0: B is stored [N][K] (K contiguous);   1: B is stored [K][N] (N contiguous)
+ *     forward  y  = x  W     : gemm(M=rows, N=out, K=in,  x, 0,  W, 1)
+ *     dgrad    dx = dy W^T   : gemm(M=rows, N=in,  K=out, dy, 0, W, 0)
+ *     wgrad    dW = x^T dy   : gemm(M=in,   N=out, K=rows, x, 1, dy, 1)
+ * Any leading dimension and any 4-byte aligned pointer is accepted (16-byte loads are used when base and
+ * leading dimension allow).  An optional epilogue runs on the tile while it is in registers and replaces the
+ * element-wise graph ops around the projections:
+ *     DEERS_EPI_ADD       C = residual + A*B                 `x + attn(...)`, `x + mlp(...)` (`src/models/gpt.rs:237-239`)
+ *     DEERS_EPI_RELU_SQ   r = max(A*B, 0); C = r*r; aux = r  `relu` and `y * y` of the MLP (`gpt.rs:194-196`)
+ *     DEERS_EPI_MUL_AUX2  t = (A*B) * aux; C = t + t         their backward (`src/ops.rs:210-214, 560-568`) given aux = r
+ * aux has the shape and leading dimension of C.  Shapes with few output tiles and a long K are split along K;
+ * the parts are added in a fixed order, so results are bitwise reproducible.  `workspace` must hold
+ * deers_b200_gemm_f32_workspace_bytes(ctx, M, N, K) bytes (0 for most shapes; 256-byte aligned).  Enqueued on
+ * the context's stream; no allocation, no synchronisation.
+ */
+enum { DEERS_EPI_NONE = 0, DEERS_EPI_ADD = 1, DEERS_EPI_RELU_SQ = 2, DEERS_EPI_MUL_AUX2 = 3 };
+typedef struct deers_gemm_epilogue {
+    int32_t kind;             /* DEERS_EPI_* */
+    const float* residual;    /* DEERS_EPI_ADD: [M][ld_residual] */
+    int64_t ld_residual;
+    float* aux;               /* DEERS_EPI_RELU_SQ: written; DEERS_EPI_MUL_AUX2: read; [M][ldc] */
+} deers_gemm_epilogue;
+size_t deers_b200_gemm_f32_workspace_bytes(deers_ctx* ctx, int32_t M, int32_t N, int32_t K);
+int deers_b200_gemm_f32(deers_ctx* ctx, int32_t M, int32_t N, int32_t K, const float* a, int64_t lda, int32_t a_mn_major,
+                        const float* b, int64_t ldb, int32_t b_mn_major, float* c, int64_t ldc,
+                        const deers_gemm_epilogue* epilogue, void* workspace, size_t workspace_bytes);
+
+/*
+ * RMSNorm backward that also adds the gradient arriving over the residual connection:
+ * dx = residual_grad + (dy*inv - x * (sum(dy*x) * inv^3 / C)).  In the block `x + f(norm(x))`
+ * (`src/models/gpt.rs:236-240`) the reference's GradientStore adds the two contributions to x with a separate
+ * element-wise add (`src/backprop.rs:101-112`).
+ */
+int deers_b200_rmsnorm_bwd_add(deers_ctx* ctx, int64_t rows, int32_t C, const float* x, const float* inv_norm,
+                               const float* dy, const float* residual_grad, float* dx);
+
+/*
+ * Embedding lookup and its backward, f32 table [vocab, C], int64 token ids on the device.  Replaces
+ * `Embedding::forward` (`src/nn.rs:214-221`: `index_select(0, ids)`, kernel `src/storage/cuda.rs:381-390`) and
+ * the index_add of its backward (`src/storage/cuda.rs:392-402`, atomic adds into a zeroed table).  bwd zeroes
+ * dweight and adds the rows of dout in token order (the first occurrence of an id owns the row), so repeated
+ * tokens give a reproducible sum equal to the CPU backend's.  An id outside [0, vocab) makes the next
+ * deers_b200_sync return DEERS_ERR_KERNEL; the row is skipped (forward: written as zeros).
+ */
+int deers_b200_embedding_fwd(deers_ctx* ctx, const float* weight, const int64_t* ids, int64_t n_ids, int32_t C,
+                             int64_t vocab, float* out);
+int deers_b200_embedding_bwd(deers_ctx* ctx, const float* dout, const int64_t* ids, int64_t n_ids, int32_t C,
+                             int64_t vocab, float* dweight);
+
+/*
+ * Cross-entropy over [rows, vocab] f32 logits (row stride ld) with int64 targets on the device.  Replaces
+ * `loss::cross_entropy` (`src/loss.rs:21-24`: log_softmax, gather, sum, scalar multiply) and its backward.
+ *   fwd  lse[row] = ln(sum exp(x - max)) + max (`src/storage/cpu.rs:755-770`); loss[0] = sum over rows of
+ *        (x[target] - lse) * (float)(-1/rows).  The log-probabilities are never written.  `scratch`:
+ *        deers_b200_cross_entropy_scratch_bytes(rows) of device memory.
+ *   bwd  dlogits = (onehot * g - exp(x - lse) * g) * upstream, g = (float)(-1/rows): gather backward and the
+ *        `x - lse` backward (`src/ops.rs:210-214, 777-799, 1162-1175`) in one pass; dlogits may be the logits
+ *        buffer itself (in place).  `upstream` is the gradient of the loss (1 for `loss.backward()`).  rows <= 65535.
+ */
+size_t deers_b200_cross_entropy_scratch_bytes(int64_t rows);
+int deers_b200_cross_entropy_fwd(deers_ctx* ctx, int64_t rows, int64_t vocab, const float* logits, int64_t ld,
+                                 const int64_t* targets, float* lse, float* loss, void* scratch, size_t scratch_bytes);
+int deers_b200_cross_entropy_bwd(deers_ctx* ctx, int64_t rows, int64_t vocab, const float* logits, int64_t ld,
+                                 const int64_t* targets, const float* lse, float upstream, float* dlogits,
+                                 int64_t ld_dlogits);
+
+/*
+ * The GPT of `src/models/gpt.rs` as one device-resident object: parameters, gradients, AdamW moments and
+ * activations live in device memory owned by the model; a training step is `GPT::forward` (`gpt.rs:329-355`) ->
+ * `loss::cross_entropy` (`src/loss.rs:21-24`) -> `backward()` -> `clip_grad_norm` (`src/optim.rs:257-297`) ->
+ * `AdamW::step_with_grads` (`src/optim.rs:214-251`), the loop body of `examples/tinystories_train.rs:188-218`
+ * with one micro-batch, enqueued as about 160 kernels of this library and nothing else (no host round trip:
+ * the clip decision and the "skip the update when the norm is not finite" rule of the trainer are taken on the
+ * device).  After the first step of a (B, T) the forward/backward part is replayed from a CUDA graph.
+ *
+ * deers_gpt_config mirrors `GPTConfig` (`gpt.rs:259-285`).  Parameters are addressed by index in the order of
+ * `GPT::parameters` (`gpt.rs:358-365`): 0 wte.weight [vocab, n_embd]; then per block q_proj, k_proj, v_proj,
+ * out_proj [n_embd, n_embd], up_proj [n_embd, mlp], down_proj [mlp, n_embd]; last lm_head.weight [n_embd, vocab];
+ * names as the reference's checkpoint keys (`blocks.{i}.attn.q_proj.weight`, ...).  Host arrays passed to
+ * param_set / param_get are compact row-major [rows, cols]; internally q, k and v of a block share one
+ * [n_embd, 3*n_embd] buffer so the three projections are one GEMM.
+ *   create           allocates everything for up to max_batch * sequence_len tokens; weights start at zero.
+ *   param_set/get    upload / read back one tensor: what = 0 weight, 1 gradient, 2 first moment, 3 second moment.
+ *   forward          logits [B*T, vocab] (compact, device) for ids [B*T] (device); logits may be NULL.
+ *   forward_backward forward, loss and every parameter gradient; loss_dev (1 float, device) may be NULL.
+ *   train_step       forward_backward, then gradient norm (written to grad_norm_dev if not NULL), clip at
+ *                    max_grad_norm (<= 0: no clipping) and the AdamW update; hyper->step is t >= 1.
+ *   train_step_host  the same with ids / targets in host memory and the loss read back: copies 16*B*T bytes in,
+ *                    4 bytes out and synchronises.
+ * Everything is enqueued on the context's stream; only create, param_get and train_step_host synchronise.
+ */
+typedef struct deers_gpt_config {
+    int32_t vocab_size, sequence_len, n_layer, n_head, n_embd, mlp_hidden_dim;
+    double rms_norm_eps;
+    float rope_base;
+} deers_gpt_config;
+typedef struct deers_gpt deers_gpt;
+int deers_b200_gpt_create(deers_ctx* ctx, const deers_gpt_config* config, int32_t max_batch, deers_gpt** out);
+void deers_b200_gpt_destroy(deers_gpt* model);
+int deers_b200_gpt_num_params(const deers_gpt* model);
+int deers_b200_gpt_param_info(const deers_gpt* model, int index, char* name, size_t name_bytes, int64_t* rows,
+                              int64_t* cols);
+int deers_b200_gpt_param_set(deers_gpt* model, int index, int what, const float* host);
+int deers_b200_gpt_param_get(deers_gpt* model, int index, int what, float* host);
+int deers_b200_gpt_set_graph(deers_gpt* model, int enable);
+int deers_b200_gpt_forward(deers_gpt* model, const int64_t* ids, int32_t B, int32_t T, float* logits);
+int deers_b200_gpt_forward_backward(deers_gpt* model, const int64_t* ids, const int64_t* targets, int32_t B, int32_t T,
+                                    float* loss_dev);
+int deers_b200_gpt_train_step(deers_gpt* model, const int64_t* ids, const int64_t* targets, int32_t B, int32_t T,
+                              const deers_adamw_hyper* hyper, double max_grad_norm, float* loss_dev,
+                              float* grad_norm_dev);
+int deers_b200_gpt_train_step_host(deers_gpt* model, const int64_t* ids_host, const int64_t* targets_host, int32_t B,
+                                   int32_t T, const deers_adamw_hyper* hyper, double max_grad_norm, float* loss_host,
+                                   float* grad_norm_host);
+
+/*
  * Status text, the way backend failures become `Error::Cuda(String)`
  * (`src/error.rs:40-41`).  last_error adds the detail of the most recent failure
  * on this context (CUDA error string, or which kernel wait gave up).
@@ -350,7 +472,7 @@ uint64_t deers_b200_launch_count(deers_ctx* ctx);
  * milliseconds and the number of launches of one kernel kind since timing was
  * enabled (or since the last call with reset != 0).
  */
-enum { DEERS_K_FWD = 0, DEERS_K_BWD_PREP = 1, DEERS_K_BWD_MAIN = 2, DEERS_K_BWD_DQ = 3, DEERS_K_ROPE = 4, DEERS_K_OPTIM = 5, DEERS_K_NORM = 6, DEERS_K_DECODE = 7, DEERS_K_GEMM = 8, DEERS_K_COUNT = 9 };
+enum { DEERS_K_FWD = 0, DEERS_K_BWD_PREP = 1, DEERS_K_BWD_MAIN = 2, DEERS_K_BWD_DQ = 3, DEERS_K_ROPE = 4, DEERS_K_OPTIM = 5, DEERS_K_NORM = 6, DEERS_K_DECODE = 7, DEERS_K_GEMM = 8, DEERS_K_GPT = 9, DEERS_K_COUNT = 10 };
 int deers_b200_kernel_timing(deers_ctx* ctx, int enable);
 int deers_b200_kernel_time(deers_ctx* ctx, int kind, int reset, double* total_ms, uint64_t* launches);
 

@@ -45,6 +45,17 @@ API int ref_num_threads(void) {
 #endif
 }
 
+/* Sets the OpenMP thread count (launchers may export OMP_NUM_THREADS=1); returns the count in use. */
+API int ref_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+    return omp_get_max_threads();
+#else
+    (void)n;
+    return 1;
+#endif
+}
+
 /* src/nn/functional.rs:12-55 — [batch, 1, tgt_len, tgt_len + offset], 0 or -inf. */
 API void ref_causal_mask(int batch, int tgt_len, int offset, float* out) {
     const int total = tgt_len + offset;

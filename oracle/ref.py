@@ -18,9 +18,9 @@ _lib = None
 
 
 def build(force: bool = False) -> str:
-    """Compile ``attn_ref.c`` with the Makefile beside it; returns the .so path."""
-    src = os.path.join(_HERE, "attn_ref.c")
-    stale = (not os.path.exists(_SO)) or os.path.getmtime(_SO) < os.path.getmtime(src)
+    """Compile ``attn_ref.c`` and ``gpt_ref.c`` with the Makefile beside them; returns the .so path."""
+    srcs = [os.path.join(_HERE, f) for f in ("attn_ref.c", "gpt_ref.c")]
+    stale = (not os.path.exists(_SO)) or any(os.path.getmtime(_SO) < os.path.getmtime(s) for s in srcs)
     if force or stale:
         subprocess.run(["make", "-C", _HERE, "-B", "_build/libattn_ref.so"], check=True,
                        stdout=subprocess.DEVNULL)
@@ -49,6 +49,27 @@ def lib() -> ctypes.CDLL:
         L.ref_attn_fwd_bwd.argtypes = ([fp, fp, fp, fp] + [ctypes.c_int] * 4 +
                                        [ctypes.c_float, ctypes.c_int] + [fp] * 5)
         L.ref_attn_fwd_bwd.restype = ctypes.c_int
+        ll, lp = ctypes.c_longlong, ctypes.POINTER(ctypes.c_longlong)
+        for name in ("ref_matmul_nn", "ref_matmul_nt", "ref_matmul_tn"):
+            getattr(L, name).argtypes = [fp, fp, fp, ll, ll, ll]
+            getattr(L, name).restype = None
+        L.ref_set_num_threads.argtypes = [ctypes.c_int]
+        L.ref_set_num_threads.restype = ctypes.c_int
+        L.ref_embedding_fwd.argtypes = [fp, lp, ll, ctypes.c_int, fp]
+        L.ref_embedding_fwd.restype = None
+        L.ref_embedding_bwd.argtypes = [fp, lp, ll, ctypes.c_int, ll, fp]
+        L.ref_embedding_bwd.restype = None
+        L.ref_cross_entropy_fwd.argtypes = [fp, lp, ll, ll, fp, fp]
+        L.ref_cross_entropy_fwd.restype = ctypes.c_float
+        L.ref_nll_loss.argtypes = [fp, lp, ll, ll, fp]
+        L.ref_nll_loss.restype = ctypes.c_float
+        L.ref_cross_entropy_bwd.argtypes = [fp, lp, ll, ll, fp]
+        L.ref_cross_entropy_bwd.restype = None
+        L.ref_rotary_cache.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_float, fp, fp]
+        L.ref_rotary_cache.restype = None
+        L.ref_gpt_step.argtypes = [ctypes.POINTER(ctypes.c_int), ctypes.c_double, ctypes.c_float, ctypes.c_int,
+                                   ctypes.c_int, lp, lp, ctypes.POINTER(fp), fp, fp, ctypes.POINTER(fp)]
+        L.ref_gpt_step.restype = ctypes.c_int
         _lib = L
     return _lib
 
@@ -210,3 +231,130 @@ def attn_decode(q, k, v, scale=None, causal=True):
     lse = (np.log(e.sum(axis=3, keepdims=True, dtype=np.float32)) + m).astype(np.float32)
     p = np.exp(s - lse).astype(np.float32)
     return np.einsum("bhij,bhjd->bhid", p, v).astype(np.float32), lse[..., 0]
+
+
+def set_num_threads(n: int | None = None) -> int:
+    """Makes the oracle's OpenMP loops use ``n`` threads (default: every core this process may run on,
+    whatever OMP_NUM_THREADS says: launchers such as torchrun export OMP_NUM_THREADS=1).  Returns n."""
+    if n is None:
+        n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    return int(lib().ref_set_num_threads(int(n)))
+
+
+def _ids(a):
+    a = np.ascontiguousarray(a, dtype=np.int64)
+    return a, a.ctypes.data_as(ctypes.POINTER(ctypes.c_longlong))
+
+
+def matmul(a, b, kind: str = "nn"):
+    """f32 matmul with k-sequential sums: nn: a[M,K] @ b[K,N]; nt: a[M,K] @ b[N,K]^T; tn: a[K,M]^T @ b[K,N]."""
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    b = np.ascontiguousarray(b, dtype=np.float32)
+    if kind == "nn":
+        (M, K), N = a.shape, b.shape[1]
+    elif kind == "nt":
+        (M, K), N = a.shape, b.shape[0]
+    else:
+        (K, M), N = a.shape, b.shape[1]
+    c = np.empty((M, N), np.float32)
+    getattr(lib(), f"ref_matmul_{kind}")(_p(a), _p(b), _p(c), M, N, K)
+    return c
+
+
+def embedding_fwd(weight, ids):
+    weight = np.ascontiguousarray(weight, dtype=np.float32)
+    ids_a, ids_p = _ids(ids)
+    out = np.empty((ids_a.size, weight.shape[1]), np.float32)
+    lib().ref_embedding_fwd(_p(weight), ids_p, ids_a.size, weight.shape[1], _p(out))
+    return out
+
+
+def embedding_bwd(dout, ids, vocab: int):
+    dout = np.ascontiguousarray(dout, dtype=np.float32)
+    ids_a, ids_p = _ids(ids)
+    dw = np.empty((vocab, dout.shape[1]), np.float32)
+    lib().ref_embedding_bwd(_p(dout), ids_p, ids_a.size, dout.shape[1], vocab, _p(dw))
+    return dw
+
+
+def nll_loss(log_probs, targets, with_grad: bool = False):
+    """nll_loss (loss.rs:11-15); with_grad also returns d loss / d log_probs."""
+    lp = np.ascontiguousarray(log_probs, dtype=np.float32)
+    t_a, t_p = _ids(targets)
+    g = np.empty_like(lp) if with_grad else None
+    loss = float(lib().ref_nll_loss(_p(lp), t_p, lp.shape[0], lp.shape[1], _p(g)))
+    return (loss, g) if with_grad else loss
+
+
+def cross_entropy(logits, targets, with_grad: bool = False):
+    """cross_entropy (loss.rs:21-24): returns loss, or (loss, lse, dlogits)."""
+    x = np.ascontiguousarray(logits, dtype=np.float32)
+    t_a, t_p = _ids(targets)
+    lse = np.empty(x.shape[0], np.float32)
+    loss = float(lib().ref_cross_entropy_fwd(_p(x), t_p, x.shape[0], x.shape[1], None, _p(lse)))
+    if not with_grad:
+        return loss
+    d = np.empty_like(x)
+    lib().ref_cross_entropy_bwd(_p(x), t_p, x.shape[0], x.shape[1], _p(d))
+    return loss, lse, d
+
+
+def rotary_cache(T: int, D: int, base: float = 10000.0):
+    cos = np.empty((T, D // 2), np.float32)
+    sin = np.empty((T, D // 2), np.float32)
+    lib().ref_rotary_cache(T, D, base, _p(cos), _p(sin))
+    return cos, sin
+
+
+def gpt_param_shapes(vocab: int, n_layer: int, n_head: int, n_embd: int, mlp_hidden: int):
+    """(name, shape) of every parameter in the order of GPT::parameters (gpt.rs:358-365)."""
+    out = [("wte.weight", (vocab, n_embd))]
+    for i in range(n_layer):
+        for n in ("q_proj", "k_proj", "v_proj", "out_proj"):
+            out.append((f"blocks.{i}.attn.{n}.weight", (n_embd, n_embd)))
+        out.append((f"blocks.{i}.mlp.up_proj.weight", (n_embd, mlp_hidden)))
+        out.append((f"blocks.{i}.mlp.down_proj.weight", (mlp_hidden, n_embd)))
+    out.append(("lm_head.weight", (n_embd, vocab)))
+    return out
+
+
+def gpt_init_params(cfg, seed: int = 0):
+    """Random-init weights with the reference's distributions (nn.rs:166-176: uniform [-k, k], k = 1/sqrt(in);
+    nn.rs:209-212: standard normal embedding) from a numpy seed (the reference's RNG is unseeded)."""
+    rng = np.random.default_rng(seed)
+    params = []
+    for name, shape in gpt_param_shapes(*cfg):
+        if name == "wte.weight":
+            params.append(rng.standard_normal(shape).astype(np.float32))
+        else:
+            k = 1.0 / np.sqrt(shape[0])
+            params.append((rng.random(shape, dtype=np.float32) * np.float32(2.0 * k) - np.float32(k)).astype(np.float32))
+    return params
+
+
+def gpt_step(cfg, params, ids, targets=None, B=None, T=None, eps: float = 1e-5, rope_base: float = 10000.0,
+             want_logits: bool = True, want_grads: bool = True):
+    """One forward (+ cross-entropy + backward) of the reference GPT on the CPU.  cfg = (vocab, n_layer, n_head,
+    n_embd, mlp_hidden); params as from gpt_init_params; ids [B, T].  Returns dict(logits, loss, grads)."""
+    ids = np.asarray(ids)
+    if B is None:
+        B, T = ids.shape
+    ids_a, ids_p = _ids(ids.reshape(-1))
+    V = cfg[0]
+    fpp = ctypes.POINTER(ctypes.c_float)
+    params = [np.ascontiguousarray(p, dtype=np.float32) for p in params]
+    parr = (fpp * len(params))(*[_p(p) for p in params])
+    logits = np.empty((B * T, V), np.float32) if want_logits else None
+    loss = np.zeros(1, np.float32)
+    tgt_p = None
+    grads = garr = None
+    if targets is not None:
+        t_a, tgt_p = _ids(np.asarray(targets).reshape(-1))
+        if want_grads:
+            grads = [np.empty_like(p) for p in params]
+            garr = (fpp * len(grads))(*[_p(g) for g in grads])
+    ccfg = (ctypes.c_int * 5)(*cfg)
+    rc = lib().ref_gpt_step(ccfg, eps, rope_base, B, T, ids_p, tgt_p, parr, _p(logits), _p(loss), garr)
+    if rc:
+        raise MemoryError("oracle: allocation failed")
+    return {"logits": logits, "loss": float(loss[0]) if targets is not None else None, "grads": grads}

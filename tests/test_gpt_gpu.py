@@ -1,0 +1,296 @@
+"""GPU parity tests of the f32 GPT step (BASELINE cfg 3) and its building blocks, through the C ABI,
+against the CPU oracle and the float64 golden vectors."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import ref
+from tests.helpers import REF_ABS_TOL_ACCEL
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+DEV = "cuda"
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
+
+
+def golden_cases():
+    blob = np.load(os.path.join(HERE, "golden", "gpt_golden.npz"))
+    cases = {}
+    for key in blob.files:
+        name, field = key.split("/")
+        cases.setdefault(name, {})[field] = blob[key]
+    return cases
+
+
+def rel(got, want):
+    got, want = np.asarray(got, np.float64), np.asarray(want, np.float64)
+    assert np.isfinite(got).all()
+    return float(np.abs(got - want).max() / max(np.abs(want).max(), 1e-30))
+
+
+# ---- f32 GEMM ---------------------------------------------------------------------------------------
+GEMM_SHAPES = [  # M, N, K: every tile shape, split-K, ragged edges, the cfg 3 projections (tokens 1024, C 192)
+    (1, 1, 1), (6, 8, 4), (65, 130, 33), (128, 128, 16), (257, 190, 100),
+    (1024, 576, 192), (1024, 192, 192), (1024, 768, 192), (1024, 192, 768),
+    (192, 576, 1024), (192, 192, 1024), (768, 192, 1024), (192, 768, 1024), (1024, 192, 576),
+    (1024, 5003, 192), (192, 5003, 1024), (1024, 192, 5003), (2048, 2048, 64),
+]
+
+
+@pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
+@pytest.mark.parametrize("a_mn,b_mn", [(0, 1), (0, 0), (1, 1), (1, 0)])
+def test_gemm_f32_matches_float64(M, N, K, a_mn, b_mn):
+    from deers_b200 import gpt
+    rng = np.random.default_rng(M * 7 + N * 3 + K)
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    b = rng.standard_normal((K, N)).astype(np.float32)
+    want = a.astype(np.float64) @ b.astype(np.float64)
+    ta = dev(a.T) if a_mn else dev(a)
+    tb = dev(b) if b_mn else dev(b.T)
+    got = gpt.gemm_f32(ta, tb, bool(a_mn), bool(b_mn))
+    got2 = gpt.gemm_f32(ta, tb, bool(a_mn), bool(b_mn))
+    torch.cuda.synchronize()
+    # f32 accumulation of K terms: error grows like sqrt(K) * 2^-24 of the row scale
+    assert rel(got.cpu().numpy(), want) < 2e-6 * max(1.0, np.sqrt(K) / 4)
+    assert torch.equal(got, got2), "split-K sums must not depend on arrival order"
+
+
+def test_gemm_f32_unaligned_views_and_oracle():
+    """Leading dimensions and base pointers that rule out 16-byte loads, checked against the oracle's matmul."""
+    from deers_b200 import gpt
+    rng = np.random.default_rng(5)
+    M, N, K = 70, 45, 37
+    big_a = dev(rng.standard_normal((M, K + 3)).astype(np.float32))
+    big_b = dev(rng.standard_normal((K, N + 5)).astype(np.float32))
+    a, b = big_a[:, 1:K + 1], big_b[:, 2:N + 2]
+    out = torch.full((M, N + 1), float("nan"), device=DEV)
+    gpt.gemm_f32(a, b, out=out[:, :N])
+    torch.cuda.synchronize()
+    want = ref.matmul(a.cpu().numpy(), b.cpu().numpy(), "nn")
+    assert rel(out[:, :N].cpu().numpy(), want) < 1e-5
+    assert torch.isnan(out[:, N]).all(), "columns beyond N must stay untouched"
+
+
+def test_gemm_f32_epilogues():
+    from deers_b200 import _lib, gpt
+    rng = np.random.default_rng(6)
+    M, N, K = 300, 200, 192
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    b = (rng.standard_normal((K, N)) / np.sqrt(K)).astype(np.float32)
+    r = rng.standard_normal((M, N)).astype(np.float32)
+    acc = a.astype(np.float64) @ b.astype(np.float64)
+    ta, tb, tr = dev(a), dev(b), dev(r)
+    got = gpt.gemm_f32(ta, tb, epilogue=_lib.EPI_ADD, residual=tr)
+    assert rel(got.cpu().numpy(), r + acc) < 1e-5
+    aux = torch.empty((M, N), device=DEV)
+    got = gpt.gemm_f32(ta, tb, epilogue=_lib.EPI_RELU_SQ, aux=aux)
+    relu = np.maximum(acc, 0.0)
+    assert rel(aux.cpu().numpy(), relu) < 1e-5
+    assert rel(got.cpu().numpy(), relu * relu) < 1e-5
+    got = gpt.gemm_f32(ta, tb, epilogue=_lib.EPI_MUL_AUX2, aux=tr)
+    assert rel(got.cpu().numpy(), 2.0 * acc * r) < 1e-5
+    # split-K shape with an epilogue (the backward of relu^2 on a wide hidden layer)
+    a2 = rng.standard_normal((64, 4096)).astype(np.float32)
+    b2 = (rng.standard_normal((4096, 64)) / 64).astype(np.float32)
+    r2 = rng.standard_normal((64, 64)).astype(np.float32)
+    got = gpt.gemm_f32(dev(a2), dev(b2), epilogue=_lib.EPI_ADD, residual=dev(r2))
+    assert rel(got.cpu().numpy(), r2 + a2.astype(np.float64) @ b2.astype(np.float64)) < 1e-5
+
+
+def test_gemm_f32_rejects_bad_arguments():
+    from deers_b200 import _lib, gpt
+    from deers_b200.errors import CudaError, LayoutMismatch
+    a = torch.zeros((4, 4), device=DEV)
+    with pytest.raises(LayoutMismatch):
+        gpt.gemm_f32(a, torch.zeros((5, 4), device=DEV))
+    with pytest.raises(CudaError):
+        gpt.gemm_f32(a, a, epilogue=_lib.EPI_ADD)            # residual missing -> DEERS_ERR_NULL
+
+
+# ---- embedding, cross-entropy -------------------------------------------------------------------------
+def test_embedding_bit_exact_with_repeated_tokens():
+    from deers_b200 import gpt
+    rng = np.random.default_rng(2)
+    V, C, n = 97, 24, 300                                   # 300 draws from 97 ids: many repeats
+    w = rng.standard_normal((V, C)).astype(np.float32)
+    ids = rng.integers(0, V, n)
+    d = rng.standard_normal((n, C)).astype(np.float32)
+    out = gpt.embedding(dev(w), dev(ids))
+    dw = gpt.embedding_backward(dev(d), dev(ids), V)
+    dw2 = gpt.embedding_backward(dev(d), dev(ids), V)
+    torch.cuda.synchronize()
+    assert np.array_equal(out.cpu().numpy(), ref.embedding_fwd(w, ids))
+    assert np.array_equal(dw.cpu().numpy(), ref.embedding_bwd(d, ids, V)), "token-order sum, as the CPU backend"
+    assert torch.equal(dw, dw2)
+    # odd width (scalar path)
+    w7 = rng.standard_normal((V, 7)).astype(np.float32)
+    assert np.array_equal(gpt.embedding(dev(w7), dev(ids)).cpu().numpy(), ref.embedding_fwd(w7, ids))
+
+
+def test_embedding_out_of_range_id_is_reported_not_trapped():
+    from deers_b200 import gpt, ops
+    from deers_b200.errors import CudaError
+    w = torch.ones((5, 8), device=DEV)
+    out = gpt.embedding(w, torch.tensor([1, 7, 2], device=DEV))
+    with pytest.raises(CudaError):
+        ops.Context.current(w.device).sync()
+    assert out[1].abs().max().item() == 0.0 and out[0].min().item() == 1.0
+    ops.Context.current(w.device).sync()                     # the error word is cleared: the next sync is clean
+    assert gpt.embedding(w, torch.tensor([4], device=DEV)).min().item() == 1.0
+
+
+def test_cross_entropy_reference_literals():
+    """src/loss.rs:67-84 on the device: gradient rows of cross_entropy sum to zero."""
+    from deers_b200 import gpt
+    logits = dev(np.array([[1.0, 2.0, 3.0], [1.0, -1.0, 0.0]], np.float32))
+    loss, lse, d = gpt.cross_entropy(logits, dev(np.array([2, 0])), with_grad=True)
+    torch.cuda.synchronize()
+    assert d.shape == (2, 3) and d.sum(1).abs().max().item() < 1e-4
+    want_loss, want_lse, want_d = ref.cross_entropy(logits.cpu().numpy(), [2, 0], with_grad=True)
+    assert abs(loss.item() - want_loss) < 1e-6
+    assert np.abs(d.cpu().numpy() - want_d).max() < 1e-7
+
+
+@pytest.mark.parametrize("rows,V,ld", [(5, 7, 7), (33, 1000, 1000), (64, 50257, 50260), (3, 4099, 4100)])
+def test_cross_entropy_matches_oracle(rows, V, ld):
+    from deers_b200 import gpt
+    rng = np.random.default_rng(rows + V)
+    x = (rng.standard_normal((rows, V)) * 3).astype(np.float32)
+    t = rng.integers(0, V, rows)
+    buf = torch.zeros((rows, ld), device=DEV)
+    buf[:, :V] = dev(x)
+    loss, lse, d = gpt.cross_entropy(buf[:, :V], dev(t), with_grad=True)
+    torch.cuda.synchronize()
+    want_loss, want_lse, want_d = ref.cross_entropy(x, t, with_grad=True)
+    assert abs(loss.item() - want_loss) < 2e-6 * max(1.0, abs(want_loss))
+    assert np.abs(lse.cpu().numpy() - want_lse).max() < 1e-5
+    assert rel(d.cpu().numpy(), want_d) < 1e-5
+
+
+# ---- the model ------------------------------------------------------------------------------------------
+def build_model(cfg, B, T, params):
+    from deers_b200 import gpt
+    V, L, H, C, Hm = cfg
+    m = gpt.GPT(gpt.GPTConfig(V, T, L, H, C, Hm), torch.device("cuda", torch.cuda.current_device()), B)
+    m.load_parameters(params)
+    return m
+
+
+@pytest.mark.parametrize("name", ["tests_gpt_rs", "two_layer_V37"])
+def test_gpt_matches_golden_and_oracle(name):
+    """The reference's own model test (tests/gpt.rs:272-343: logits, loss and every parameter gradient at
+    vocab 8, 1 layer, 2 heads of head_dim 2, B=2, T=3, its token ids) with its accelerator tolerance 2e-3, and
+    1e-4 of max-abs against the CPU oracle."""
+    g = golden_cases()[name]
+    V, L, H, C, Hm, B, T = (int(v) for v in g["cfg"])
+    n = 2 + 6 * L
+    params = [g[f"param{i}"] for i in range(n)]
+    m = build_model((V, L, H, C, Hm), B, T, params)
+    ids, tgt = dev(g["ids"].reshape(B, T)), dev(g["targets"])
+    logits = m.forward(ids)
+    loss = m.forward_backward(ids, tgt)
+    m.ctx.sync()
+    want = ref.gpt_step((V, L, H, C, Hm), params, g["ids"].reshape(B, T), g["targets"])
+    got_logits = logits.cpu().numpy().reshape(B * T, V)
+    assert np.abs(got_logits - g["logits"]).max() < REF_ABS_TOL_ACCEL
+    assert abs(loss.item() - float(g["loss"])) < REF_ABS_TOL_ACCEL
+    assert rel(got_logits, want["logits"]) < 1e-4
+    assert abs(loss.item() - want["loss"]) < 1e-5
+    for i in range(n):
+        got = m.grad(i)
+        assert np.abs(got - g[f"grad{i}"]).max() < REF_ABS_TOL_ACCEL, m.parameter_info(i)
+        assert np.abs(got - want["grads"][i]).max() <= 1e-4 * np.abs(want["grads"][i]).max() + 1e-7, m.parameter_info(i)
+    names = [nm for nm, _ in m.named_parameters()]
+    assert names == [nm for nm, _ in ref.gpt_param_shapes(V, L, H, C, Hm)]
+
+
+CFG3 = (50257, 6, 6, 192, 768)       # BASELINE cfg 3: vocab, layers, heads, n_embd, mlp hidden; B=4, T=256
+
+
+@pytest.fixture(scope="module")
+def cfg3_case():
+    params = ref.gpt_init_params(CFG3, seed=0)
+    rng = np.random.default_rng(1)
+    ids = rng.integers(0, CFG3[0], (4, 256))
+    tgt = rng.integers(0, CFG3[0], 4 * 256)
+    ref.set_num_threads()
+    want = ref.gpt_step(CFG3, params, ids, tgt)
+    return params, ids, tgt, want
+
+
+def test_gpt_cfg3_forward_backward_matches_oracle(cfg3_case):
+    """BASELINE cfg 3 at full size: logits, loss and all 38 parameter gradients against the CPU oracle.  Tolerance:
+    the reference's accelerator tolerance (abs 2e-3, tests/gpt.rs:8-9) and 2e-4 of each tensor's max-abs."""
+    params, ids, tgt, want = cfg3_case
+    m = build_model(CFG3, 4, 256, params)
+    logits = m.forward(dev(ids))
+    loss = m.forward_backward(dev(ids), dev(tgt))
+    m.ctx.sync()
+    got_logits = logits.cpu().numpy().reshape(1024, CFG3[0])
+    assert np.abs(got_logits - want["logits"]).max() < REF_ABS_TOL_ACCEL
+    assert rel(got_logits, want["logits"]) < 2e-4
+    assert abs(loss.item() - want["loss"]) < 1e-4
+    for i in range(m.num_parameters()):
+        got, w = m.grad(i), want["grads"][i]
+        assert np.isfinite(got).all()
+        err = np.abs(got - w).max()
+        assert err < REF_ABS_TOL_ACCEL and err <= 2e-4 * np.abs(w).max() + 1e-9, (m.parameter_info(i), err, np.abs(w).max())
+
+
+def test_gpt_cfg3_training_steps_follow_oracle(cfg3_case):
+    """Four optimizer steps on the same batch (eager, graph capture, two graph replays): the loss of every step
+    follows the CPU oracle (forward/backward restatement + the bit-exact AdamW and clip restatements)."""
+    params, ids, tgt, _ = cfg3_case
+    m = build_model(CFG3, 4, 256, params)
+    lr, wd, max_norm = 5e-4, 0.1, 1.0
+    w = [p.copy() for p in params]
+    mom = [(np.zeros_like(p), np.zeros_like(p)) for p in params]
+    losses, norms, want_losses, want_norms = [], [], [], []
+    for step in range(1, 5):
+        loss, norm = m.train_step(dev(ids), dev(tgt), lr=lr, weight_decay=wd, max_grad_norm=max_norm)
+        losses.append(loss.item()); norms.append(norm.item())
+        r = ref.gpt_step(CFG3, w, ids, tgt, want_logits=False)
+        want_losses.append(r["loss"])
+        want_norms.append(ref.clip_grad_norm(r["grads"], max_norm))
+        for p, g, (m1, v1) in zip(w, r["grads"], mom):
+            ref.adamw_step(p, g, m1, v1, step, lr, weight_decay=wd)
+    m.ctx.sync()
+    assert np.abs(np.array(losses) - np.array(want_losses)).max() < 1e-3, (losses, want_losses)
+    assert np.abs(np.array(norms) - np.array(want_norms)).max() < 1e-3 * max(want_norms), (norms, want_norms)
+    assert losses[-1] < losses[0], "the loss goes down on a repeated batch"
+    # Adam's update is lr * m_hat / (sqrt(v_hat) + eps): an element whose gradient is rounding noise may move by up
+    # to lr per step in either direction, so the bound on single elements is loose and the bulk is checked tightly.
+    for i in range(m.num_parameters()):
+        diff = np.abs(m.parameter(i) - w[i])
+        assert diff.max() <= 2 * 4 * lr, (m.parameter_info(i), diff.max())
+        assert np.median(diff) < 1e-6, (m.parameter_info(i), np.median(diff))
+
+
+def test_gpt_host_step_and_graph_toggle(cfg3_case):
+    """train_step_host (ids from host memory, loss read back) gives the same losses with and without graph replay."""
+    params, ids, tgt, _ = cfg3_case
+    runs = []
+    for graph in (True, False):
+        m = build_model(CFG3, 4, 256, params)
+        m.set_graph(graph)
+        runs.append([m.train_step_host(ids, tgt, lr=5e-4, weight_decay=0.1, max_grad_norm=1.0) for _ in range(3)])
+    assert runs[0] == runs[1], "graph replay and eager launches run the same kernels: bitwise equal"
+    assert all(np.isfinite(v) for pair in runs[0] for v in pair)
+
+
+def test_gpt_rejects_bad_shapes():
+    from deers_b200 import gpt
+    from deers_b200.errors import CudaError
+    d = torch.device("cuda", torch.cuda.current_device())
+    with pytest.raises(CudaError):
+        gpt.GPT(gpt.GPTConfig(8, 4, 1, 3, 4, 8), d, 2)        # n_embd not divisible by n_head
+    m = gpt.GPT(gpt.GPTConfig(8, 4, 1, 2, 4, 8), d, 2)
+    with pytest.raises(CudaError):
+        m.forward(torch.zeros((2, 5), dtype=torch.int64, device=DEV))   # longer than the rotary cache (gpt.rs:335)
+    with pytest.raises(CudaError):
+        m.forward(torch.zeros((3, 4), dtype=torch.int64, device=DEV))   # more sequences than allocated
