@@ -30,7 +30,10 @@ SYMBOLS = [
     "deers_b200_gpt_create", "deers_b200_gpt_destroy", "deers_b200_gpt_num_params", "deers_b200_gpt_param_info",
     "deers_b200_gpt_param_set", "deers_b200_gpt_param_get", "deers_b200_gpt_set_graph", "deers_b200_gpt_forward",
     "deers_b200_gpt_forward_backward", "deers_b200_gpt_train_step", "deers_b200_gpt_train_step_host",
+    "deers_b200_shard_range", "deers_b200_comm_init_all", "deers_b200_comm_export", "deers_b200_comm_init_ipc",
+    "deers_b200_comm_destroy", "deers_b200_allgather_o", "deers_b200_allgather_join", "deers_b200_allgather_flush",
 ]
+IPC_HANDLE_BYTES = 72
 K_FWD, K_BWD_PREP, K_BWD_MAIN, K_BWD_DQ, K_ROPE, K_OPTIM, K_NORM, K_DECODE, K_GEMM, K_GPT = range(10)
 EPI_NONE, EPI_ADD, EPI_RELU_SQ, EPI_MUL_AUX2 = range(4)
 
@@ -155,6 +158,16 @@ def lib() -> ctypes.CDLL:
     L.deers_b200_gpt_train_step.argtypes = [vp, vp, vp, ctypes.c_int32, ctypes.c_int32, hp, ctypes.c_double, vp, vp]
     L.deers_b200_gpt_train_step_host.argtypes = [vp, vp, vp, ctypes.c_int32, ctypes.c_int32, hp, ctypes.c_double,
                                                  ctypes.POINTER(ctypes.c_float), ctypes.POINTER(ctypes.c_float)]
+    L.deers_b200_shard_range.argtypes = [i64, ctypes.c_int32, ctypes.c_int32, ctypes.POINTER(i64), ctypes.POINTER(i64)]
+    L.deers_b200_shard_range.restype = None
+    L.deers_b200_comm_init_all.argtypes = [ctypes.c_int32, ctypes.POINTER(vp), ctypes.POINTER(vp), sz, ctypes.POINTER(vp)]
+    L.deers_b200_comm_export.argtypes = [vp, vp, ctypes.c_char_p]
+    L.deers_b200_comm_init_ipc.argtypes = [vp, ctypes.c_int32, ctypes.c_int32, vp, sz, ctypes.c_char_p, ctypes.POINTER(vp)]
+    L.deers_b200_comm_destroy.argtypes = [vp]
+    L.deers_b200_comm_destroy.restype = None
+    L.deers_b200_allgather_o.argtypes = [vp, sz, sz]
+    L.deers_b200_allgather_join.argtypes = [vp]
+    L.deers_b200_allgather_flush.argtypes = [vp]
     L.deers_b200_status_string.argtypes = [i32]
     L.deers_b200_status_string.restype = ctypes.c_char_p
     L.deers_b200_last_error.argtypes = [vp]

@@ -32,29 +32,6 @@
 #include "sm100_ptx.cuh"
 #include "tma_host.cuh"
 
-#ifdef DEERS_TRACE
-// Development aid: clock64() stamps of CTA 0's first iterations, read back by a debug entry point.
-__device__ unsigned long long g_bwd_trace[48 * 3 * 8];
-#define BWD_TRACE(role, ev)                                                                              \
-    do {                                                                                                 \
-        if (blockIdx.x == gridDim.x - 1 && it < 48) g_bwd_trace[(it * 3 + (role)) * 8 + (ev)] = clock64();           \
-    } while (0)
-extern "C" __attribute__((visibility("default"))) int deers_b200_debug_bwd_trace(unsigned long long* out) {
-    return (int)cudaMemcpyFromSymbol(out, g_bwd_trace, sizeof(g_bwd_trace));
-}
-#else
-#define BWD_TRACE(role, ev) do {} while (0)
-#endif
-#if defined(DEERS_TRACE) && DEERS_TRACE == 1
-#define TRACE_A(role, ev) BWD_TRACE(role, ev)
-#else
-#define TRACE_A(role, ev) do {} while (0)
-#endif
-#if defined(DEERS_TRACE) && DEERS_TRACE == 2
-#define TRACE_B(role, ev) BWD_TRACE(role, ev)
-#else
-#define TRACE_B(role, ev) do {} while (0)
-#endif
 
 namespace {
 using namespace sm100;
@@ -307,12 +284,10 @@ attn_bwd_dkdv_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
                     const bool more = it + 1 < niter;
                     // dV += P^T dO, then S^T of the next query tile: the pipe is in order, so the
                     // new S^T lands only after dV has consumed P^T from the same columns.
-                    TRACE_A(0, 0);
                     if (!mbar_wait(ws, &bars[A_P], par, DEERS_KERR_BWD_F16 | 8)) { ok = false; break; }
                     // The previous item's dK / dV must have left TMEM before this item accumulates.
                     if (it == 0 && !mbar_wait(ws, &bars[A_ACC_FREE], ((uint32_t)n & 1u) ^ 1u, DEERS_KERR_BWD_F16 | 9)) { ok = false; break; }
                     tc_fence_after_sync();
-                    TRACE_A(0, 1);
 #pragma unroll
                     for (int ks = 0; ks < BT / 16; ++ks)
                         umma_ts(tmem + TM_DV, a_tmem(TM_S, ks), do_mn + mnmajor_step(ks), IDESC_KV, (it > 0 || ks > 0));
@@ -322,10 +297,8 @@ attn_bwd_dkdv_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
                         issue_st((gi + 1u) % 3u);
                     }
                     // dK += dS^T Q, then dP^T of the next query tile over the consumed dS^T columns.
-                    TRACE_A(0, 2);
                     if (!mbar_wait(ws, &bars[A_DS], par, DEERS_KERR_BWD_F16 | 11)) { ok = false; break; }
                     tc_fence_after_sync();
-                    TRACE_A(0, 3);
 #pragma unroll
                     for (int ks = 0; ks < BT / 16; ++ks)
                         umma_ts(tmem + TM_DK, a_tmem(TM_DP, ks), q_mn + mnmajor_step(ks), IDESC_KV, (it > 0 || ks > 0));
@@ -339,7 +312,6 @@ attn_bwd_dkdv_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
                     // dO of this iteration was last read by dV (and dP^T before it): its stage is free once
                     // everything issued so far has finished.
                     umma_commit(&bars[A_DO_EMPTY + ds]);
-                    TRACE_A(0, 4);
                 }
                 umma_commit(&bars[A_DONE]);
             }
@@ -355,9 +327,6 @@ attn_bwd_dkdv_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         const float sl2 = p.scale * LOG2E;
         uint32_t gi = 0;
         bool alive = true;
-#if defined(DEERS_TRACE) && DEERS_TRACE == 1
-        const bool tr = lane == 0 && (warp == 2 || warp == 6);
-#endif
 
         for (int4 cur = next_item(p, 0, n_items, nq), nxt = next_item(p, 1, n_items, nq), n4 = make_int4(0, 0, 0, 0); alive && cur.x >= 0;
                  ++n4.x, cur = nxt, nxt = next_item(p, n4.x + 1, n_items, nq)) {
@@ -374,14 +343,8 @@ attn_bwd_dkdv_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
                 const float* lse2 = lse2_s + ss * BT + 64 * g;
                 const float* dlt = delta_s + ss * BT + 64 * g;
                 if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[A_ST_FULL + ss], (gi >> 1) & 1u, DEERS_KERR_BWD_F16 | 13))) { alive = false; break; }
-#if defined(DEERS_TRACE) && DEERS_TRACE == 1
-                if (tr) TRACE_A(1 + g, 0);
-#endif
                 if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[A_S], par, DEERS_KERR_BWD_F16 | 14))) { alive = false; break; }
                 tc_fence_after_sync();
-#if defined(DEERS_TRACE) && DEERS_TRACE == 1
-                if (tr) TRACE_A(1 + g, 1);
-#endif
                 const bool diag = p.causal && (i == kt);
                 uint32_t pk[32];                            // P^T row, 64 query columns as f16 pairs
 #pragma unroll
@@ -413,15 +376,9 @@ attn_bwd_dkdv_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
                 tmem_wait_st();
                 tc_fence_before_sync();
                 mbar_arrive(&bars[A_P]);
-#if defined(DEERS_TRACE) && DEERS_TRACE == 1
-                if (tr) TRACE_A(1 + g, 2);
-#endif
 
                 if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[A_DP], par, DEERS_KERR_BWD_F16 | 15))) { alive = false; break; }
                 tc_fence_after_sync();
-#if defined(DEERS_TRACE) && DEERS_TRACE == 1
-                if (tr) TRACE_A(1 + g, 3);
-#endif
                 uint32_t dd[32];                            // dS^T row, 64 query columns as f16 pairs
 #pragma unroll
                 for (int c = 0; c < 2; ++c) {
@@ -441,9 +398,6 @@ attn_bwd_dkdv_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
                 tmem_wait_st();
                 tc_fence_before_sync();
                 mbar_arrive(&bars[A_DS]);
-#if defined(DEERS_TRACE) && DEERS_TRACE == 1
-                if (tr) TRACE_A(1 + g, 4);
-#endif
                 if (p.ds) {
                     // The same dS^T row also goes to global memory, already swizzled, for the dQ kernel (off the
                     // critical path: the tensor core has what it needs).  The row's eight 16-byte chunks are
@@ -664,18 +618,13 @@ attn_bwd_dq_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
                 issue_s(kvc % 3u);
                 issue_dp(kvc & 1u);
                 for (int j = 0; j < ntiles; ++j, ++kvc) {
-#if defined(DEERS_TRACE) && DEERS_TRACE == 2
-                    const int it = (int)kvc;
-#endif
                     const uint32_t ks = kvc % 3u, ksn = (kvc + 1u) % 3u, vsn = (kvc + 1u) & 1u;
                     const uint32_t par = kvc & 1u;
                     const bool more = j + 1 < ntiles;
                     // S and dP of the next KV tile as soon as the compute threads have read this S:
                     // dP lands in the buffer whose dS the product issued one step ago has consumed
                     // (the pipe is in order), so the tensor core never waits for this step's dS.
-                    TRACE_B(0, 0);
                     if (!mbar_wait(ws, &bars[Q_PDONE], par, DEERS_KERR_BWD_F16 | 0x14)) { ok = false; break; }
-                    TRACE_B(0, 1);
                     if (more) {
                         if (!mbar_wait(ws, &bars[Q_K_FULL + ksn], ((kvc + 1u) / 3u) & 1u, DEERS_KERR_BWD_F16 | 0x15)) { ok = false; break; }
                         tc_fence_after_sync();
@@ -687,12 +636,10 @@ attn_bwd_dq_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
                         umma_commit(&bars[Q_QDO_EMPTY]);               // every product reading Q / dO has been issued
                     }
                     // dQ += dS K
-                    TRACE_B(0, 2);
                     if (!mbar_wait(ws, &bars[Q_DS + par], (kvc >> 1) & 1u, DEERS_KERR_BWD_F16 | 0x16)) { ok = false; break; }
                     // The previous item's dQ must have left TMEM before this item accumulates.
                     if (j == 0 && n > 0 && !mbar_wait(ws, &bars[Q_DQ_FREE], ((uint32_t)n - 1u) & 1u, DEERS_KERR_BWD_F16 | 0x1a)) { ok = false; break; }
                     tc_fence_after_sync();
-                    TRACE_B(0, 3);
                     const uint64_t k_mn = k_mn0 + (uint64_t)ks * STAGE_STEP;
                     const uint32_t tm_ds = tmem + TM_DP + par * 128u;
 #pragma unroll
@@ -700,7 +647,6 @@ attn_bwd_dq_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
                         umma_ts(tm_dq, tm_ds + (uint32_t)(ks >> 2) * 64u + (uint32_t)(ks & 3) * 8u,
                                 k_mn + mnmajor_step(ks), IDESC_DQ, (j > 0 || ks > 0));
                     umma_commit(&bars[Q_K_EMPTY + ks]);                // S and dQ have both read this K tile
-                    TRACE_B(0, 4);
                 }
                 umma_commit(&bars[Q_DONE]);
             }
@@ -716,9 +662,6 @@ attn_bwd_dq_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         const float sl2 = p.scale * LOG2E;
         uint32_t gi = 0;                                        // KV iterations so far (all items)
         bool alive = true;
-#if defined(DEERS_TRACE) && DEERS_TRACE == 2
-        const bool tr = lane == 0 && (warp == 2 || warp == 6);
-#endif
         // The epilogue of item n (scale, convert, store its dQ tile, release the accumulator) is
         // deferred until the first dS of item n+1 has been handed over: the tensor core then still
         // has S and dP of the second KV tile to compute before it needs the accumulator.
@@ -765,16 +708,9 @@ attn_bwd_dq_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
             const float delta_r = p.delta[(long long)bh * p.Tpad + q0 + r];
 
             for (int j = 0; j < ntiles; ++j, ++gi) {
-#if defined(DEERS_TRACE) && DEERS_TRACE == 2
-                const int it = (int)gi;
-                if (tr) TRACE_B(1 + g, 0);
-#endif
                 const uint32_t par = gi & 1u;
                 if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[Q_S], par, DEERS_KERR_BWD_F16 | 0x17))) { alive = false; break; }
                 tc_fence_after_sync();
-#if defined(DEERS_TRACE) && DEERS_TRACE == 2
-                if (tr) TRACE_B(1 + g, 1);
-#endif
                 const int k0 = j * BT;
                 const bool edge = (p.causal && j == qt) || (k0 + BT > p.T);
                 float pv[64];                               // P row, this warpgroup's 64 key columns
@@ -797,15 +733,9 @@ attn_bwd_dq_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
                         for (int e = 0; e < 64; ++e) pv[e] = ex2(fmaf(__uint_as_float(sr[e]), sl2, -lse2_r));
                     }
                 }
-#if defined(DEERS_TRACE) && DEERS_TRACE == 2
-                if (tr) TRACE_B(1 + g, 2);
-#endif
 
                 if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[Q_DP + par], (gi >> 1) & 1u, DEERS_KERR_BWD_F16 | 0x18))) { alive = false; break; }
                 tc_fence_after_sync();
-#if defined(DEERS_TRACE) && DEERS_TRACE == 2
-                if (tr) TRACE_B(1 + g, 3);
-#endif
                 uint32_t dd[32];
 #pragma unroll
                 for (int c = 0; c < 2; ++c) {
@@ -822,9 +752,6 @@ attn_bwd_dq_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
                 tmem_wait_st();
                 tc_fence_before_sync();
                 mbar_arrive(&bars[Q_DS + par]);
-#if defined(DEERS_TRACE) && DEERS_TRACE == 2
-                if (tr) TRACE_B(1 + g, 4);
-#endif
                 if (j == 0 && !epilogue()) { alive = false; break; }       // previous item's dQ tile
             }
             if (!alive) break;
@@ -1160,25 +1087,20 @@ constexpr size_t kStaticScratchFloats = 2u * 1024u * 1024u;            // 8 MiB:
 static __device__ __align__(256) float g_bwd_static_scratch[kStaticScratchFloats];
 
 // In host code the array's name is only a handle; kernels need its device address, which differs
-// per device and is looked up once per device with that device current.
+// per device and is looked up once per device with that device current.  Two host threads that make
+// the first call on one device at the same time both store the same address: harmless.
 static void* g_static_scratch_addr[64] = {nullptr};
 
 extern "C" __attribute__((visibility("default")))
 int deers_b200_attn_bwd_f16_static(deers_ctx* ctx, const deers_attn_desc* d, const void* q, const void* k,
                                    const void* v, const void* o, const float* lse, const void* d_o, void* dq,
                                    void* dk, void* dv) {
-    if (!ctx || !d || !q || !k || !v || !o || !lse || !d_o || !dq || !dk || !dv) return DEERS_ERR_NULL;
+    if (!ctx) return DEERS_ERR_NULL;
+    // the same checks, in the same order, as deers_b200_attn_bwd: both accept and refuse the same descriptors
+    const int rc = deers_check_bwd_args(d, q, k, v, o, lse, d_o, dq, dk, dv);
+    if (rc) return rc;
     if (d->dtype != DEERS_F16) return DEERS_ERR_DTYPE;
-    if (d->B < 1 || d->H < 1 || d->T < 1 || (d->D != 64 && d->D != 128)) return DEERS_ERR_SHAPE;
     if (ctx->device < 0 || ctx->device >= 64) return DEERS_ERR_DEVICE;
-    const int64_t* strides[8] = {d->q_strides, d->k_strides, d->v_strides, d->o_strides,
-                                 d->do_strides, d->dq_strides, d->dk_strides, d->dv_strides};
-    const void* ptrs[8] = {q, k, v, o, d_o, dq, dk, dv};
-    for (int i = 0; i < 8; ++i) {
-        if (strides[i][3] != 1 || ((uintptr_t)ptrs[i] & 15u) != 0) return DEERS_ERR_LAYOUT;
-        for (int a = 0; a < 3; ++a)
-            if (strides[i][a] < 0 || ((strides[i][a] * 2) & 15) != 0) return DEERS_ERR_LAYOUT;
-    }
     const size_t need = attn_bwd_f16_workspace_bytes(d, false);
     if (need > sizeof(float) * kStaticScratchFloats) {
         snprintf(ctx->last_error, sizeof(ctx->last_error),

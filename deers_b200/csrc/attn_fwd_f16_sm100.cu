@@ -24,30 +24,7 @@
 #include "sm100_ptx.cuh"
 #include "tma_host.cuh"
 
-#if defined(DEERS_TRACE) && DEERS_TRACE == 3
-// Development aid: clock64() stamps of the last CTA's first steps, read back by a debug entry point.
-__device__ unsigned long long g_fwd_trace[16 * 3 * 8];
-#define FWD_TRACE(role, step, ev)                                                                        \
-    do {                                                                                                 \
-        if (blockIdx.x == gridDim.x - 1 && (step) < 16) g_fwd_trace[((step) * 3 + (role)) * 8 + (ev)] = clock64(); \
-    } while (0)
-extern "C" __attribute__((visibility("default"))) int deers_b200_debug_fwd_trace(unsigned long long* out) {
-    return (int)cudaMemcpyFromSymbol(out, g_fwd_trace, sizeof(g_fwd_trace));
-}
-#else
-#define FWD_TRACE(role, step, ev) do {} while (0)
-#endif
 
-#if defined(DEERS_TRACE) && DEERS_TRACE == 4
-// Development aid: last known position of every role of every CTA, to locate a stalled wait.
-__device__ int g_fwd_state[160 * 16 * 4];
-#define FWD_STATE(slot, a, b, c) do { int* s_ = g_fwd_state + ((int)blockIdx.x * 16 + (slot)) * 4; s_[0] = (a); s_[1] = (b); s_[2] = (c); s_[3] = 1; } while (0)
-extern "C" __attribute__((visibility("default"))) int deers_b200_debug_fwd_state(int* out) {
-    return (int)cudaMemcpyFromSymbol(out, g_fwd_state, sizeof(g_fwd_state));
-}
-#else
-#define FWD_STATE(slot, a, b, c) do {} while (0)
-#endif
 
 namespace {
 using namespace sm100;
@@ -60,10 +37,7 @@ constexpr float LN2 = 0.6931471805599453f;
 constexpr float RESCALE_THRESHOLD = 8.0f;     // log2 units: P stays below 2^8, safe in f16
 // Softmax warpgroups per CTA.  Four (32 key columns each) rather than two: the softmax threads are bound by
 // instruction latency, not by any one pipe, and four resident warps per scheduler hide it better than two.
-#ifndef DEERS_FWD_NWG
-#define DEERS_FWD_NWG 4
-#endif
-constexpr int NWG = DEERS_FWD_NWG;
+constexpr int NWG = 4;
 constexpr int CW = 128 / NWG;                 // key columns of a step per warpgroup
 constexpr int FWD_THREADS = 32 * (2 + 4 * NWG + 1);
 constexpr int S_WARP = 2 + 4 * NWG;           // the warp that issues S
@@ -224,7 +198,6 @@ attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 const int b = c.b, h = c.h;
                 if (c.j == 0) {
                     const int qb = c.n & 1;
-                    FWD_STATE(0, (int)g, c.n, c.j * 10 + 1);
                     if (!mbar_wait(ws, &bars[F_Q_EMPTY + qb], (((uint32_t)c.n >> 1) & 1u) ^ 1u, DEERS_KERR_FWD_F16 | 1)) break;
                     mbar_arrive_expect_tx(&bars[F_Q_FULL + qb], TILE_BYTES);
 #pragma unroll
@@ -232,13 +205,11 @@ attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                         tma_load_4d(sQ + qb * TILE_BYTES + blk * BLOCK_BYTES, &tmap_q, &bars[F_Q_FULL + qb], blk * 64, c.qt * BM, h, b);
                 }
                 const uint32_t st = g & 1u, ph = ((g >> 1) & 1u) ^ 1u;
-                FWD_STATE(0, (int)g, c.n, c.j * 10 + 2);
                 if (!mbar_wait(ws, &bars[F_S_FULL + st], ph, DEERS_KERR_FWD_F16 | 2)) break;      // S of step g-2 done
                 mbar_arrive_expect_tx(&bars[F_K_FULL + st], TILE_BYTES);
 #pragma unroll
                 for (int blk = 0; blk < DBLK; ++blk)
                     tma_load_4d(sK + st * TILE_BYTES + blk * BLOCK_BYTES, &tmap_k, &bars[F_K_FULL + st], blk * 64, c.j * BN, h, b);
-                FWD_STATE(0, (int)g, c.n, c.j * 10 + 3);
                 if (!mbar_wait(ws, &bars[F_PV_DONE + st], ph, DEERS_KERR_FWD_F16 | 3)) break;     // P V of step g-2 done
                 mbar_arrive_expect_tx(&bars[F_V_FULL + st], TILE_BYTES);
 #pragma unroll
@@ -257,9 +228,7 @@ attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             pc.init(p, nq, n_items);
             for (uint32_t gp = 0; pc.valid(n_items); ++gp) {
                 const uint32_t st = gp & 1u;
-                FWD_TRACE(0, gp, 0);
                 if (!mbar_wait(ws, &bars[F_P_FULL + st], (gp >> 1) & 1u, DEERS_KERR_FWD_F16 | 6)) break;
-                FWD_TRACE(0, gp, 1);
                 if (!mbar_wait(ws, &bars[F_V_FULL + st], (gp >> 1) & 1u, DEERS_KERR_FWD_F16 | 7)) break;
                 // The accumulator of item n was last used by item n-2: its epilogue must be over.
                 if (pc.j == 0 && !mbar_wait(ws, &bars[F_O_FREE + (pc.n & 1)], (((uint32_t)pc.n >> 1) & 1u) ^ 1u, DEERS_KERR_FWD_F16 | 8)) break;
@@ -272,10 +241,8 @@ attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                     umma_ts(o_tmem, p_tmem + (uint32_t)(ks / (CW / 16)) * CW + (uint32_t)(ks % (CW / 16)) * 8u, v_mn + mnmajor_step(ks),
                             IDESC_O, (pc.j > 0 || ks > 0));
                 umma_commit(&bars[F_PV_DONE + st]);
-                FWD_TRACE(0, gp, 2);
                 if (pc.j == pc.ntiles - 1) umma_commit(&bars[F_O_DONE + (pc.n & 1)]);
                 pc.advance(p, nq, n_items);
-                FWD_TRACE(0, gp, 3);
             }
         }
     } else if (warp == S_WARP) {
@@ -290,20 +257,17 @@ attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             for (uint32_t gs = 0; sc.valid(n_items); ++gs) {
                 const uint32_t st = gs & 1u;
                 const int qb = sc.n & 1;
-                FWD_TRACE(0, gs, 4);
                 if (sc.j == 0 && !mbar_wait(ws, &bars[F_Q_FULL + qb], ((uint32_t)sc.n >> 1) & 1u, DEERS_KERR_FWD_F16 | 4)) break;
                 if (!mbar_wait(ws, &bars[F_K_FULL + st], (gs >> 1) & 1u, DEERS_KERR_FWD_F16 | 5)) break;
                 // This S tile still holds P of step gs-2 until the product reading it has finished.
                 if (!mbar_wait(ws, &bars[F_PV_DONE + st], ((gs >> 1) & 1u) ^ 1u, DEERS_KERR_FWD_F16 | 0x15)) break;
                 tc_fence_after_sync();
-                FWD_TRACE(0, gs, 5);
                 const uint64_t q_km = q_km0 + (uint64_t)qb * STAGE_STEP, k_km = k_km0 + (uint64_t)st * STAGE_STEP;
                 const uint32_t d_tmem = tmem + TM_S + st * 128u;
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks)
                     umma_ss(d_tmem, q_km + kmajor_step(ks, BLOCK_BYTES), k_km + kmajor_step(ks, BLOCK_BYTES), IDESC_S, ks > 0);
                 umma_commit(&bars[F_S_FULL + st]);
-                FWD_TRACE(0, gs, 6);
                 if (sc.j == sc.ntiles - 1) umma_commit(&bars[F_Q_EMPTY + qb]);     // last product reading this Q
                 sc.advance(p, nq, n_items);
             }
@@ -332,7 +296,6 @@ attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             float l = 0.f;
 #pragma unroll
             for (int w = 0; w < NWG; ++w) l += lxp[w * BM + row];        // same order in every warpgroup
-            if (lane == 0) FWD_STATE(warp, -1, n, 10);
             if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[F_O_DONE + (n & 1)], ((uint32_t)n >> 1) & 1u, DEERS_KERR_FWD_F16 | 10))) return false;
             tc_fence_after_sync();
             const float inv = 1.f / l;
@@ -358,13 +321,6 @@ attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
 #pragma unroll
                 for (int q8 = 0; q8 < NP; ++q8) oc[q8] = pack8_f16(r + q8 * 8, inv);
             }
-#ifdef DEERS_FWD_DIRECT_STORE
-            if (pend_grow < p.T) {
-                __half* orow = p.o + b * p.so_b + h * p.so_h + (long long)pend_grow * p.so_t + g * DH;
-#pragma unroll
-                for (int c = 0; c < NP; ++c) *reinterpret_cast<uint4*>(orow + c * 8) = oc[c];
-            }
-#else
             transpose_pieces<NP>(oc, (uint32_t)lane);
             const int grow0 = pend_grow - lane + (lane & ~(NP - 1));
             __half* ob = p.o + b * p.so_b + h * p.so_h + g * DH + (lane & (NP - 1)) * 8;
@@ -373,7 +329,6 @@ attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 const int grow = grow0 + c;
                 if (grow < p.T) *reinterpret_cast<uint4*>(ob + (long long)grow * p.so_t) = oc[c];
             }
-#endif
             if (g == 0 && pend_grow < p.T) p.lse[(long long)pend_bh * p.T + pend_grow] = (pend_m + log2f(l)) * LN2;
             return true;
         };
@@ -386,9 +341,6 @@ attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             float m_used = -INFINITY, l = 0.f;                  // l: partial sum over this warpgroup's columns
             for (int j = 0; j < ntiles; ++j, ++gstep) {
                 const uint32_t sb = gstep & 1u;
-                const bool tr = lane == 0 && (warp == 2 || warp == 6);
-                if (tr) FWD_TRACE(1 + g, gstep, 0);
-                if (lane == 0) FWD_STATE(warp, (int)gstep, n, j * 100 + 11);
                 if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[F_S_FULL + sb], (gstep >> 1) & 1u, DEERS_KERR_FWD_F16 | 11))) { alive = false; break; }
                 tc_fence_after_sync();
                 float s[CW];
@@ -396,7 +348,6 @@ attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
 #pragma unroll
                 for (int cc = 0; cc < CW / 32; ++cc) tmem_ld_x32(ts + cc * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[cc * 32]));
                 tmem_wait_ld();
-                if (tr) FWD_TRACE(1 + g, gstep, 1);
                 // Steps that touch the diagonal or the end of the sequence are scaled here and
                 // masked with -inf; all others keep raw scores and fold the scale into the
                 // exponent's FFMA.
@@ -422,14 +373,12 @@ attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 }
                 mx *= c1;
                 // Exchange the partial row max with the twin threads of the other warpgroups.
-                if (tr) FWD_TRACE(1 + g, gstep, 2);
                 float* xp = xch + sb * NWG * BM;
                 xp[g * BM + row] = mx;
                 mbar_arrive(&bars[F_XCH]);
                 if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[F_XCH], gstep & 1u, DEERS_KERR_FWD_F16 | 12))) { alive = false; break; }
 #pragma unroll
                 for (int w = 0; w < NWG; ++w) mx = fmaxf(mx, xp[w * BM + row]);
-                if (tr) FWD_TRACE(1 + g, gstep, 3);
 
                 const float m_new = fmaxf(m_used, mx);
                 // Lazy rescale: keep the old reference max unless this row grew by more than 2^8.
@@ -450,7 +399,6 @@ attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 }
                 l = l * alpha + rs;
                 m_used = m_cur;
-                if (tr) FWD_TRACE(1 + g, gstep, 4);
 
                 if (j > 0 && warp_grow) {
                     // O += P V of the previous step must have landed before O is rescaled.
@@ -482,7 +430,6 @@ attn_fwd_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 tmem_wait_st();
                 tc_fence_before_sync();
                 mbar_arrive(&bars[F_P_FULL + sb]);
-                if (tr) FWD_TRACE(1 + g, gstep, 5);
                 if (j == 0 && !epilogue()) { alive = false; break; }          // previous item's O tile
             }
             if (!alive) break;

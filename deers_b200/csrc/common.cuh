@@ -19,6 +19,17 @@ struct deers_ktimer {
     uint64_t launches;
 };
 
+constexpr int DEERS_SCHED_CAP = 1 << 20;                 // ints per schedule table
+constexpr int DEERS_SCHED_ENTRIES = 4;
+struct deers_sched_entry {
+    int key[5];             // key[0] < 0: empty
+    int rows;
+    int* dev;               // DEERS_SCHED_CAP ints of device memory
+    int* host;              // pinned staging of the same size
+    cudaEvent_t uploaded;   // recorded after the upload: the staging copy may be rewritten once it has fired
+    uint64_t last_use;
+};
+
 struct deers_ctx {
     int device;
     cudaStream_t stream;
@@ -35,11 +46,13 @@ struct deers_ctx {
     void* encode_tiled;
     bool timing;
     deers_ktimer kt[DEERS_K_COUNT];
-    // Balanced work schedule of the persistent f16 kernels: table[n * grid + cta] = n-th work item
-    // of that CTA (or -1), built on the host for the last (B, H, T, causal, grid) seen.
-    int* sched_dev;
-    int sched_key[5];
-    int sched_rows;
+    // Balanced work schedules of the persistent f16 kernels: table[n * grid + cta] = n-th work item
+    // of that CTA (or -1), built on the host per (B, H, tiles, causal, grid).  A few shapes stay cached
+    // (least recently used goes first), each with its own device table and pinned staging copy, so that a
+    // caller alternating shapes (training / evaluation, the ragged last chunk of the host pipeline) neither
+    // rebuilds nor waits: the upload is an asynchronous copy on the context's stream.
+    deers_sched_entry sched[DEERS_SCHED_ENTRIES];
+    uint64_t sched_clock;
     // Side streams and events of the host-tensor pipeline (created on first use).
     cudaStream_t h2d_stream, d2h_stream;
     cudaEvent_t pipe_ev[3][3];      // [buffer set][h2d done, compute done, d2h done]
@@ -88,8 +101,13 @@ enum {
 // ntile - slot when causal).  The table hands the items, in that order, to whichever CTA is least
 // loaded so far, which balances the causal triangle for any slice count.  Returns nullptr (plain
 // strided assignment) when the table would not fit.
-constexpr int DEERS_SCHED_CAP = 1 << 20;                 // table entries
 const int4* deers_get_schedule(deers_ctx* ctx, int B, int H, int ntile, int causal, int grid, int* rows);
+
+// Argument validation shared by every attention entry point (ctx.cu)
+int deers_check_desc(const deers_attn_desc* d);
+int deers_check_tensor(const deers_attn_desc* d, const void* p, const int64_t* s, size_t esize);
+int deers_check_bwd_args(const deers_attn_desc* d, const void* q, const void* k, const void* v, const void* o,
+                         const float* lse, const void* d_o, void* dq, void* dk, void* dv);
 
 // f32 FFMA path (attn_f32.cu)
 int launch_attn_fwd_f32(deers_ctx* ctx, const deers_attn_desc* d, const float* q, const float* k,

@@ -79,8 +79,18 @@ extern "C" int deers_b200_init(int device_ordinal, void* stream, deers_ctx** out
         return DEERS_ERR_CUDA;
     }
     *ctx->host_err = 0;
-    if (cudaMalloc((void**)&ctx->sched_dev, sizeof(int) * DEERS_SCHED_CAP) != cudaSuccess) ctx->sched_dev = nullptr;
-    ctx->sched_key[0] = -1;
+    for (int e = 0; e < DEERS_SCHED_ENTRIES; ++e) {
+        deers_sched_entry* se = &ctx->sched[e];
+        se->key[0] = -1;
+        if (cudaMalloc((void**)&se->dev, sizeof(int) * DEERS_SCHED_CAP) != cudaSuccess ||
+            cudaHostAlloc((void**)&se->host, sizeof(int) * DEERS_SCHED_CAP, cudaHostAllocDefault) != cudaSuccess ||
+            cudaEventCreateWithFlags(&se->uploaded, cudaEventDisableTiming) != cudaSuccess) {
+            cudaGetLastError();
+            if (se->dev) cudaFree(se->dev);
+            if (se->host) cudaFreeHost(se->host);
+            se->dev = nullptr; se->host = nullptr; se->uploaded = nullptr;   // this slot stays unused
+        }
+    }
     cudaDriverEntryPointQueryResult qres;
     void* fn = nullptr;
     if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess ||
@@ -98,7 +108,11 @@ extern "C" void deers_b200_destroy(deers_ctx* ctx) {
     if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
     if (ctx->host_err) cudaFreeHost(ctx->host_err);
     if (ctx->dev_err) cudaFree(ctx->dev_err);
-    if (ctx->sched_dev) cudaFree(ctx->sched_dev);
+    for (int e = 0; e < DEERS_SCHED_ENTRIES; ++e) {
+        if (ctx->sched[e].dev) cudaFree(ctx->sched[e].dev);
+        if (ctx->sched[e].host) cudaFreeHost(ctx->sched[e].host);
+        if (ctx->sched[e].uploaded) cudaEventDestroy(ctx->sched[e].uploaded);
+    }
     if (ctx->pipe_ready) {
         cudaStreamDestroy(ctx->h2d_stream);
         cudaStreamDestroy(ctx->d2h_stream);
@@ -191,14 +205,27 @@ extern "C" int deers_b200_sync(deers_ctx* ctx) {
 const int4* deers_get_schedule(deers_ctx* ctx, int B, int H, int ntile, int causal, int grid, int* rows) {
     *rows = 0;
     const long long n_items = (long long)B * H * ntile;
-    if (!ctx->sched_dev || grid < 1 || n_items < 1) return nullptr;
+    if (grid < 1 || n_items < 1) return nullptr;
     const int key[5] = {B, H, ntile, causal, grid};
-    if (memcmp(key, ctx->sched_key, sizeof(key)) == 0) {
-        *rows = ctx->sched_rows;
-        return ctx->sched_rows > 0 ? reinterpret_cast<const int4*>(ctx->sched_dev) : nullptr;
+    deers_sched_entry* victim = nullptr;
+    for (int e = 0; e < DEERS_SCHED_ENTRIES; ++e) {
+        deers_sched_entry* se = &ctx->sched[e];
+        if (!se->dev) continue;
+        if (se->key[0] >= 0 && memcmp(key, se->key, sizeof(key)) == 0) {
+            se->last_use = ++ctx->sched_clock;
+            *rows = se->rows;
+            return se->rows > 0 ? reinterpret_cast<const int4*>(se->dev) : nullptr;
+        }
+        if (!victim || se->key[0] < 0 || (victim->key[0] >= 0 && se->last_use < victim->last_use)) victim = se;
     }
-    memcpy(ctx->sched_key, key, sizeof(key));
-    ctx->sched_rows = 0;
+    if (!victim) return nullptr;
+    // A miss while the stream is being captured takes the plain strided assignment: the upload would become a
+    // graph node that re-reads the staging copy at every replay.
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(ctx->stream, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
+        cudaGetLastError();
+        return nullptr;
+    }
     // Greedy list scheduling in item order: each item goes to the CTA with the least work so far.
     std::vector<std::vector<int>> lists(grid);
     typedef std::pair<long long, int> Load;                            // (work so far, cta)
@@ -217,10 +244,16 @@ const int4* deers_get_schedule(deers_ctx* ctx, int B, int H, int ntile, int caus
     }
     size_t nrows = 0;
     for (auto& v : lists) nrows = v.size() > nrows ? v.size() : nrows;
-    if (nrows * (size_t)grid * 4 > (size_t)DEERS_SCHED_CAP) return nullptr;
+    memcpy(victim->key, key, sizeof(key));
+    victim->last_use = ++ctx->sched_clock;
+    victim->rows = 0;
+    if (nrows * (size_t)grid * 4 > (size_t)DEERS_SCHED_CAP) return nullptr;   // cached as "no table": strided assignment
+    // The staging copy of this slot may still be the source of an earlier upload: wait for that one copy.
+    if (cudaEventSynchronize(victim->uploaded) != cudaSuccess) { cudaGetLastError(); victim->key[0] = -1; return nullptr; }
     // Entry = {slot, slice, batch, head}: the kernels' single issuing threads would otherwise spend about a
     // thousand cycles per item on the integer divisions that turn an item index into these.
-    std::vector<int4> table(nrows * grid, make_int4(-1, 0, 0, 0));
+    int4* table = reinterpret_cast<int4*>(victim->host);
+    for (size_t i = 0; i < nrows * grid; ++i) table[i] = make_int4(-1, 0, 0, 0);
     for (int c = 0; c < grid; ++c)
         for (size_t n = 0; n < lists[c].size(); ++n) {
             const long long w = lists[c][n];
@@ -230,21 +263,22 @@ const int4* deers_get_schedule(deers_ctx* ctx, int B, int H, int ntile, int caus
             const int bh = group * 16 + within % gsize;
             table[n * grid + c] = make_int4(within / gsize, bh, bh / H, bh % H);
         }
-    if (cudaMemcpyAsync(ctx->sched_dev, table.data(), table.size() * sizeof(int4), cudaMemcpyHostToDevice, ctx->stream) !=
+    if (cudaMemcpyAsync(victim->dev, victim->host, nrows * grid * sizeof(int4), cudaMemcpyHostToDevice, ctx->stream) !=
             cudaSuccess ||
-        cudaStreamSynchronize(ctx->stream) != cudaSuccess) {           // the host vector goes away on return
-        ctx->sched_key[0] = -1;
+        cudaEventRecord(victim->uploaded, ctx->stream) != cudaSuccess) {
+        cudaGetLastError();
+        victim->key[0] = -1;
         return nullptr;
     }
-    ctx->sched_rows = (int)nrows;
-    *rows = ctx->sched_rows;
-    return reinterpret_cast<const int4*>(ctx->sched_dev);
+    victim->rows = (int)nrows;
+    *rows = victim->rows;
+    return reinterpret_cast<const int4*>(victim->dev);
 }
 
 // ---------------------------------------------------------------------------
 // Validation shared by forward and backward
 // ---------------------------------------------------------------------------
-static int check_tensor(const deers_attn_desc* d, const void* p, const int64_t* s, size_t esize) {
+int deers_check_tensor(const deers_attn_desc* d, const void* p, const int64_t* s, size_t esize) {
     if (!p) return DEERS_ERR_NULL;
     if (s[3] != 1) return DEERS_ERR_LAYOUT;
     // f16 (TMA) needs 16-byte aligned bases and row starts; the f32 kernels fall
@@ -259,7 +293,7 @@ static int check_tensor(const deers_attn_desc* d, const void* p, const int64_t* 
     return DEERS_OK;
 }
 
-static int check_desc(const deers_attn_desc* d) {
+int deers_check_desc(const deers_attn_desc* d) {
     if (!d) return DEERS_ERR_NULL;
     if (d->dtype != DEERS_F16 && d->dtype != DEERS_F32) return DEERS_ERR_DTYPE;
     if (d->B < 1 || d->H < 1 || d->T < 1 || d->D < 1) return DEERS_ERR_SHAPE;
@@ -274,6 +308,24 @@ static int check_desc(const deers_attn_desc* d) {
     return DEERS_OK;
 }
 
+// Everything deers_b200_attn_bwd and deers_b200_attn_bwd_f16_static check before looking at scratch memory.
+int deers_check_bwd_args(const deers_attn_desc* d, const void* q, const void* k, const void* v, const void* o,
+                         const float* lse, const void* d_o, void* dq, void* dk, void* dv) {
+    int rc = deers_check_desc(d);
+    if (rc) return rc;
+    if (!lse) return DEERS_ERR_NULL;
+    const size_t es = d->dtype == DEERS_F16 ? 2 : 4;
+    if ((rc = deers_check_tensor(d, q, d->q_strides, es))) return rc;
+    if ((rc = deers_check_tensor(d, k, d->k_strides, es))) return rc;
+    if ((rc = deers_check_tensor(d, v, d->v_strides, es))) return rc;
+    if ((rc = deers_check_tensor(d, o, d->o_strides, es))) return rc;
+    if ((rc = deers_check_tensor(d, d_o, d->do_strides, es))) return rc;
+    if ((rc = deers_check_tensor(d, dq, d->dq_strides, es))) return rc;
+    if ((rc = deers_check_tensor(d, dk, d->dk_strides, es))) return rc;
+    if ((rc = deers_check_tensor(d, dv, d->dv_strides, es))) return rc;
+    return DEERS_OK;
+}
+
 static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 static size_t delta_bytes(const deers_attn_desc* d) {
@@ -281,7 +333,7 @@ static size_t delta_bytes(const deers_attn_desc* d) {
 }
 
 extern "C" size_t deers_b200_attn_workspace_bytes(const deers_attn_desc* d, int pass) {
-    if (check_desc(d) != DEERS_OK || pass == 0) return 0;
+    if (deers_check_desc(d) != DEERS_OK || pass == 0) return 0;
     // pass 1: the least the backward needs; pass 2: what lets the f16 backward keep its dS tiles
     return d->dtype == DEERS_F16 ? attn_bwd_f16_workspace_bytes(d, pass >= 2) : delta_bytes(d);
 }
@@ -291,14 +343,14 @@ extern "C" int deers_b200_attn_fwd(deers_ctx* ctx, const deers_attn_desc* d, con
                                    size_t workspace_bytes) {
     (void)workspace; (void)workspace_bytes;
     if (!ctx) return DEERS_ERR_NULL;
-    int rc = check_desc(d);
+    int rc = deers_check_desc(d);
     if (rc) return rc;
     if (!lse) return DEERS_ERR_NULL;
     const size_t es = d->dtype == DEERS_F16 ? 2 : 4;
-    if ((rc = check_tensor(d, q, d->q_strides, es))) return rc;
-    if ((rc = check_tensor(d, k, d->k_strides, es))) return rc;
-    if ((rc = check_tensor(d, v, d->v_strides, es))) return rc;
-    if ((rc = check_tensor(d, o, d->o_strides, es))) return rc;
+    if ((rc = deers_check_tensor(d, q, d->q_strides, es))) return rc;
+    if ((rc = deers_check_tensor(d, k, d->k_strides, es))) return rc;
+    if ((rc = deers_check_tensor(d, v, d->v_strides, es))) return rc;
+    if ((rc = deers_check_tensor(d, o, d->o_strides, es))) return rc;
     DEERS_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
     if (d->dtype == DEERS_F32)
         return launch_attn_fwd_f32(ctx, d, (const float*)q, (const float*)k, (const float*)v, (float*)o, lse);
@@ -310,18 +362,8 @@ extern "C" int deers_b200_attn_bwd(deers_ctx* ctx, const deers_attn_desc* d, con
                                    const void* d_o, void* dq, void* dk, void* dv, void* workspace,
                                    size_t workspace_bytes) {
     if (!ctx) return DEERS_ERR_NULL;
-    int rc = check_desc(d);
+    int rc = deers_check_bwd_args(d, q, k, v, o, lse, d_o, dq, dk, dv);
     if (rc) return rc;
-    if (!lse) return DEERS_ERR_NULL;
-    const size_t es = d->dtype == DEERS_F16 ? 2 : 4;
-    if ((rc = check_tensor(d, q, d->q_strides, es))) return rc;
-    if ((rc = check_tensor(d, k, d->k_strides, es))) return rc;
-    if ((rc = check_tensor(d, v, d->v_strides, es))) return rc;
-    if ((rc = check_tensor(d, o, d->o_strides, es))) return rc;
-    if ((rc = check_tensor(d, d_o, d->do_strides, es))) return rc;
-    if ((rc = check_tensor(d, dq, d->dq_strides, es))) return rc;
-    if ((rc = check_tensor(d, dk, d->dk_strides, es))) return rc;
-    if ((rc = check_tensor(d, dv, d->dv_strides, es))) return rc;
     const size_t need = deers_b200_attn_workspace_bytes(d, 1);
     if (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 255u) != 0)
         return DEERS_ERR_WORKSPACE;
@@ -407,7 +449,7 @@ ChunkLayout chunk_layout(const deers_attn_desc* d, int chunk) {
 }  // namespace
 
 extern "C" size_t deers_b200_attn_host_scratch_bytes(const deers_attn_desc* d, int chunk_slices) {
-    if (check_desc(d) != DEERS_OK || chunk_slices < 1) return 0;
+    if (deers_check_desc(d) != DEERS_OK || chunk_slices < 1) return 0;
     return kPipeSets * chunk_layout(d, chunk_slices).set_bytes;
 }
 
@@ -416,7 +458,7 @@ extern "C" int deers_b200_attn_fwd_bwd_host(deers_ctx* ctx, const deers_attn_des
                                             float* lse_host, void* dq_host, void* dk_host, void* dv_host,
                                             int chunk_slices, void* device_scratch, size_t scratch_bytes) {
     if (!ctx || !q_host || !k_host || !v_host || !do_host || !o_host || !dq_host || !dk_host || !dv_host) return DEERS_ERR_NULL;
-    int rc = check_desc(d);
+    int rc = deers_check_desc(d);
     if (rc) return rc;
     if (chunk_slices < 1) return DEERS_ERR_SHAPE;
     const size_t need = deers_b200_attn_host_scratch_bytes(d, chunk_slices);

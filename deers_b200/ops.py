@@ -45,11 +45,13 @@ class Context:
         if device.type != "cuda":
             raise DeviceMismatch("the fused attention op only exists on the CUDA device (no CPU fallback)")
         idx = device.index if device.index is not None else torch.cuda.current_device()
-        stream = torch.cuda.current_stream(idx).cuda_stream
+        stream_obj = torch.cuda.current_stream(idx)
+        stream = stream_obj.cuda_stream
         key = (idx, stream)
         ctx = cls._cache.get(key)
         if ctx is None:
             ctx = cls(idx, stream)
+            ctx._stream_obj = stream_obj     # keeps the stream alive: its handle value cannot be reused by another
             cls._cache[key] = ctx
         return ctx
 
@@ -97,7 +99,7 @@ def _check_inputs(name: str, tensors) -> None:
 
 def _usable(t: torch.Tensor) -> bool:
     """True if the kernels can read `t` in place: inner stride 1 and aligned rows."""
-    if t.stride(3) != 1 and t.shape[3] > 1:
+    if t.stride(3) != 1:                 # the C ABI wants inner stride 1 even for a head_dim of 1
         return False
     esize = t.element_size()
     align = 16 if t.dtype == torch.float16 else 4
@@ -296,20 +298,22 @@ class GradientStore:
     """Insert-or-add gradient map keyed by tensor identity (src/backprop.rs:74-128)."""
 
     def __init__(self):
-        self._grads: Dict[int, torch.Tensor] = {}
+        # id -> (tensor, gradient): holding the tensor keeps its id from being reused while the entry lives
+        self._grads: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = {}
 
     def accumulate(self, tensor: torch.Tensor, grad: torch.Tensor) -> None:
         key = id(tensor)
         if key in self._grads:
-            self._grads[key] = self._grads[key] + grad
+            self._grads[key] = (tensor, self._grads[key][1] + grad)
         else:
-            self._grads[key] = grad
+            self._grads[key] = (tensor, grad)
 
     def get(self, tensor: torch.Tensor) -> Optional[torch.Tensor]:
-        return self._grads.get(id(tensor))
+        entry = self._grads.get(id(tensor))
+        return entry[1] if entry is not None and entry[0] is tensor else None
 
     def insert(self, tensor: torch.Tensor, grad: torch.Tensor) -> None:
-        self._grads[id(tensor)] = grad
+        self._grads[id(tensor)] = (tensor, grad)
 
 
 class CausalAttention:

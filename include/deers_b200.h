@@ -16,9 +16,10 @@
  *    that the caller can compact() and retry.  Outputs are written with the
  *    strides given in the descriptor.
  *  - Work is enqueued on the context's stream and the call returns at once; no
- *    allocation happens inside attn_fwd / attn_bwd, and no synchronisation except
- *    once per new (B, H, T, causal) on the f16 path, when a small work-schedule
- *    table is rebuilt on the host and uploaded.
+ *    allocation and no stream synchronisation happens inside attn_fwd / attn_bwd.
+ *    On the f16 path the first call with a new (B, H, T, causal) builds a small
+ *    work-schedule table on the host and uploads it asynchronously from pinned
+ *    memory; the tables of the last few shapes stay cached.
  *  - Nothing aborts or traps.  Every function returns a status (0 = OK) and
  *    device-side waits are bounded: a kernel that gives up records a code that
  *    deers_b200_sync() reports as DEERS_ERR_KERNEL.
@@ -184,9 +185,12 @@ int deers_b200_attn_fwd_bwd_host(deers_ctx* ctx, const deers_attn_desc* desc, co
  * Limits and rules:
  *  - B * H * ceil(T/128)*128 must not exceed 1,048,576 rows; larger problems return
  *    DEERS_ERR_WORKSPACE (deers_b200_last_error names the sizes) and must use deers_b200_attn_bwd.
- *  - The call allocates nothing and synchronises nothing.  The first call on each device looks up
- *    the array's device address (cudaGetSymbolAddress); make that first call outside any stream
- *    capture.
+ *  - The call allocates nothing.  The first call on each device looks up the array's device address
+ *    (cudaGetSymbolAddress), and the first call with a new (B, H, T, causal) builds a work-schedule table
+ *    on the host and uploads it with an asynchronous copy (as deers_b200_attn_bwd does); a few shapes
+ *    stay cached.  Make those first calls outside any stream capture: a new shape met while capturing
+ *    falls back to an unbalanced work assignment.  The only host-side wait is for an earlier upload from
+ *    the same cache slot, which has long finished unless shapes change on every call.
  *  - All calls on a device share the one array, which keeps the previous call's contents.  The
  *    backward's first kernel overwrites everything it later reads, so nothing has to be cleared, but
  *    two calls that overlap on the GPU (different streams or contexts) race on it: serialise them.
@@ -251,8 +255,11 @@ int deers_b200_rope_pack(deers_ctx* ctx, const deers_rope_desc* desc, const void
  *               reference's scalar ops do (`src/storage.rs:105-123`), so w, m, v are bit-identical to
  *               its CPU path.  `hyper->step` is the step count AFTER the increment of
  *               `optim.rs:215` (t >= 1).  With norm_dev != NULL the clip of grad_clip is applied to
- *               g on the fly (g itself is left untouched), which removes the host round trip of
- *               clip_grad_norm from the training step; with NULL the gradients are used as they are.
+ *               g on the fly, which removes the host round trip of clip_grad_norm from the training
+ *               step; with NULL the gradients are used as they are.  NOTE: g itself is left untouched,
+ *               whereas the reference's clip_grad_norm replaces the gradients in the GradientStore
+ *               (`optim.rs:287-294`): a caller that reads, logs or accumulates gradients after the step
+ *               and wants the clipped values calls deers_b200_grad_clip first and passes NULL here.
  */
 typedef struct deers_optim_tensor {
     void* w;        /* weights, updated in place (unused by grad_norm / grad_clip) */
@@ -449,6 +456,45 @@ int deers_b200_gpt_train_step(deers_gpt* model, const int64_t* ids, const int64_
 int deers_b200_gpt_train_step_host(deers_gpt* model, const int64_t* ids_host, const int64_t* targets_host, int32_t B,
                                    int32_t T, const deers_adamw_hyper* hyper, double max_grad_norm, float* loss_host,
                                    float* grad_norm_host);
+
+/*
+ * Multi-GPU: (batch x head) shards over the GPUs of one box and the all-gather of O.  No counterpart in the
+ * reference, which runs one context on device 0 (`src/storage/cuda.rs:455-462,503`; `Device::Cuda` carries no
+ * ordinal, `src/device.rs:15-22`).  The slices of [B,H,T,D] are independent in forward and backward
+ * (`src/models/gpt.rs:139-144` is batched over the two leading axes), so a rank runs deers_b200_attn_fwd / _bwd on
+ * its own contiguous range of flattened (b*H + h) slices and nothing is exchanged for the gradients.
+ *
+ *   shard_range     [begin, end) of the slices rank owns: contiguous, the first n mod world ranks one longer.
+ *   comm_init_all   one process, one context per GPU: full_buffers[r] is rank r's [n_slices, T, D] gather
+ *                   buffer (device memory of ctxs[r]'s GPU, `bytes` long); enables peer access between the GPUs
+ *                   and writes one communicator per rank to out[0..n).
+ *   comm_export /   one process per GPU: export writes a DEERS_IPC_HANDLE_BYTES handle of this rank's buffer
+ *   comm_init_ipc   (memory from cudaMalloc, possibly carved out of a larger allocation by a caching allocator;
+ *                   stream-ordered pool memory such as deers_b200_alloc's is NOT exportable); the host program
+ *                   passes all ranks' handles, in rank order, to init_ipc on every rank.
+ *   allgather_o     pushes bytes [offset, offset + bytes) of this rank's buffer (normally the range its forward
+ *                   just wrote its O slices to) into the same range of every peer's buffer: one device-to-device
+ *                   copy per peer over NVLink, each on its own stream, ordered after the work already enqueued on
+ *                   the context's stream.  The copies run on the copy engines and take no SM from the kernels that
+ *                   follow (the persistent backward kernels want one CTA on every SM).  Returns at once.
+ *   allgather_join  makes the context's stream wait for this rank's pushes (no host wait).
+ *   allgather_flush host-side wait for this rank's pushes.  A peer's slices are complete in this rank's buffer once
+ *                   THAT peer's pushes have finished: exchange that fact on the host (the transport that carried the
+ *                   handles, a barrier) after flush and before reading the gathered O.  A failed copy (a peer that
+ *                   went away) surfaces as DEERS_ERR_CUDA from the call that meets it, never as a device-side wait.
+ * No kernel of this library reads another GPU's memory.
+ */
+#define DEERS_IPC_HANDLE_BYTES 72
+typedef struct deers_comm deers_comm;
+void deers_b200_shard_range(int64_t n_slices, int32_t world, int32_t rank, int64_t* begin, int64_t* end);
+int deers_b200_comm_init_all(int32_t n, deers_ctx* const* ctxs, void* const* full_buffers, size_t bytes, deers_comm** out);
+int deers_b200_comm_export(deers_ctx* ctx, void* buffer, unsigned char* handle);
+int deers_b200_comm_init_ipc(deers_ctx* ctx, int32_t rank, int32_t world, void* local_buffer, size_t bytes,
+                             const unsigned char* handles, deers_comm** out);
+void deers_b200_comm_destroy(deers_comm* comm);
+int deers_b200_allgather_o(deers_comm* comm, size_t offset, size_t bytes);
+int deers_b200_allgather_join(deers_comm* comm);
+int deers_b200_allgather_flush(deers_comm* comm);
 
 /*
  * Status text, the way backend failures become `Error::Cuda(String)`

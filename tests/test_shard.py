@@ -68,3 +68,57 @@ def test_two_rank_gloo_gather_matches_unsharded(tmp_path, n_bh):
     world = 2
     mp.spawn(_worker, args=(world, _free_port(), n_bh, str(tmp_path)), nprocs=world, join=True)
     assert all((tmp_path / f"ok{r}").exists() for r in range(world))
+
+
+def test_partition_matches_the_c_abi():
+    """deers_b200_shard_range (what a Rust host calls) and shard.partition agree."""
+    import ctypes
+    from deers_b200 import _lib
+    L = _lib.lib()
+    b, e = ctypes.c_int64(), ctypes.c_int64()
+    for n in (0, 1, 5, 24, 2048, 2049):
+        for w in (1, 2, 3, 8):
+            for r in range(w):
+                L.deers_b200_shard_range(n, w, r, ctypes.byref(b), ctypes.byref(e))
+                assert (b.value, e.value) == shard.partition(n, w, r)
+    L.deers_b200_shard_range(8, 2, 2, ctypes.byref(b), ctypes.byref(e))      # bad rank: empty range, no crash
+    assert (b.value, e.value) == (0, 0)
+
+
+def _leaver(rank, world, port, result_dir, announce):
+    """Rank 1 runs one step and leaves between steps; rank 0 must get RankLeft at its next step, not hang."""
+    import time
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    store = dist.distributed_c10d._get_default_store()
+    rv = shard.StepRendezvous(store, rank, world, timeout_s=3.0)
+    rv.arrive(0)                                            # step 0: everyone is here
+    if rank == 1:
+        if announce:
+            rv.leave()
+        open(os.path.join(result_dir, "left1"), "w").close()
+        os._exit(0)                                          # gone between steps, nothing in flight
+    t0 = time.monotonic()
+    try:
+        rv.arrive(1)
+    except shard.RankLeft as err:
+        took = time.monotonic() - t0
+        assert err.missing == [1] and err.step == 1
+        assert took < (1.5 if announce else 10.0), took
+        open(os.path.join(result_dir, "ok0"), "w").close()
+    os._exit(0)                                              # no collective teardown with a dead peer
+
+
+@pytest.mark.parametrize("announce", [True, False])
+def test_rank_leaving_between_steps_raises_on_the_others(tmp_path, announce):
+    world = 2
+    ctx = mp.get_context("spawn")
+    port = _free_port()
+    procs = [ctx.Process(target=_leaver, args=(r, world, port, str(tmp_path), announce)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=60)
+        assert not p.is_alive(), "a rank hung"
+    assert (tmp_path / "left1").exists() and (tmp_path / "ok0").exists()
