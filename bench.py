@@ -710,6 +710,8 @@ def run_gpt_step(args):
         torch.cuda.synchronize()
 
     sampler = ClockSampler(local) if rank == 0 else None
+    torch.cuda.synchronize()
+    torch.cuda.set_stream(model.stream)                     # the timed loop and its events live on the model's stream
     for i in range(max(args.warmup, 3)):
         model.train_step(ids_d[i % n_batches], tgt_d[i % n_batches], **kw)
     barrier()
@@ -727,6 +729,7 @@ def run_gpt_step(args):
         blocks.append(ev0.elapsed_time(ev1))
     barrier()
     launches = (ctx.launch_count() - launches0) / len(blocks)
+    graph_active = model.graph_active()
     clocks = sampler.stop() if sampler else None
     ms = statistics.median(blocks) / args.steps
     ms_t = torch.tensor([ms], device=dev, dtype=torch.float64)
@@ -802,7 +805,9 @@ def run_gpt_step(args):
                            "parallelism": "1 GPU" if world == 1 else f"{world} independent replicas (replicas only)",
                            "timing": f"median of {len(blocks)} blocks of {args.steps} steps ({sum(blocks) / 1e3:.2f} s of device time)",
                            "l2": "weights, moments, gradients and logits (560 MB) exceed L2: no flush needed",
-                           "final_loss": final_loss, "graph": "forward + loss + backward + gradient norm replayed from a CUDA graph, AdamW launched after it",
+                           "final_loss": final_loss,
+                           "graph": ("forward + loss + backward + gradient norm replayed from a CUDA graph, AdamW launched after it"
+                                     if graph_active else "not captured: every kernel launched eagerly"),
                            "ms_x_median_sm_mhz": (ms_max * clocks["sm_mhz"]) if clocks and clocks.get("sm_mhz") else None},
                 "e2e": e2e, "gpu_launches": int(round(eager_launches * args.steps)),
                 "launches_per_step": {"kernels": eager_launches, "host_calls_with_graph": launches / args.steps},
@@ -824,10 +829,11 @@ def main():
     ap.add_argument("--shape", default=None, help="B,T,H,D: a custom shape (profiling captures on a small case)")
     ap.add_argument("--dtype", default=None, choices=["f16", "f32"], help="dtype for --shape")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--gather", default="none", choices=["overlap", "none"],
-                    help="N>1: include an all-gather of O over NCCL (side stream, overlapping the backward) in the "
-                         "timed step.  Default none: gradients and O stay sharded, as a training step needs them; "
-                         "the gather's cost is measured separately and reported under config.gather_probe")
+    ap.add_argument("--gather", default="peer", choices=["peer", "nccl", "none"],
+                    help="N>1: the all-gather of O that the sharded workload names, inside the timed step.  peer "
+                         "(default): the C ABI's copy-engine pushes into every rank's buffer, started after the forward "
+                         "and overlapping the backward; nccl: a library all-gather on a side stream; none: O stays "
+                         "sharded (compute only).  The other variants are timed beside it under config.gather_probe")
     ap.add_argument("--bwd", default="keep-ds", choices=["keep-ds", "recompute"],
                     help="f16 backward: keep the dS tiles in the workspace between its kernels (default), or "
                          "recompute S and dP in the dQ kernel (workspace of a few MB)")
@@ -926,15 +932,36 @@ def main():
     # The backward keeps its dS tiles when the workspace has room for them (pass 2), else recomputes S and dP.
     ws_bytes = ops.workspace_bytes(q, scale, pass_=1 if args.bwd == "recompute" else 2)
     workspace = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=dev)
-    gatherer = shard.OverlappedGather(n_total, T, D, tdtype, dev) if world > 1 else None
+    nccl_gather = shard.OverlappedGather(n_total, T, D, tdtype, dev) if world > 1 else None
+    peer_gather, peer_error = None, None
+    if world > 1:
+        try:
+            peer_gather = shard.PeerGather(n_total, T, D, tdtype, dev, ctx)
+        except Exception as err:                             # peer mappings unavailable on this box: say so, use NCCL
+            peer_error = f"{type(err).__name__}: {err}"
+        ok = torch.tensor([1 if peer_gather is not None else 0], device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)            # all ranks take the same path
+        if int(ok.item()) == 0:
+            peer_gather = None
+    gather_mode = args.gather if world > 1 else "none"
+    if gather_mode == "peer" and peer_gather is None:
+        gather_mode = "nccl"
 
-    def step(gather=(args.gather == "overlap")):
-        o, lse = ops.attention_fwd(q, k, v, scale, True)
-        if gather and gatherer is not None:
-            gatherer.start(o)
+    def step(mode=None):
+        mode = gather_mode if mode is None else mode
+        if mode == "peer":
+            # the forward writes this rank's O straight into its slices of the gather buffer
+            o, lse = ops.attention_fwd(q, k, v, scale, True, out=peer_gather.local().view(Bs, Hs, T, D))
+            peer_gather.start()                              # pushes run on the copy engines under the backward
+        else:
+            o, lse = ops.attention_fwd(q, k, v, scale, True)
+            if mode == "nccl":
+                nccl_gather.start(o)
         grads = ops.attention_bwd(q, k, v, o, lse, do, scale, True, workspace=workspace)
-        if gather and gatherer is not None:
-            gatherer.finish()
+        if mode == "peer":
+            peer_gather.join()                               # the step ends when this rank's pushes have left
+        elif mode == "nccl":
+            nccl_gather.finish()
         return o, grads
 
     def barrier():
@@ -947,17 +974,30 @@ def main():
         step()
     barrier()
 
-    ctx.kernel_timing(True)
+    # The driver fixes --steps; a block of K steps can be far shorter than the time the clocks need to settle under
+    # the power cap, so blocks are repeated (every rank the same number of times) until about two seconds of device
+    # time have passed, and the median block is reported.  Per-kernel events are taken in one extra block.
+    def timed_block(mode=None, steps=None):
+        a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        a.record()
+        for _ in range(steps or args.steps):
+            step(mode)
+        b_.record()
+        barrier()
+        t = torch.tensor([a.elapsed_time(b_) / (steps or args.steps)], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)         # max over ranks
+        return float(t.item())
+
+    first = timed_block()
+    n_blocks = int(min(400, max(3, round(2000.0 / max(first * args.steps, 1e-3)))))
     launches0 = ctx.launch_count()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    ev0.record()
-    for _ in range(args.steps):
-        step()
-    ev1.record()
-    barrier()
-    ms = ev0.elapsed_time(ev1) / args.steps
-    launches = ctx.launch_count() - launches0
+    blocks = [timed_block() for _ in range(n_blocks)]
+    launches = (ctx.launch_count() - launches0) // n_blocks
+    ms_max = statistics.median(blocks)
+    ctx.kernel_timing(True)
+    timed_block()
     ktimes = {name: ctx.kernel_time(kind) for name, kind in
               (("fwd", _lib.K_FWD), ("bwd_prep", _lib.K_BWD_PREP), ("bwd_main", _lib.K_BWD_MAIN),
                ("bwd_dq", _lib.K_BWD_DQ))}
@@ -965,32 +1005,42 @@ def main():
     ctx.sync()
     clocks = sampler.stop() if sampler else None
 
-    ms_t = torch.tensor([ms], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(ms_t, op=dist.ReduceOp.MAX)
-    ms_max = float(ms_t.item())
-
     # ---- N > 1: what the optional all-gather of O costs (overlapped with the backward, and alone) ----
     gather_probe = None
     if world > 1:
-        def timed(fn, reps):
+        probe = {"bytes_received_per_gpu": (n_total - n_local) * T * D * esize,
+                 "bytes_sent_per_gpu": (world - 1) * n_local * T * D * esize, "peer_error": peer_error}
+        modes = ["none", "nccl"] + (["peer"] if peer_gather is not None else [])
+        for mode in modes:
+            step(mode)
+            probe[f"step_ms_gather_{mode}"] = statistics.median([timed_block(mode, 5) for _ in range(5)])
+
+        def alone(fn):
             a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             barrier()
             a.record()
-            for _ in range(reps):
+            for _ in range(5):
                 fn()
             b_.record()
             barrier()
-            t = torch.tensor([a.elapsed_time(b_) / reps], device=dev, dtype=torch.float64)
+            t = torch.tensor([a.elapsed_time(b_) / 5], device=dev, dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             return float(t.item())
         o_probe, _ = ops.attention_fwd(q, k, v, scale, True)
-        step(True)
-        overlap_ms = timed(lambda: step(True), 5)
-        shard.gather_output(o_probe, n_total, out=gatherer.out)
-        alone_ms = timed(lambda: shard.gather_output(o_probe, n_total, out=gatherer.out), 5)
-        gather_probe = {"step_with_overlapped_gather_ms": overlap_ms, "allgather_alone_ms": alone_ms,
-                        "bytes_received_per_gpu": (n_total - n_local) * T * D * esize}
+        probe["nccl_allgather_alone_ms"] = alone(lambda: shard.gather_output(o_probe, n_total, out=nccl_gather.out))
+        if peer_gather is not None:
+            def push():
+                peer_gather.start()
+                peer_gather.join()
+            probe["peer_allgather_alone_ms"] = alone(push)
+            # gathered O must equal what the library all-gather delivers (every rank's forward is deterministic)
+            o_p, _ = ops.attention_fwd(q, k, v, scale, True, out=peer_gather.local().view(Bs, Hs, T, D))
+            peer_gather.start()
+            got = peer_gather.wait_all()
+            want = shard.gather_output(o_p, n_total, out=nccl_gather.out)
+            torch.cuda.synchronize()
+            probe["peer_gather_matches_nccl"] = bool(torch.equal(got, want))
+        gather_probe = probe
         del o_probe
     total_flops = flops_fwd_bwd(n_total, T, D)
     value = total_flops / (ms_max * 1e-3) / 1e12
@@ -1005,6 +1055,7 @@ def main():
                    (torch.empty(q.shape[:3], dtype=torch.float32, pin_memory=True),)
         nbytes = q.numel() * esize
         chunk = max(1, min(n_local, (args.e2e_chunk_mb << 20) // max(4 * T * D * esize, 1)))
+        chunk = max(1, min(chunk, -(-n_local // 12)))        # at least twelve chunks: the three-stage pipeline needs a run-in
         dsc = _lib.AttnDesc()
         _lib.lib().deers_b200_attn_desc_compact(dsc, Bs, Hs, T, D, _lib.F16 if dtype == "f16" else _lib.F32, 1, scale)
         scratch = torch.empty(int(_lib.lib().deers_b200_attn_host_scratch_bytes(dsc, chunk)), dtype=torch.uint8, device=dev)
@@ -1024,6 +1075,8 @@ def main():
         e2e = {"value": total_flops / (float(e_ms.item()) * 1e-3) / 1e12, "unit": UNIT,
                "h2d_bytes_per_step": 4 * nbytes, "d2h_bytes_per_step": 4 * nbytes + q.numel() // D * 4,
                "ms_per_step": float(e_ms.item()), "steps": args.e2e_steps,
+               "host_link_gbs_each_way_per_gpu": 4 * nbytes / (float(e_ms.item()) * 1e-3) / 1e9,
+               "chunks_per_rank": -(-n_local // chunk),
                "api": f"deers_b200_attn_fwd_bwd_host: pinned host Q,K,V,dO -> O,dQ,dK,dV,lse on the host, "
                       f"{chunk} slices per chunk, copies and kernels pipelined on three streams; timed on the host "
                       "clock around the blocking calls (the call returns after the last copy)"}
@@ -1035,7 +1088,12 @@ def main():
         bwd_avg = bwd_ms / max(bwd_n, 1)
         # The dominant kernel is the dK/dV kernel: 4 causal products (S^T, dP^T, dV, dK) of n*T^2*D FLOPs each.
         dkdv_flops = 4.0 * n_local * T * T * D
-        peak = peaks["tflops_sustained"] if dtype == "f16" else None
+        # Which measured peak is the honest comparator follows from the clocks seen during the timed region: at
+        # (nearly) the maximum clock with no power cap the burst figure, otherwise the sustained one.
+        at_max_clock = bool(clocks and clocks.get("sm_mhz") and clocks.get("sm_max_mhz") and
+                            clocks["sm_mhz"] >= 0.95 * clocks["sm_max_mhz"] and "sw_power_cap" not in clocks.get("reasons", []))
+        peak_kind = "burst" if at_max_clock else "sustained"
+        peak = peaks["tflops_" + peak_kind] if dtype == "f16" else None
         roofline = None
         if dtype == "f16":
             achieved = dkdv_flops / (bwd_avg * 1e-3) / 1e12
@@ -1048,7 +1106,9 @@ def main():
             roofline = {"bound": "tensor", "kernel": "attn_bwd_dkdv_f16_kernel", "achieved": achieved, "peak": peak,
                         "unit": UNIT, "frac": achieved / peak, "traffic": traffic,
                         "flops_per_launch": dkdv_flops,
-                        "peak_source": f"{peaks['source']} sustained bf16 (kernel timed inside a long step)",
+                        "peak_source": f"{peaks['source']} {peak_kind} bf16 (median SM clock {clocks.get('sm_mhz') if clocks else None} MHz "
+                                       f"of {clocks.get('sm_max_mhz') if clocks else None}, reasons {clocks.get('reasons') if clocks else None})",
+                        "frac_of_burst": achieved / peaks["tflops_burst"], "frac_of_sustained": achieved / peaks["tflops_sustained"],
                         "avg_launch_ms": bwd_avg}
         else:
             # f32 FFMA path at this size is HBM/latency bound: algorithmic bytes of the whole step.
@@ -1080,14 +1140,21 @@ def main():
                 "config": {"workload": workload_name(args.workload, dtype, B, T, H, D),
                            "flops_per_step": total_flops, "flop_convention": "7*B*H*T^2*D (causal fwd 2, bwd 5)",
                            "parallelism": f"(b x h) shards over {world} GPU(s), {n_local} slices on rank 0",
-                           "gather": (args.gather if world > 1 else "n/a (1 GPU)"), "gather_probe": gather_probe,
+                           "gather": ({"peer": "all-gather of O inside the timed step: copy-engine pushes (deers_b200_allgather_o), overlapping the backward",
+                                       "nccl": "all-gather of O inside the timed step: NCCL on a side stream, overlapping the backward",
+                                       "none": "none (compute only)"}[gather_mode] if world > 1 else "n/a (1 GPU)"),
+                           "gather_probe": gather_probe,
+                           "timing": f"median of {n_blocks} blocks of {args.steps} steps ({sum(blocks) * args.steps / 1e3:.2f} s of device time), max over ranks per block",
+                           "ms_x_median_sm_mhz": (ms_max * clocks["sm_mhz"]) if clocks and clocks.get("sm_mhz") else None,
                            "backward": ("dS tiles kept in the workspace between the dK/dV and dQ kernels"
                                         if args.bwd == "keep-ds" and dtype == "f16" else "dQ kernel recomputes S and dP"),
                            "workspace_bytes": ws_bytes,
                            "l2": "inputs larger than L2 (no flush needed)" if 4 * q.numel() * esize > 126e6
                                  else "inputs fit in L2 (not flushed)",
-                           "frac_of_dense_peak": value / world / peaks["tflops_sustained"],
-                           "peak_tflops": peaks["tflops_sustained"], "peak_source": peaks["source"]},
+                           "frac_of_dense_peak": value / world / peaks["tflops_" + peak_kind],
+                           "frac_of_burst_peak": value / world / peaks["tflops_burst"],
+                           "frac_of_sustained_peak": value / world / peaks["tflops_sustained"],
+                           "peak_tflops": peaks["tflops_" + peak_kind], "peak_kind": peak_kind, "peak_source": peaks["source"]},
                 "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "roofline": roofline,
                 "kernels": kernels, "cpu_baseline": cb}
         sys.stdout.flush()

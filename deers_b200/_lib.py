@@ -28,10 +28,12 @@ SYMBOLS = [
     "deers_b200_embedding_fwd", "deers_b200_embedding_bwd", "deers_b200_cross_entropy_scratch_bytes",
     "deers_b200_cross_entropy_fwd", "deers_b200_cross_entropy_bwd",
     "deers_b200_gpt_create", "deers_b200_gpt_destroy", "deers_b200_gpt_num_params", "deers_b200_gpt_param_info",
-    "deers_b200_gpt_param_set", "deers_b200_gpt_param_get", "deers_b200_gpt_set_graph", "deers_b200_gpt_forward",
+    "deers_b200_gpt_param_set", "deers_b200_gpt_param_get", "deers_b200_gpt_set_graph", "deers_b200_gpt_graph_active",
+    "deers_b200_gpt_forward",
     "deers_b200_gpt_forward_backward", "deers_b200_gpt_train_step", "deers_b200_gpt_train_step_host",
     "deers_b200_shard_range", "deers_b200_comm_init_all", "deers_b200_comm_export", "deers_b200_comm_init_ipc",
     "deers_b200_comm_destroy", "deers_b200_allgather_o", "deers_b200_allgather_join", "deers_b200_allgather_flush",
+    "deers_b200_selftest_wait",
 ]
 IPC_HANDLE_BYTES = 72
 K_FWD, K_BWD_PREP, K_BWD_MAIN, K_BWD_DQ, K_ROPE, K_OPTIM, K_NORM, K_DECODE, K_GEMM, K_GPT = range(10)
@@ -153,6 +155,7 @@ def lib() -> ctypes.CDLL:
     L.deers_b200_gpt_param_set.argtypes = [vp, i32, i32, vp]
     L.deers_b200_gpt_param_get.argtypes = [vp, i32, i32, vp]
     L.deers_b200_gpt_set_graph.argtypes = [vp, i32]
+    L.deers_b200_gpt_graph_active.argtypes = [vp]
     L.deers_b200_gpt_forward.argtypes = [vp, vp, ctypes.c_int32, ctypes.c_int32, vp]
     L.deers_b200_gpt_forward_backward.argtypes = [vp, vp, vp, ctypes.c_int32, ctypes.c_int32, vp]
     L.deers_b200_gpt_train_step.argtypes = [vp, vp, vp, ctypes.c_int32, ctypes.c_int32, hp, ctypes.c_double, vp, vp]
@@ -175,6 +178,7 @@ def lib() -> ctypes.CDLL:
     L.deers_b200_launch_count.argtypes = [vp]
     L.deers_b200_launch_count.restype = ctypes.c_uint64
     L.deers_b200_selftest_umma.argtypes = [vp, ctypes.POINTER(ctypes.c_float)]
+    L.deers_b200_selftest_wait.argtypes = [vp, ctypes.c_uint32, ctypes.POINTER(ctypes.c_int32)]
     L.deers_b200_kernel_timing.argtypes = [vp, i32]
     L.deers_b200_kernel_time.argtypes = [vp, i32, i32, ctypes.POINTER(ctypes.c_double),
                                          ctypes.POINTER(ctypes.c_uint64)]

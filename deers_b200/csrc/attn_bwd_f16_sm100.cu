@@ -175,7 +175,7 @@ attn_bwd_dkdv_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         for (int s = 0; s < 3; ++s) { mbar_init(&bars[A_Q_FULL + s], 1); mbar_init(&bars[A_Q_EMPTY + s], 1); }
         for (int s = 0; s < 2; ++s) {
             mbar_init(&bars[A_DO_FULL + s], 1); mbar_init(&bars[A_DO_EMPTY + s], 1);
-            mbar_init(&bars[A_ST_FULL + s], 1); mbar_init(&bars[A_ST_EMPTY + s], 256);
+            mbar_init(&bars[A_ST_FULL + s], 256);
         }
         mbar_init(&bars[A_S], 1);
         mbar_init(&bars[A_DP], 1);
@@ -225,10 +225,6 @@ attn_bwd_dkdv_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
 #pragma unroll
                     for (int blk = 0; blk < DBLK; ++blk)
                         tma_load_4d(sQ + qs * TILE_BYTES + blk * BLOCK_BYTES, &tmap_q, &bars[A_Q_FULL + qs], blk * 64, q0, h, b);
-                    if (!mbar_wait(ws, &bars[A_ST_EMPTY + ds], ((gi >> 1) & 1u) ^ 1u, DEERS_KERR_BWD_F16 | 3)) { ok = false; break; }
-                    mbar_arrive_expect_tx(&bars[A_ST_FULL + ds], 2 * BT * 4);
-                    bulk_load(lse2_s + ds * BT, p.lse2 + (long long)bh * p.Tpad + q0, BT * 4, &bars[A_ST_FULL + ds]);
-                    bulk_load(delta_s + ds * BT, p.delta + (long long)bh * p.Tpad + q0, BT * 4, &bars[A_ST_FULL + ds]);
                     if (!mbar_wait(ws, &bars[A_DO_EMPTY + ds], ((gi >> 1) & 1u) ^ 1u, DEERS_KERR_BWD_F16 | 4)) { ok = false; break; }
                     mbar_arrive_expect_tx(&bars[A_DO_FULL + ds], TILE_BYTES);
 #pragma unroll
@@ -327,6 +323,22 @@ attn_bwd_dkdv_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         const float sl2 = p.scale * LOG2E;
         uint32_t gi = 0;
         bool alive = true;
+        // The 128 lse * log2e and the 128 delta values of a query tile are staged in shared memory by the compute
+        // threads themselves: thread ct fetches element ct of the NEXT iteration's 256 values one iteration ahead
+        // (a plain global load, in flight during this iteration's products), stores it at the top of that
+        // iteration and arrives on the stage's barrier; everyone waits for all 256 before reading.  A stage is
+        // rewritten two iterations after it was read, and nobody gets there before all threads have passed the
+        // barrier of the iteration in between, i.e. have finished reading.  (An earlier version had the producer
+        // warp bring these rows in with bulk copies; repeated full-size runs then showed, once in a few dozen, one
+        // warp seeing a stale 32-byte piece of the delta row in the first iteration of an item.)
+        const int ct = (warp - 2) * 32 + lane;
+        const float* stat_src = (ct < BT) ? p.lse2 + ct : p.delta + (ct - BT);
+        float* stat_dst = (ct < BT) ? lse2_s + ct : delta_s + (ct - BT);
+        float stat_next = 0.f;
+        {
+            const int4 first = next_item(p, 0, n_items, nq);
+            if (first.x >= 0) stat_next = __ldg(stat_src + (long long)first.y * p.Tpad + (p.causal ? first.x : 0) * BT);
+        }
 
         for (int4 cur = next_item(p, 0, n_items, nq), nxt = next_item(p, 1, n_items, nq), n4 = make_int4(0, 0, 0, 0); alive && cur.x >= 0;
                  ++n4.x, cur = nxt, nxt = next_item(p, n4.x + 1, n_items, nq)) {
@@ -342,6 +354,11 @@ attn_bwd_dkdv_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
                 const uint32_t ss = gi & 1u, par = gi & 1u;
                 const float* lse2 = lse2_s + ss * BT + 64 * g;
                 const float* dlt = delta_s + ss * BT + 64 * g;
+                stat_dst[ss * BT] = stat_next;              // this iteration's value, fetched one iteration ago
+                mbar_arrive(&bars[A_ST_FULL + ss]);
+                // next iteration's value: the next query tile of this item, or the first one of the next item
+                if (it + 1 < niter) stat_next = __ldg(stat_src + (long long)bh * p.Tpad + (i + 1) * BT);
+                else if (nxt.x >= 0) stat_next = __ldg(stat_src + (long long)nxt.y * p.Tpad + (p.causal ? nxt.x : 0) * BT);
                 if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[A_ST_FULL + ss], (gi >> 1) & 1u, DEERS_KERR_BWD_F16 | 13))) { alive = false; break; }
                 if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[A_S], par, DEERS_KERR_BWD_F16 | 14))) { alive = false; break; }
                 tc_fence_after_sync();
@@ -393,7 +410,6 @@ attn_bwd_dkdv_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
                                                     pf.y * (__uint_as_float(dr[e * 2 + 1]) - dlt[cl + 1]));
                     }
                 }
-                mbar_arrive(&bars[A_ST_EMPTY + ss]);        // this stage's lse / delta rows have been read
                 tmem_st_x32(tmem + TM_DP + t_lane + 64 * g, dd);
                 tmem_wait_st();
                 tc_fence_before_sync();

@@ -119,11 +119,14 @@ int launch_attn_bwd_f32(deers_ctx* ctx, const deers_attn_desc* d, const float* q
 // f16 tcgen05 path (attn_f16_sm100.cu)
 int launch_attn_fwd_f16(deers_ctx* ctx, const deers_attn_desc* d, const void* q, const void* k,
                         const void* v, void* o, float* lse);
+int launch_attn_fwd2_f16(deers_ctx* ctx, const deers_attn_desc* d, const void* q, const void* k,
+                         const void* v, void* o, float* lse);
 int launch_attn_bwd_f16(deers_ctx* ctx, const deers_attn_desc* d, const void* q, const void* k,
                         const void* v, const void* o, const float* lse, const void* d_o, void* dq,
                         void* dk, void* dv, void* workspace, bool keep_ds);
 size_t attn_bwd_f16_workspace_bytes(const deers_attn_desc* d, bool keep_ds);
 int run_selftest_umma(deers_ctx* ctx, float* max_abs_err);
+int run_selftest_wait(deers_ctx* ctx, unsigned int limit_ms, int* result_host);
 
 // f32 GEMM (gemm_f32.cu)
 size_t gemm_f32_workspace_bytes(const deers_ctx* ctx, int M, int N, int K);

@@ -528,3 +528,10 @@ extern "C" int deers_b200_selftest_umma(deers_ctx* ctx, float* max_abs_err) {
     DEERS_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
     return run_selftest_umma(ctx, max_abs_err);
 }
+
+extern "C" int deers_b200_selftest_wait(deers_ctx* ctx, uint32_t limit_ms, int32_t* result) {
+    if (!ctx || !result) return DEERS_ERR_NULL;
+    if (limit_ms < 1 || limit_ms > 1000) return DEERS_ERR_SHAPE;
+    DEERS_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    return run_selftest_wait(ctx, limit_ms, result);
+}

@@ -474,6 +474,8 @@ extern "C" int deers_b200_gpt_set_graph(deers_gpt* m, int enable) {
     return DEERS_OK;
 }
 
+extern "C" int deers_b200_gpt_graph_active(const deers_gpt* m) { return (m && m->graph_exec) ? 1 : 0; }
+
 extern "C" int deers_b200_gpt_forward(deers_gpt* m, const int64_t* ids, int32_t B, int32_t T, float* logits) {
     if (!m || !ids) return DEERS_ERR_NULL;
     GPT_TRY(check_bt(m, B, T));

@@ -49,12 +49,13 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 // (shared memory) makes every later wait of the CTA return at once, and the
 // first code is recorded in the context's error word (global) so that CTAs not
 // yet started exit immediately and the host learns of it at the next sync.
+constexpr uint64_t kWaitLimitNs = 2000000000ull;   // 2 s without progress = give up
+
 struct WaitState {
     volatile uint32_t* abort;   // shared memory flag
-    unsigned int* err;          // global (mapped host) error word
+    unsigned int* err;          // error word in device memory
+    uint64_t limit_ns = kWaitLimitNs;
 };
-
-constexpr uint64_t kWaitLimitNs = 2000000000ull;   // 2 s without progress = give up
 
 // Waits for the phase with the given parity.  Returns false if this or an
 // earlier wait of the CTA gave up; callers then fall through to the teardown.
@@ -68,7 +69,7 @@ __device__ __forceinline__ bool mbar_wait(const WaitState& ws, uint64_t* bar, ui
             if (*ws.abort) return false;
             const uint64_t now = global_timer_ns();
             if (t0 == 0) t0 = now;
-            else if (now - t0 > kWaitLimitNs) {
+            else if (now - t0 > ws.limit_ns) {
                 *ws.abort = 1;
                 atomicCAS(ws.err, 0u, code);
                 return false;

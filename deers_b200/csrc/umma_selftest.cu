@@ -129,6 +129,49 @@ int make_tmap_2d(deers_ctx* ctx, CUtensorMap* out, const __half* base, int rows,
 
 }  // namespace
 
+// Bounded-wait self-test: a barrier nobody arrives at.  Thread 0 waits on it through the same mbar_wait every
+// kernel of the library uses, with a limit of a few milliseconds instead of two seconds; the wait must give
+// up, raise the CTA's abort flag and record its code in the error word.  Thread 32 then waits on the same
+// barrier and must return at once because of the flag.  The kernel ends normally: no trap, no hang.
+__global__ void __launch_bounds__(64) wait_selftest_kernel(unsigned int* err, unsigned long long limit_ns, int* out) {
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ uint32_t abort_s;
+    if (threadIdx.x == 0) {
+        abort_s = 0;
+        mbar_init(&bar, 1);
+        fence_barrier_init();
+    }
+    __syncthreads();
+    WaitState ws{&abort_s, err, limit_ns};
+    if (threadIdx.x == 0) {
+        const uint64_t t0 = global_timer_ns();
+        const bool ok = mbar_wait(ws, &bar, 0, DEERS_KERR_SELFTEST | 0x7f);
+        out[0] = ok ? 0 : 1;                                   // 1: gave up, as it must
+        out[2] = (int)((global_timer_ns() - t0) / 1000ull);    // microseconds spent waiting
+    }
+    __syncthreads();
+    if (threadIdx.x == 32) {
+        const uint64_t t0 = global_timer_ns();
+        const bool ok = mbar_wait(ws, &bar, 0, DEERS_KERR_SELFTEST | 0x7e);
+        out[1] = ok ? 0 : 1;
+        out[3] = (int)((global_timer_ns() - t0) / 1000ull);
+    }
+}
+
+int run_selftest_wait(deers_ctx* ctx, unsigned int limit_ms, int* result_host) {
+    int* d = nullptr;
+    DEERS_CUDA_TRY(ctx, cudaMalloc(&d, 4 * sizeof(int)));
+    cudaMemsetAsync(d, 0xff, 4 * sizeof(int), ctx->stream);
+    wait_selftest_kernel<<<1, 64, 0, ctx->stream>>>(ctx->dev_err, (unsigned long long)limit_ms * 1000000ull, d);
+    ctx->launches += 1;
+    cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) e = cudaMemcpyAsync(result_host, d, 4 * sizeof(int), cudaMemcpyDeviceToHost, ctx->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);      // the error word is left for deers_b200_sync
+    cudaFree(d);
+    DEERS_CUDA_TRY(ctx, e);
+    return DEERS_OK;
+}
+
 int run_selftest_umma(deers_ctx* ctx, float* max_abs_err) {
     const int M = 128, K = ST_K;
     struct Case { int N, a_mn, b_mn, a_manual; };

@@ -45,7 +45,12 @@ class GPT:
         if device.type != "cuda":
             raise DeviceMismatch("the model step only exists on the CUDA device (no CPU fallback)")
         self.config = config
-        self.ctx = Context.current(device)
+        # The step is replayed from a CUDA graph, and the legacy default stream cannot be captured: the model
+        # enqueues on a stream of its own.  Calls order it after the caller's current stream and the caller's
+        # stream after it, so tensors passed in and handed back behave as on one stream.
+        self.stream = torch.cuda.Stream(device=device)
+        with torch.cuda.stream(self.stream):
+            self.ctx = Context.current(device)
         self.device = device
         self.handle = ctypes.c_void_p()
         c = _lib.GptConfig(config.vocab_size, config.sequence_len, config.n_layer, config.n_head, config.n_embd,
@@ -113,6 +118,10 @@ class GPT:
         self._set(index, 2, m)
         self._set(index, 3, v)
 
+    def graph_active(self) -> bool:
+        """True once steps are replayed from a captured CUDA graph."""
+        return bool(_lib.lib().deers_b200_gpt_graph_active(self.handle))
+
     def set_graph(self, enable: bool) -> None:
         _lib.check(_lib.lib().deers_b200_gpt_set_graph(self.handle, int(enable)), self.ctx.handle)
 
@@ -127,15 +136,36 @@ class GPT:
             raise LayoutMismatch(f"{name}: expected {n} ids, got {t.numel()}")
         return t
 
+    class _Ordered:
+        """Orders the model's stream after the caller's current stream on entry and the caller's after the
+        model's on exit (two event waits, no host synchronisation; nothing when they are the same stream)."""
+
+        def __init__(self, model):
+            self.model = model
+
+        def __enter__(self):
+            self.outer = torch.cuda.current_stream(self.model.device)
+            if self.outer != self.model.stream:
+                self.model.stream.wait_stream(self.outer)
+            self.guard = torch.cuda.stream(self.model.stream)
+            self.guard.__enter__()
+
+        def __exit__(self, *exc):
+            self.guard.__exit__(*exc)
+            if self.outer != self.model.stream:
+                self.outer.wait_stream(self.model.stream)
+            return False
+
     def forward(self, idx: torch.Tensor) -> torch.Tensor:
         """`GPT::forward` (gpt.rs:329-355): ids [B, T] -> logits [B, T, vocab]."""
         if idx.dim() != 2:
             raise LayoutMismatch("GPT expects token ids with shape [B, T]")
         idx = self._ids("idx", idx)
         B, T = idx.shape
-        logits = torch.empty((B, T, self.config.vocab_size), dtype=torch.float32, device=self.device)
-        _lib.check(_lib.lib().deers_b200_gpt_forward(self.handle, idx.data_ptr(), B, T, logits.data_ptr()),
-                   self.ctx.handle)
+        with GPT._Ordered(self):
+            logits = torch.empty((B, T, self.config.vocab_size), dtype=torch.float32, device=self.device)
+            _lib.check(_lib.lib().deers_b200_gpt_forward(self.handle, idx.data_ptr(), B, T, logits.data_ptr()),
+                       self.ctx.handle)
         return logits
 
     def forward_backward(self, idx: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
@@ -144,9 +174,10 @@ class GPT:
         idx = self._ids("idx", idx)
         B, T = idx.shape
         targets = self._ids("targets", targets, B * T)
-        loss = torch.empty(1, dtype=torch.float32, device=self.device)
-        _lib.check(_lib.lib().deers_b200_gpt_forward_backward(self.handle, idx.data_ptr(), targets.data_ptr(), B, T,
-                                                              loss.data_ptr()), self.ctx.handle)
+        with GPT._Ordered(self):
+            loss = torch.empty(1, dtype=torch.float32, device=self.device)
+            _lib.check(_lib.lib().deers_b200_gpt_forward_backward(self.handle, idx.data_ptr(), targets.data_ptr(), B, T,
+                                                                  loss.data_ptr()), self.ctx.handle)
         return loss
 
     def _hyper(self, lr, betas, eps, weight_decay) -> _lib.AdamWHyper:
@@ -160,11 +191,12 @@ class GPT:
         idx = self._ids("idx", idx)
         B, T = idx.shape
         targets = self._ids("targets", targets, B * T)
-        out = torch.empty(2, dtype=torch.float32, device=self.device)
         h = self._hyper(lr, betas, eps, weight_decay)
-        _lib.check(_lib.lib().deers_b200_gpt_train_step(self.handle, idx.data_ptr(), targets.data_ptr(), B, T,
-                                                        ctypes.byref(h), max_grad_norm, out.data_ptr(),
-                                                        out.data_ptr() + 4), self.ctx.handle)
+        with GPT._Ordered(self):
+            out = torch.empty(2, dtype=torch.float32, device=self.device)
+            _lib.check(_lib.lib().deers_b200_gpt_train_step(self.handle, idx.data_ptr(), targets.data_ptr(), B, T,
+                                                            ctypes.byref(h), max_grad_norm, out.data_ptr(),
+                                                            out.data_ptr() + 4), self.ctx.handle)
         return out[0:1], out[1:2]
 
     def train_step_host(self, idx: np.ndarray, targets: np.ndarray, lr: float, betas=(0.9, 0.999), eps: float = 1e-8,
@@ -178,6 +210,7 @@ class GPT:
         B, T = idx.shape
         loss, norm = ctypes.c_float(), ctypes.c_float()
         h = self._hyper(lr, betas, eps, weight_decay)
+        torch.cuda.set_device(self.device)
         _lib.check(_lib.lib().deers_b200_gpt_train_step_host(self.handle, idx.ctypes.data_as(ctypes.c_void_p),
                                                              targets.ctypes.data_as(ctypes.c_void_p), B, T,
                                                              ctypes.byref(h), max_grad_norm, ctypes.byref(loss),

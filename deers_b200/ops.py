@@ -72,6 +72,13 @@ class Context:
                                                      ctypes.byref(n)), self.handle)
         return ms.value, int(n.value)
 
+    def selftest_wait(self, limit_ms: int = 5) -> List[int]:
+        """Runs the give-up path of the bounded device waits (deers_b200_selftest_wait): returns
+        [first wait gave up, second wait saw the abort flag, microseconds of each]."""
+        res = (ctypes.c_int32 * 4)()
+        _lib.check(_lib.lib().deers_b200_selftest_wait(self.handle, limit_ms, res), self.handle)
+        return [int(v) for v in res]
+
     def selftest_umma(self) -> List[float]:
         errs = (ctypes.c_float * 6)()
         _lib.check(_lib.lib().deers_b200_selftest_umma(self.handle, errs), self.handle)
@@ -129,8 +136,12 @@ def default_scale(head_dim: int) -> float:
     return 1.0 / math.sqrt(float(head_dim))
 
 
-def attention_fwd(q, k, v, scale: float, causal: bool = True, token_major_out: bool = False):
+def attention_fwd(q, k, v, scale: float, causal: bool = True, token_major_out: bool = False,
+                  out: Optional[torch.Tensor] = None):
     """Storage-level forward: returns (o [B,H,T,D], lse [B,H,T] float32).
+
+    ``out`` (same shape and dtype as q, inner stride 1) receives O in place, e.g. this rank's slices of
+    the buffer an all-gather of O pushes from.
 
     o is compact by default.  With ``token_major_out`` its memory is a compact [B,T,H,D] buffer
     and the returned tensor is the [B,H,T,D] view of it, so the module's
@@ -139,7 +150,11 @@ def attention_fwd(q, k, v, scale: float, causal: bool = True, token_major_out: b
     _check_inputs("attention_fwd", (q, k, v))
     q, k, v = _compact(q), _compact(k), _compact(v)
     ctx = Context.current(q.device)
-    if token_major_out:
+    if out is not None:
+        if out.shape != q.shape or out.dtype != q.dtype or out.device != q.device or not _usable(out):
+            raise LayoutMismatch(f"attention_fwd: out must match q ({tuple(q.shape)}, {q.dtype}) with unit inner stride")
+        o = out
+    elif token_major_out:
         B, H, T, D = q.shape
         o = torch.empty((B, T, H, D), dtype=q.dtype, device=q.device).permute(0, 2, 1, 3)
     else:

@@ -431,7 +431,9 @@ int deers_b200_cross_entropy_bwd(deers_ctx* ctx, int64_t rows, int64_t vocab, co
  *                    max_grad_norm (<= 0: no clipping) and the AdamW update; hyper->step is t >= 1.
  *   train_step_host  the same with ids / targets in host memory and the loss read back: copies 16*B*T bytes in,
  *                    4 bytes out and synchronises.
- * Everything is enqueued on the context's stream; only create, param_get and train_step_host synchronise.
+ * Everything is enqueued on the context's stream; only create, param_set, param_get and train_step_host
+ * synchronise.  Graph replay needs a capturable stream: a context on the legacy default stream runs every step
+ * eagerly (same kernels, more launch overhead); deers_b200_gpt_graph_active tells which.
  */
 typedef struct deers_gpt_config {
     int32_t vocab_size, sequence_len, n_layer, n_head, n_embd, mlp_hidden_dim;
@@ -447,6 +449,7 @@ int deers_b200_gpt_param_info(const deers_gpt* model, int index, char* name, siz
 int deers_b200_gpt_param_set(deers_gpt* model, int index, int what, const float* host);
 int deers_b200_gpt_param_get(deers_gpt* model, int index, int what, float* host);
 int deers_b200_gpt_set_graph(deers_gpt* model, int enable);
+int deers_b200_gpt_graph_active(const deers_gpt* model);   /* 1 once a step is being replayed from a captured graph */
 int deers_b200_gpt_forward(deers_gpt* model, const int64_t* ids, int32_t B, int32_t T, float* logits);
 int deers_b200_gpt_forward_backward(deers_gpt* model, const int64_t* ids, const int64_t* targets, int32_t B, int32_t T,
                                     float* loss_dev);
@@ -532,6 +535,18 @@ int deers_b200_kernel_time(deers_ctx* ctx, int kind, int reset, double* total_ms
  */
 enum { DEERS_SELFTEST_CASES = 6 };
 int deers_b200_selftest_umma(deers_ctx* ctx, float* max_abs_err);
+
+/*
+ * Bounded-wait self-test: runs the give-up path of the device-side waits without a fault or a hang.  One small
+ * kernel waits, through the same helper every kernel of the library uses, on a barrier that nothing completes,
+ * with a limit of `limit_ms` (1..1000) milliseconds instead of the usual two seconds.  result (4 ints, host):
+ * [0] 1 if the first wait gave up, [1] 1 if a second wait in the same CTA returned through the abort flag,
+ * [2], [3] the microseconds each of them spent.  The call waits for the kernel but leaves the error word set:
+ * the next deers_b200_sync() returns DEERS_ERR_KERNEL and clears it; until then the persistent f16 kernels,
+ * which read the word when they start, return without writing their outputs.  No counterpart in the
+ * reference (it has no device-side waits).
+ */
+int deers_b200_selftest_wait(deers_ctx* ctx, uint32_t limit_ms, int32_t* result);
 
 #if defined(__GNUC__)
 #pragma GCC visibility pop

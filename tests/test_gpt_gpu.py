@@ -167,8 +167,8 @@ def test_cross_entropy_matches_oracle(rows, V, ld):
     loss, lse, d = gpt.cross_entropy(buf[:, :V], dev(t), with_grad=True)
     torch.cuda.synchronize()
     want_loss, want_lse, want_d = ref.cross_entropy(x, t, with_grad=True)
-    assert abs(loss.item() - want_loss) < 2e-6 * max(1.0, abs(want_loss))
-    assert np.abs(lse.cpu().numpy() - want_lse).max() < 1e-5
+    assert abs(loss.item() - want_loss) < 1e-5 * max(1.0, abs(want_loss))      # differently ordered f32 sums
+    assert np.abs(lse.cpu().numpy() - want_lse).max() < 1e-5 * max(1.0, np.abs(want_lse).max())
     assert rel(d.cpu().numpy(), want_d) < 1e-5
 
 
@@ -260,6 +260,7 @@ def test_gpt_cfg3_training_steps_follow_oracle(cfg3_case):
         for p, g, (m1, v1) in zip(w, r["grads"], mom):
             ref.adamw_step(p, g, m1, v1, step, lr, weight_decay=wd)
     m.ctx.sync()
+    assert m.graph_active(), "steps 3 and 4 are replayed from the captured graph"
     assert np.abs(np.array(losses) - np.array(want_losses)).max() < 1e-3, (losses, want_losses)
     assert np.abs(np.array(norms) - np.array(want_norms)).max() < 1e-3 * max(want_norms), (norms, want_norms)
     assert losses[-1] < losses[0], "the loss goes down on a repeated batch"
