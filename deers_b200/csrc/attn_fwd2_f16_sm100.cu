@@ -13,11 +13,14 @@
 //                 and all 128 key columns of a step, so the row maximum and the row sum are plain loops in
 //                 registers: no exchange between threads.  P (f16 pairs) goes back into TMEM over the scores.
 //                 O is rescaled (by the same threads, in TMEM) only when a row's maximum grew by more than 2^8.
-//   warps 12-15   epilogue: when a tile's last product has landed, read O from TMEM, normalise by the row
-//                 sum, convert, store, write the row lse.  The softmax threads go straight on to the next item.
-//   warps 2-3     idle (they complete the first warpgroup: register quotas are set per warpgroup)
+//                 When a tile's last product has landed, the same threads read O from TMEM, normalise by the row
+//                 sum, convert, store and write the row lse; with the causal mask tile A does this while tile B
+//                 runs its extra (diagonal) step, and tile B while tile A already works on the next item.
+//   warps 2-3     idle (they keep the softmax warps on TMEM lane quadrants 0-3: a warp reaches lanes 32*(warp%4)...)
 // TMEM: S_A | S_B | O_A | O_B, 128 columns each (O: head_dim columns).  Scale, causal mask, softmax and both
 // products happen in this one pass; the T x T scores never reach global memory.
+#include <type_traits>
+
 #include "sm100_ptx.cuh"
 #include "tma_host.cuh"
 
@@ -30,7 +33,7 @@ constexpr uint32_t BLOCK_BYTES = 128 * 128;   // one 64-column block of a 128-ro
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
 constexpr float RESCALE_THRESHOLD = 8.0f;     // log2 units: P stays below 2^8, safe in f16
-constexpr int FWD2_THREADS = 512;
+constexpr int FWD2_THREADS = 384;
 
 struct Fwd2Params {
     __half* o;
@@ -50,11 +53,6 @@ __device__ __forceinline__ float ex2f(float x) {
     return y;
 }
 
-template <int N>
-__device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
-template <int N>
-__device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
-
 template <int D>
 struct Fwd2Smem {
     static constexpr uint32_t TILE = 128u * D * 2u;
@@ -63,14 +61,13 @@ struct Fwd2Smem {
     static constexpr uint32_t Q = 0;                         // Q_A, Q_B
     static constexpr uint32_t K = Q + 2 * TILE;
     static constexpr uint32_t V = K + KS * TILE;
-    static constexpr uint32_t STAT = V + VS * TILE;          // [2 tiles][2: m, l][128] floats
-    static constexpr uint32_t BARS = STAT + 2 * 2 * BM * 4;
+    static constexpr uint32_t BARS = V + VS * TILE;
     static constexpr uint32_t TOTAL = BARS + 320;
 };
 
 // per-tile barriers come in pairs (index + tile)
 enum Fwd2Bar { G_Q_FULL = 0, G_Q_EMPTY = 2, G_S_FULL = 4, G_P_FULL = 6, G_PV_DONE = 8, G_O_DONE = 10, G_O_FREE = 12,
-               G_ST_FULL = 14, G_ST_FREE = 16, G_K_FULL = 18, G_K_EMPTY = 21, G_V_FULL = 24, G_V_EMPTY = 27, G_COUNT = 30 };
+               G_K_FULL = 14, G_K_EMPTY = 17, G_V_FULL = 20, G_V_EMPTY = 23, G_COUNT = 26 };
 
 // One work item as every role sees it.
 struct Item2 {
@@ -92,6 +89,18 @@ __device__ __forceinline__ int4 table2(const Fwd2Params& p, int idx, int nq2, in
     return make_int4(within / gsize, s, s / p.H, s % p.H);
 }
 
+__device__ __forceinline__ Item2 decode2(const Fwd2Params& p, int4 e, int nq, int nq2);
+
+// This CTA's item list, one entry ahead: the table read for item n+1 (an L2 round trip) is issued when item n
+// becomes current and not looked at before the next advance.
+struct Cursor2 {
+    int n;
+    int4 e_next;
+    Item2 it;
+    __device__ __forceinline__ void init(const Fwd2Params& p, int nq, int nq2, int n_items);
+    __device__ __forceinline__ void advance(const Fwd2Params& p, int nq, int nq2, int n_items);
+};
+
 __device__ __forceinline__ Item2 decode2(const Fwd2Params& p, int4 e, int nq, int nq2) {
     Item2 it;
     it.valid = e.x >= 0;
@@ -102,6 +111,17 @@ __device__ __forceinline__ Item2 decode2(const Fwd2Params& p, int4 e, int nq, in
     it.ntB = it.hasB ? (p.causal ? 2 * it.qt2 + 2 : nq) : 0;
     it.nt = it.ntA > it.ntB ? it.ntA : it.ntB;
     return it;
+}
+
+__device__ __forceinline__ void Cursor2::init(const Fwd2Params& p, int nq, int nq2, int n_items) {
+    n = 0;
+    it = decode2(p, table2(p, 0, nq2, n_items), nq, nq2);
+    e_next = table2(p, 1, nq2, n_items);
+}
+__device__ __forceinline__ void Cursor2::advance(const Fwd2Params& p, int nq, int nq2, int n_items) {
+    it = decode2(p, e_next, nq, nq2);
+    ++n;
+    e_next = table2(p, n + 1, nq2, n_items);
 }
 
 template <int D>
@@ -119,7 +139,6 @@ attn_fwd2_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     uint8_t* sQ = smem + L::Q;
     uint8_t* sK = smem + L::K;
     uint8_t* sV = smem + L::V;
-    float* stat = reinterpret_cast<float*>(smem + L::STAT);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BARS);
     uint32_t* tmem_base_s = reinterpret_cast<uint32_t*>(bars + G_COUNT);
     volatile uint32_t* abort_s = tmem_base_s + 1;
@@ -143,7 +162,6 @@ attn_fwd2_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
             mbar_init(&bars[G_S_FULL + x], 1); mbar_init(&bars[G_P_FULL + x], 128);
             mbar_init(&bars[G_PV_DONE + x], 1);
             mbar_init(&bars[G_O_DONE + x], 1); mbar_init(&bars[G_O_FREE + x], 128);
-            mbar_init(&bars[G_ST_FULL + x], 128); mbar_init(&bars[G_ST_FREE + x], 128);
         }
         for (int s = 0; s < 3; ++s) {
             mbar_init(&bars[G_K_FULL + s], 1); mbar_init(&bars[G_K_EMPTY + s], 1);
@@ -165,14 +183,14 @@ attn_fwd2_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     WaitState ws{abort_s, p.err};
 
     if (warp < 4) {
-        reg_dec<80>();
         if (warp == 0 && lane == 0) {
             // ------------------------------ TMA producer ------------------------------
             uint32_t gk = 0, gv = 0, useB = 0;
             bool ok = true;
-            int n = 0;
-            for (Item2 it = decode2(p, table2(p, 0, nq2, n_items), nq, nq2); ok && it.valid;
-                 ++n, it = decode2(p, table2(p, n, nq2, n_items), nq, nq2)) {
+            Cursor2 c;
+            for (c.init(p, nq, nq2, n_items); ok && c.it.valid; c.advance(p, nq, nq2, n_items)) {
+                const Item2& it = c.it;
+                const int n = c.n;
                 if (!mbar_wait(ws, &bars[G_Q_EMPTY + 0], ((uint32_t)n & 1u) ^ 1u, DEERS_KERR_FWD_F16 | 0x41)) break;
                 mbar_arrive_expect_tx(&bars[G_Q_FULL + 0], TILE_BYTES);
 #pragma unroll
@@ -241,9 +259,11 @@ attn_fwd2_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
 
             int n = 0;
             Item2 cur = decode2(p, table2(p, 0, nq2, n_items), nq, nq2);
+            int4 e_nxt = table2(p, 1, nq2, n_items);
             bool pre = false;                        // the first S of `cur` went out during the previous item's last step
             while (ok && cur.valid) {
-                const Item2 nxt = decode2(p, table2(p, n + 1, nq2, n_items), nq, nq2);
+                const Item2 nxt = decode2(p, e_nxt, nq, nq2);
+                e_nxt = table2(p, n + 2, nq2, n_items);          // looked at one item from now
                 if (!pre) {
                     // ---- first S of the item (only the very first item of this CTA comes this way)
                     const uint32_t sk = gk % (uint32_t)KS;
@@ -319,9 +339,8 @@ attn_fwd2_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
                 ++n;
             }
         }
-    } else if (warp < 12) {
-        // ------------------------------ softmax of tile x ------------------------------
-        reg_inc<168>();
+    } else {
+        // ------------------------------ softmax and epilogue of tile x ------------------------------
         const int x = (warp - 4) >> 2;                          // 0: tile A, 1: tile B
         const int lane_base = (warp & 3) * 32;
         const int row = lane_base + lane;                       // row inside the query tile == TMEM lane
@@ -331,9 +350,9 @@ attn_fwd2_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         const uint32_t to = tmem + TM_O + (uint32_t)x * D + t_lane;
         uint32_t cnt = 0, use = 0;
         bool alive = true;
-        int n = 0;
-        for (Item2 it = decode2(p, table2(p, 0, nq2, n_items), nq, nq2); alive && it.valid;
-             ++n, it = decode2(p, table2(p, n, nq2, n_items), nq, nq2)) {
+        Cursor2 c;
+        for (c.init(p, nq, nq2, n_items); alive && c.it.valid; c.advance(p, nq, nq2, n_items)) {
+            const Item2& it = c.it;
             if (x == 1 && !it.hasB) continue;
             const int qt = 2 * it.qt2 + x;
             const int ntiles = x ? it.ntB : it.ntA;
@@ -341,37 +360,61 @@ attn_fwd2_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
             for (int j = 0; j < ntiles; ++j, ++cnt) {
                 if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[G_S_FULL + x], cnt & 1u, DEERS_KERR_FWD_F16 | 0x61))) { alive = false; break; }
                 tc_fence_after_sync();
-                float s[BN];
-#pragma unroll
-                for (int cc = 0; cc < BN / 32; ++cc) tmem_ld_x32(ts + cc * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[cc * 32]));
-                tmem_wait_ld();
-                // Steps that touch the diagonal or the end of the sequence are scaled here and masked with -inf;
-                // all others keep raw scores and fold the scale into the exponent's FFMA.
+                // Two sweeps over the row's 128 scores, 32 columns at a time (the next chunk's TMEM load is in
+                // flight while this one is worked on): the row maximum first, then exponentials, row sum and P.
+                // Reading the scores twice keeps a thread at a few dozen live registers instead of 128 + 64.
+                // Steps that touch the diagonal or the end of the sequence mask with -inf (columns beyond `lim`);
+                // the scale is folded into the exponent's FFMA.
                 const int k0 = j * BN;
-                const bool edge = (p.causal && j == qt) || (k0 + BN > p.T);
-                float c1 = sl2;
-                if (edge) {
-                    int lim = p.T - 1 - k0;                     // keys end at T
-                    if (p.causal && j == qt) lim = min(lim, row);   // diagonal tile (k0 == q0): key <= query
+                int lim = BN - 1;
+                if (k0 + BN > p.T) lim = p.T - 1 - k0;              // keys end at T
+                if (p.causal && j == qt) lim = min(lim, row);       // diagonal tile (k0 == q0): key <= query
+                const bool pos = sl2 >= 0.f;
+                const bool edge = lim < BN - 1;                     // warp-uniform on all but the diagonal tile
+                const bool warp_edge = __any_sync(0xffffffffu, edge);
+                float mx;
+                auto sweep_max = [&](auto mask_tag) {
+                    constexpr bool MASK = decltype(mask_tag)::value;
+                    uint32_t a[32], b[32];
+                    float m0 = pos ? -INFINITY : INFINITY, m1 = m0, m2 = m0, m3 = m0;
+                    tmem_ld_x32(ts, a);
+                    tmem_wait_ld();
 #pragma unroll
-                    for (int i = 0; i < BN; ++i) s[i] = (i > lim) ? -INFINITY : s[i] * sl2;
-                    c1 = 1.0f;
-                }
-                float mx0 = s[0], mx1 = s[1], mx2 = s[2], mx3 = s[3];
-                if (c1 >= 0.f) {
+                    for (int ch = 0; ch < BN / 32; ch += 2) {
+                        tmem_ld_x32(ts + (ch + 1) * 32, b);
 #pragma unroll
-                    for (int i = 4; i < BN; i += 4) {
-                        mx0 = fmaxf(mx0, s[i]); mx1 = fmaxf(mx1, s[i + 1]); mx2 = fmaxf(mx2, s[i + 2]); mx3 = fmaxf(mx3, s[i + 3]);
+                        for (int i = 0; i < 32; i += 4) {
+                            const int c0 = ch * 32 + i;
+                            const float v0 = __uint_as_float(a[i]), v1 = __uint_as_float(a[i + 1]);
+                            const float v2 = __uint_as_float(a[i + 2]), v3 = __uint_as_float(a[i + 3]);
+                            if (pos) {
+                                m0 = (!MASK || c0 <= lim) ? fmaxf(m0, v0) : m0; m1 = (!MASK || c0 + 1 <= lim) ? fmaxf(m1, v1) : m1;
+                                m2 = (!MASK || c0 + 2 <= lim) ? fmaxf(m2, v2) : m2; m3 = (!MASK || c0 + 3 <= lim) ? fmaxf(m3, v3) : m3;
+                            } else {
+                                m0 = (!MASK || c0 <= lim) ? fminf(m0, v0) : m0; m1 = (!MASK || c0 + 1 <= lim) ? fminf(m1, v1) : m1;
+                                m2 = (!MASK || c0 + 2 <= lim) ? fminf(m2, v2) : m2; m3 = (!MASK || c0 + 3 <= lim) ? fminf(m3, v3) : m3;
+                            }
+                        }
+                        tmem_wait_ld();
+                        if (ch + 2 < BN / 32) tmem_ld_x32(ts + (ch + 2) * 32, a);
+#pragma unroll
+                        for (int i = 0; i < 32; i += 4) {
+                            const int c0 = (ch + 1) * 32 + i;
+                            const float v0 = __uint_as_float(b[i]), v1 = __uint_as_float(b[i + 1]);
+                            const float v2 = __uint_as_float(b[i + 2]), v3 = __uint_as_float(b[i + 3]);
+                            if (pos) {
+                                m0 = (!MASK || c0 <= lim) ? fmaxf(m0, v0) : m0; m1 = (!MASK || c0 + 1 <= lim) ? fmaxf(m1, v1) : m1;
+                                m2 = (!MASK || c0 + 2 <= lim) ? fmaxf(m2, v2) : m2; m3 = (!MASK || c0 + 3 <= lim) ? fmaxf(m3, v3) : m3;
+                            } else {
+                                m0 = (!MASK || c0 <= lim) ? fminf(m0, v0) : m0; m1 = (!MASK || c0 + 1 <= lim) ? fminf(m1, v1) : m1;
+                                m2 = (!MASK || c0 + 2 <= lim) ? fminf(m2, v2) : m2; m3 = (!MASK || c0 + 3 <= lim) ? fminf(m3, v3) : m3;
+                            }
+                        }
+                        if (ch + 2 < BN / 32) tmem_wait_ld();
                     }
-                    mx0 = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-                } else {
-#pragma unroll
-                    for (int i = 4; i < BN; i += 4) {
-                        mx0 = fminf(mx0, s[i]); mx1 = fminf(mx1, s[i + 1]); mx2 = fminf(mx2, s[i + 2]); mx3 = fminf(mx3, s[i + 3]);
-                    }
-                    mx0 = fminf(fminf(mx0, mx1), fminf(mx2, mx3));
-                }
-                const float mx = mx0 * c1;
+                    mx = (pos ? fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)) : fminf(fminf(m0, m1), fminf(m2, m3))) * sl2;
+                };
+                if (warp_edge) sweep_max(std::true_type{}); else sweep_max(std::false_type{});
                 const float m_new = fmaxf(m_used, mx);
                 // Lazy rescale: keep the old reference max unless this row grew by more than 2^8.
                 const bool grow = (j > 0) && (m_new - m_used > RESCALE_THRESHOLD);
@@ -379,19 +422,6 @@ attn_fwd2_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
                 const float m_safe = (m_cur == -INFINITY) ? 0.f : m_cur;
                 const float alpha = (j == 0) ? 0.f : ex2f(m_used - m_safe);
                 const bool warp_grow = __any_sync(0xffffffffu, grow);
-
-                uint32_t pk[BN / 2];
-                float rs0 = 0.f, rs1 = 0.f;
-#pragma unroll
-                for (int i = 0; i < BN / 2; ++i) {
-                    const float e0 = ex2f(fmaf(s[2 * i], c1, -m_safe));
-                    const float e1 = ex2f(fmaf(s[2 * i + 1], c1, -m_safe));
-                    rs0 += e0; rs1 += e1;
-                    pk[i] = pack_half2(e0, e1);
-                }
-                l = l * alpha + (rs0 + rs1);
-                m_used = m_cur;
-
                 if (j > 0 && warp_grow) {
                     // O += P V of the previous step must have landed before O is rescaled.
                     if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[G_PV_DONE + x], (cnt - 1u) & 1u, DEERS_KERR_FWD_F16 | 0x62))) { alive = false; break; }
@@ -406,71 +436,88 @@ attn_fwd2_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
                         tmem_st_x32(to + cc * 32, r);
                     }
                 }
-                // P replaces the first 64 columns of this tile's S in TMEM.
-                tmem_st_x32(ts, *reinterpret_cast<uint32_t(*)[32]>(&pk[0]));
-                tmem_st_x32(ts + 32, *reinterpret_cast<uint32_t(*)[32]>(&pk[32]));
+                // Second sweep.  P (f16 pairs) replaces the first 64 columns of this tile's S, sixteen packed columns
+                // per chunk: a chunk of P lands on score columns that have already been read.
+                float rs0 = 0.f, rs1 = 0.f;
+                auto sweep_exp = [&](auto mask_tag) {
+                    constexpr bool MASK = decltype(mask_tag)::value;
+                    uint32_t a[32], b[32];
+                    tmem_ld_x32(ts, a);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int ch = 0; ch < BN / 32; ch += 2) {
+                        tmem_ld_x32(ts + (ch + 1) * 32, b);
+                        uint32_t pk[16];
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            const int c0 = ch * 32 + 2 * i;
+                            float e0 = ex2f(fmaf(__uint_as_float(a[2 * i]), sl2, -m_safe));
+                            float e1 = ex2f(fmaf(__uint_as_float(a[2 * i + 1]), sl2, -m_safe));
+                            if (MASK) {
+                                e0 = (c0 <= lim) ? e0 : 0.f;
+                                e1 = (c0 + 1 <= lim) ? e1 : 0.f;
+                            }
+                            rs0 += e0; rs1 += e1;
+                            pk[i] = pack_half2(e0, e1);
+                        }
+                        tmem_wait_ld();                              // chunk ch+1 is in registers
+                        tmem_st_x16(ts + ch * 16, pk);
+                        if (ch + 2 < BN / 32) tmem_ld_x32(ts + (ch + 2) * 32, a);
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            const int c0 = (ch + 1) * 32 + 2 * i;
+                            float e0 = ex2f(fmaf(__uint_as_float(b[2 * i]), sl2, -m_safe));
+                            float e1 = ex2f(fmaf(__uint_as_float(b[2 * i + 1]), sl2, -m_safe));
+                            if (MASK) {
+                                e0 = (c0 <= lim) ? e0 : 0.f;
+                                e1 = (c0 + 1 <= lim) ? e1 : 0.f;
+                            }
+                            rs0 += e0; rs1 += e1;
+                            pk[i] = pack_half2(e0, e1);
+                        }
+                        if (ch + 2 < BN / 32) tmem_wait_ld();        // chunk ch+2 is in registers: its columns may be overwritten later
+                        tmem_st_x16(ts + (ch + 1) * 16, pk);
+                    }
+                };
+                if (warp_edge) sweep_exp(std::true_type{}); else sweep_exp(std::false_type{});
+                l = l * alpha + (rs0 + rs1);
+                m_used = m_cur;
                 tmem_wait_st();
                 tc_fence_before_sync();
                 mbar_arrive(&bars[G_P_FULL + x]);
             }
             if (!alive) break;
-            // hand the row statistics to the epilogue warps and go on with the next item
-            if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[G_ST_FREE + x], (use & 1u) ^ 1u, DEERS_KERR_FWD_F16 | 0x63))) { alive = false; break; }
-            stat[(x * 2 + 0) * BM + row] = m_used;
-            stat[(x * 2 + 1) * BM + row] = l;
-            mbar_arrive(&bars[G_ST_FULL + x]);
+            // ---- epilogue of this tile: its last product has been issued right after the hand-over above
+            if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[G_O_DONE + x], use & 1u, DEERS_KERR_FWD_F16 | 0x72))) { alive = false; break; }
+            tc_fence_after_sync();
             ++use;
-        }
-    } else {
-        // ------------------------------ epilogue ------------------------------
-        reg_dec<96>();
-        const int lane_base = (warp & 3) * 32;
-        const int row = lane_base + lane;
-        const uint32_t t_lane = (uint32_t)lane_base << 16;
-        uint32_t use[2] = {0, 0};
-        bool alive = true;
-        int n = 0;
-        for (Item2 it = decode2(p, table2(p, 0, nq2, n_items), nq, nq2); alive && it.valid;
-             ++n, it = decode2(p, table2(p, n, nq2, n_items), nq, nq2)) {
-            for (int x = 0; x < 2 && alive; ++x) {
-                if (x == 1 && !it.hasB) continue;
-                if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[G_ST_FULL + x], use[x] & 1u, DEERS_KERR_FWD_F16 | 0x71))) { alive = false; break; }
-                const float m = stat[(x * 2 + 0) * BM + row];
-                const float l = stat[(x * 2 + 1) * BM + row];
-                mbar_arrive(&bars[G_ST_FREE + x]);
-                if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[G_O_DONE + x], use[x] & 1u, DEERS_KERR_FWD_F16 | 0x72))) { alive = false; break; }
-                tc_fence_after_sync();
-                ++use[x];
-                const float inv = 1.f / l;
-                const int q0 = (2 * it.qt2 + x) * BM;
-                const int grow_row = q0 + row;
-                // The thread's row of O, 64 columns at a time, as 16-byte pieces transposed within 8-lane groups so
-                // that every store instruction writes whole 128-byte row segments.
-                const int grow0 = q0 + lane_base + (lane & ~7);
-                __half* ob = p.o + it.b * p.so_b + it.h * p.so_h + (lane & 7) * 8;
+            const float inv = 1.f / l;
+            const int q0 = qt * BM;
+            // The thread's row of O, 64 columns at a time, as 16-byte pieces transposed within 8-lane groups so
+            // that every store instruction writes whole 128-byte row segments.
+            const int grow0 = q0 + lane_base + (lane & ~7);
+            __half* ob = p.o + it.b * p.so_b + it.h * p.so_h + (lane & 7) * 8;
 #pragma unroll 1
-                for (int part = 0; part < D / 64; ++part) {
-                    uint32_t r[64];
-                    uint4 pc[8];
-                    const uint32_t to = tmem + TM_O + (uint32_t)x * D + t_lane + part * 64;
-                    tmem_ld_x32(to, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
-                    tmem_ld_x32(to + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
-                    tmem_wait_ld();
-                    if (part == D / 64 - 1) {                    // the accumulator is in registers: release it
-                        tc_fence_before_sync();
-                        mbar_arrive(&bars[G_O_FREE + x]);
-                    }
-#pragma unroll
-                    for (int q8 = 0; q8 < 8; ++q8) pc[q8] = pack8_f16(r + q8 * 8, inv);
-                    transpose_pieces<8>(pc, (uint32_t)lane);
-#pragma unroll
-                    for (int c = 0; c < 8; ++c) {
-                        const int grow = grow0 + c;
-                        if (grow < p.T) *reinterpret_cast<uint4*>(ob + (long long)grow * p.so_t + part * 64) = pc[c];
-                    }
+            for (int part = 0; part < D / 64; ++part) {
+                uint32_t r[64];
+                uint4 pc[8];
+                tmem_ld_x32(to + part * 64, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+                tmem_ld_x32(to + part * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+                tmem_wait_ld();
+                if (part == D / 64 - 1) {                        // the accumulator is in registers: release it
+                    tc_fence_before_sync();
+                    mbar_arrive(&bars[G_O_FREE + x]);
                 }
-                if (grow_row < p.T) p.lse[(long long)it.bh * p.T + grow_row] = (m + log2f(l)) * LN2;
+#pragma unroll
+                for (int q8 = 0; q8 < 8; ++q8) pc[q8] = pack8_f16(r + q8 * 8, inv);
+                transpose_pieces<8>(pc, (uint32_t)lane);
+#pragma unroll
+                for (int cc = 0; cc < 8; ++cc) {
+                    const int grow = grow0 + cc;
+                    if (grow < p.T) *reinterpret_cast<uint4*>(ob + (long long)grow * p.so_t + part * 64) = pc[cc];
+                }
             }
+            if (q0 + row < p.T) p.lse[(long long)it.bh * p.T + q0 + row] = (m_used + log2f(l)) * LN2;
         }
     }
 

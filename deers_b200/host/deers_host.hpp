@@ -12,6 +12,9 @@
 //   Error::{LayoutMismatch, DTypeMismatch, DeviceMismatch, Cuda}   src/error.rs:8-42
 //   Device::synchronize                                   src/device.rs:66-72
 //
+//   GPTConfig / GPT {forward, parameters} and the trainer's step     src/models/gpt.rs:259-378,
+//                                                         examples/tinystories_train.rs:188-218
+//
 // Header-only, C++17; link with libdeers_b200.so.  There is no CPU fallback.
 #pragma once
 #include <cmath>
@@ -404,5 +407,88 @@ inline GradientStore backward(const Tensor& out, const Tensor& out_grad) {
     if (out.op()) out.op()->backward(grads, out_grad);
     return grads;
 }
+
+// GPTConfig (src/models/gpt.rs:259-285) and the model as one device-resident object: GPT::forward
+// (gpt.rs:329-355) and one step of the trainer loop (tinystories_train.rs:188-218: forward, cross_entropy,
+// backward, clip_grad_norm, AdamW::step_with_grads).  Parameters are addressed by index in the order of
+// GPT::parameters (gpt.rs:358-365).
+struct GPTConfig {
+    int vocab_size, sequence_len, n_layer, n_head, n_embd, mlp_hidden_dim;
+    double rms_norm_eps = 1e-5;
+    float rope_base = 10000.f;
+};
+
+class GPT {
+public:
+    GPT(const GPTConfig& cfg, int max_batch, int device = 0) : rt_(Runtime::get(device)), cfg_(cfg), model_(nullptr) {
+        deers_gpt_config c{cfg.vocab_size, cfg.sequence_len, cfg.n_layer, cfg.n_head, cfg.n_embd, cfg.mlp_hidden_dim,
+                           cfg.rms_norm_eps, cfg.rope_base};
+        rt_.check(deers_b200_gpt_create(rt_.ctx(), &c, max_batch, &model_));
+    }
+    ~GPT() { deers_b200_gpt_destroy(model_); }
+    GPT(const GPT&) = delete;
+    GPT& operator=(const GPT&) = delete;
+
+    int num_parameters() const { return deers_b200_gpt_num_params(model_); }
+    std::pair<std::string, std::pair<int64_t, int64_t>> parameter_info(int index) const {
+        char name[96];
+        int64_t rows = 0, cols = 0;
+        rt_.check(deers_b200_gpt_param_info(model_, index, name, sizeof(name), &rows, &cols));
+        return {name, {rows, cols}};
+    }
+    void load_parameter(int index, const std::vector<float>& host) {
+        const auto shape = parameter_info(index).second;
+        if ((int64_t)host.size() != shape.first * shape.second)
+            throw Error(Error::Kind::LayoutMismatch, "GPT::load_parameter: wrong element count for " + parameter_info(index).first);
+        rt_.check(deers_b200_gpt_param_set(model_, index, 0, host.data()));
+    }
+    std::vector<float> read(int index, int what) const {        // 0 weight, 1 gradient, 2 / 3 AdamW moments
+        const auto shape = parameter_info(index).second;
+        std::vector<float> host((size_t)(shape.first * shape.second));
+        rt_.check(deers_b200_gpt_param_get(model_, index, what, host.data()));
+        return host;
+    }
+    // ids: B*T token ids on the host (the trainer's sample_batch + from_vec); returns logits [B*T, vocab].
+    std::vector<float> forward(const std::vector<int64_t>& ids, int B, int T) {
+        DeviceBuffer d_ids(rt_, ids.size() * sizeof(int64_t)), d_logits(rt_, (size_t)B * T * cfg_.vocab_size * sizeof(float));
+        rt_.check(deers_b200_memcpy_h2d(rt_.ctx(), d_ids.ptr, ids.data(), ids.size() * sizeof(int64_t)));
+        rt_.check(deers_b200_gpt_forward(model_, (const int64_t*)d_ids.ptr, B, T, (float*)d_logits.ptr));
+        std::vector<float> logits((size_t)B * T * cfg_.vocab_size);
+        rt_.check(deers_b200_memcpy_d2h(rt_.ctx(), logits.data(), d_logits.ptr, logits.size() * sizeof(float)));
+        return logits;
+    }
+    // forward + cross_entropy + backward; returns the loss, gradients are read with read(index, 1).
+    float forward_backward(const std::vector<int64_t>& ids, const std::vector<int64_t>& targets, int B, int T) {
+        DeviceBuffer d_ids(rt_, ids.size() * sizeof(int64_t)), d_tgt(rt_, targets.size() * sizeof(int64_t)), d_loss(rt_, 4);
+        rt_.check(deers_b200_memcpy_h2d(rt_.ctx(), d_ids.ptr, ids.data(), ids.size() * sizeof(int64_t)));
+        rt_.check(deers_b200_memcpy_h2d(rt_.ctx(), d_tgt.ptr, targets.data(), targets.size() * sizeof(int64_t)));
+        rt_.check(deers_b200_gpt_forward_backward(model_, (const int64_t*)d_ids.ptr, (const int64_t*)d_tgt.ptr, B, T, (float*)d_loss.ptr));
+        float loss = 0.f;
+        rt_.check(deers_b200_memcpy_d2h(rt_.ctx(), &loss, d_loss.ptr, 4));
+        return loss;
+    }
+    // One optimizer step on host ids; returns {loss, gradient norm before clipping}.
+    std::pair<float, float> train_step(const std::vector<int64_t>& ids, const std::vector<int64_t>& targets, int B, int T,
+                                       double lr, double beta1 = 0.9, double beta2 = 0.999, double eps = 1e-8,
+                                       double weight_decay = 0.0, double max_grad_norm = 0.0) {
+        deers_adamw_hyper h{lr, beta1, beta2, eps, weight_decay, ++step_};
+        float loss = 0.f, norm = 0.f;
+        rt_.check(deers_b200_gpt_train_step_host(model_, ids.data(), targets.data(), B, T, &h, max_grad_norm, &loss, &norm));
+        return {loss, norm};
+    }
+    int64_t step_count() const { return step_; }
+
+private:
+    struct DeviceBuffer {
+        Runtime& rt;
+        void* ptr = nullptr;
+        DeviceBuffer(Runtime& r, size_t bytes) : rt(r) { rt.check(deers_b200_alloc(rt.ctx(), bytes, &ptr)); }
+        ~DeviceBuffer() { deers_b200_free(rt.ctx(), ptr); }
+    };
+    Runtime& rt_;
+    GPTConfig cfg_;
+    deers_gpt* model_;
+    int64_t step_ = 0;
+};
 
 }  // namespace deers

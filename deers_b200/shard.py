@@ -119,10 +119,9 @@ class PeerGather:
         L = _lib.lib()
         handle = ctypes.create_string_buffer(_lib.IPC_HANDLE_BYTES)
         _lib.check(L.deers_b200_comm_export(ctx.handle, self.out.data_ptr(), handle), ctx.handle)
-        mine = torch.frombuffer(bytearray(handle.raw), dtype=torch.uint8).to(device)
-        everyone = torch.empty(self.world * _lib.IPC_HANDLE_BYTES, dtype=torch.uint8, device=device)
-        dist.all_gather_into_tensor(everyone, mine, group=group)
-        blob = bytes(everyone.cpu().numpy().tobytes())
+        everyone = [None] * self.world                       # any backend: the handles are 72 opaque bytes each
+        dist.all_gather_object(everyone, bytes(handle.raw), group=group)
+        blob = b"".join(everyone)
         self.handle = ctypes.c_void_p()
         _lib.check(L.deers_b200_comm_init_ipc(ctx.handle, self.rank, self.world, self.out.data_ptr(),
                                               self.out.numel() * self.out.element_size(), blob,

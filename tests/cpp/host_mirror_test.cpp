@@ -140,10 +140,61 @@ static int run_other_ops() {
     return fails;
 }
 
+// The reference's model test (tests/gpt.rs:38-66: vocab 8, 1 layer, 2 heads, n_embd 4, mlp 8, B=2, T=3, its token
+// ids) through deers::GPT, against the C oracle's step: logits, loss, every parameter gradient (2e-3, the
+// reference's accelerator tolerance), then one optimizer step.
+extern "C" int ref_gpt_step(const int* cfg, double eps, float rope_base, int B, int T, const long long* ids,
+                            const long long* targets, const float* const* params, float* logits_out, float* loss_out,
+                            float* const* grads);
+
+static int run_gpt() {
+    int fails = 0;
+    const int V = 8, L = 1, H = 2, C = 4, Hm = 8, B = 2, T = 3;
+    deers::GPT model({V, 4, L, H, C, Hm}, B);
+    std::mt19937 rng(77);
+    std::uniform_real_distribution<float> uni(-0.5f, 0.5f);
+    std::vector<std::vector<float>> params, grads;
+    for (int i = 0; i < model.num_parameters(); ++i) {
+        const auto shape = model.parameter_info(i).second;
+        params.emplace_back((size_t)(shape.first * shape.second));
+        for (auto& e : params.back()) e = uni(rng);
+        grads.emplace_back(params.back().size());
+        model.load_parameter(i, params.back());
+    }
+    const std::vector<int64_t> ids = {1, 2, 3, 4, 3, 2}, targets = {2, 3, 4, 3, 2, 1};
+    const std::vector<long long> ids_ll(ids.begin(), ids.end()), tgt_ll(targets.begin(), targets.end());
+    std::vector<const float*> pp;
+    std::vector<float*> gp;
+    for (size_t i = 0; i < params.size(); ++i) { pp.push_back(params[i].data()); gp.push_back(grads[i].data()); }
+    const int cfg[5] = {V, L, H, C, Hm};
+    std::vector<float> want_logits((size_t)B * T * V);
+    float want_loss = 0.f;
+    ref_gpt_step(cfg, 1e-5, 10000.f, B, T, ids_ll.data(), tgt_ll.data(), pp.data(), want_logits.data(), &want_loss, gp.data());
+    const std::vector<float> logits = model.forward(ids, B, T);
+    const float loss = model.forward_backward(ids, targets, B, T);
+    float err = std::fabs(loss - want_loss);
+    for (size_t i = 0; i < logits.size(); ++i) err = std::max(err, std::fabs(logits[i] - want_logits[i]));
+    for (int i = 0; i < model.num_parameters(); ++i) {
+        const std::vector<float> g = model.read(i, 1);
+        for (size_t e = 0; e < g.size(); ++e) err = std::max(err, std::fabs(g[e] - grads[i][e]));
+    }
+    bool ok = err < 2e-3f && model.parameter_info(1).first == "blocks.0.attn.q_proj.weight";
+    std::printf("%s GPT logits / loss / gradients (max abs err %.2e)\n", ok ? "PASS" : "FAIL", err);
+    fails += !ok;
+    const auto step = model.train_step(ids, targets, B, T, 1e-2, 0.9, 0.999, 1e-8, 0.1, 1.0);
+    const float loss2 = model.forward_backward(ids, targets, B, T);
+    ok = std::fabs(step.first - want_loss) < 2e-3f && std::isfinite(step.second) && loss2 < step.first;
+    std::printf("%s GPT training step lowers the loss (%.4f -> %.4f, grad norm %.4f)\n", ok ? "PASS" : "FAIL", step.first, loss2,
+                step.second);
+    fails += !ok;
+    return fails;
+}
+
 int main() {
     int fails = 0;
     try {
         fails += run_other_ops();
+        fails += run_gpt();
         fails += run_case(deers::DType::F32, 2, 3, 96, 32, 1e-4f);
         fails += run_case(deers::DType::F16, 2, 2, 300, 128, 2e-2f);
         fails += run_case(deers::DType::F16, 1, 3, 200, 64, 2e-2f);

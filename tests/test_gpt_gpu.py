@@ -169,7 +169,9 @@ def test_cross_entropy_matches_oracle(rows, V, ld):
     want_loss, want_lse, want_d = ref.cross_entropy(x, t, with_grad=True)
     assert abs(loss.item() - want_loss) < 1e-5 * max(1.0, abs(want_loss))      # differently ordered f32 sums
     assert np.abs(lse.cpu().numpy() - want_lse).max() < 1e-5 * max(1.0, np.abs(want_lse).max())
-    assert rel(d.cpu().numpy(), want_d) < 1e-5
+    # the oracle sums 50257 exponentials left to right in f32 (as the reference does), the kernel in a tree:
+    # the row lse differs by a few 1e-6, and so does every probability
+    assert rel(d.cpu().numpy(), want_d) < 1e-4
 
 
 # ---- the model ------------------------------------------------------------------------------------------

@@ -33,4 +33,4 @@ def test_host_mirror_matches_oracle_on_gpu():
     out = subprocess.run([build_binary()], capture_output=True, text=True, timeout=300)
     print(out.stdout, out.stderr)
     assert out.returncode == 0, out.stdout + out.stderr
-    assert out.stdout.count("PASS") == 7 and "FAIL" not in out.stdout
+    assert out.stdout.count("PASS") == 9 and "FAIL" not in out.stdout
