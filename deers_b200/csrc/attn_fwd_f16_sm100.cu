@@ -481,9 +481,6 @@ int fwd_launch(deers_ctx* ctx, const deers_attn_desc* d, const void* q, const vo
 
 int launch_attn_fwd_f16(deers_ctx* ctx, const deers_attn_desc* d, const void* q, const void* k, const void* v,
                         void* o, float* lse) {
-    // Sequences of more than two query tiles take the kernel that keeps two query tiles per CTA in flight
-    // (attn_fwd2_f16_sm100.cu); shorter ones keep 128-row work items, which spread better over the SMs.
-    if (d->T > 2 * BM) return launch_attn_fwd2_f16(ctx, d, q, k, v, o, lse);
     if (d->D == 64) return fwd_launch<64>(ctx, d, q, k, v, o, lse);
     if (d->D == 128) return fwd_launch<128>(ctx, d, q, k, v, o, lse);
     return DEERS_ERR_UNSUPPORTED;

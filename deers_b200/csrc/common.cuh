@@ -119,8 +119,6 @@ int launch_attn_bwd_f32(deers_ctx* ctx, const deers_attn_desc* d, const float* q
 // f16 tcgen05 path (attn_f16_sm100.cu)
 int launch_attn_fwd_f16(deers_ctx* ctx, const deers_attn_desc* d, const void* q, const void* k,
                         const void* v, void* o, float* lse);
-int launch_attn_fwd2_f16(deers_ctx* ctx, const deers_attn_desc* d, const void* q, const void* k,
-                         const void* v, void* o, float* lse);
 int launch_attn_bwd_f16(deers_ctx* ctx, const deers_attn_desc* d, const void* q, const void* k,
                         const void* v, const void* o, const float* lse, const void* d_o, void* dq,
                         void* dk, void* dv, void* workspace, bool keep_ds);
