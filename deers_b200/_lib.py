@@ -33,10 +33,10 @@ SYMBOLS = [
     "deers_b200_gpt_forward_backward", "deers_b200_gpt_train_step", "deers_b200_gpt_train_step_host",
     "deers_b200_shard_range", "deers_b200_comm_init_all", "deers_b200_comm_export", "deers_b200_comm_init_ipc",
     "deers_b200_comm_destroy", "deers_b200_allgather_o", "deers_b200_allgather_join", "deers_b200_allgather_flush",
-    "deers_b200_selftest_wait",
+    "deers_b200_selftest_wait", "deers_b200_split_f16x3", "deers_b200_gemm_f16x3_workspace_bytes", "deers_b200_gemm_f16x3",
 ]
 IPC_HANDLE_BYTES = 72
-K_FWD, K_BWD_PREP, K_BWD_MAIN, K_BWD_DQ, K_ROPE, K_OPTIM, K_NORM, K_DECODE, K_GEMM, K_GPT = range(10)
+K_FWD, K_BWD_PREP, K_BWD_MAIN, K_BWD_DQ, K_ROPE, K_OPTIM, K_NORM, K_DECODE, K_GEMM, K_GPT, K_GEMM_X3 = range(11)
 EPI_NONE, EPI_ADD, EPI_RELU_SQ, EPI_MUL_AUX2 = range(4)
 
 
@@ -139,6 +139,10 @@ def lib() -> ctypes.CDLL:
     L.deers_b200_gemm_f32_workspace_bytes.restype = sz
     L.deers_b200_gemm_f32.argtypes = [vp, i32, i32, i32, vp, i64, i32, vp, i64, i32, vp, i64,
                                       ctypes.POINTER(GemmEpilogue), vp, sz]
+    L.deers_b200_split_f16x3.argtypes = [vp, i64, ctypes.c_int32, vp, i64, ctypes.c_float, vp, vp, i64]
+    L.deers_b200_gemm_f16x3_workspace_bytes.argtypes = [vp, i32, i32, i32]
+    L.deers_b200_gemm_f16x3_workspace_bytes.restype = sz
+    L.deers_b200_gemm_f16x3.argtypes = [vp, i32, i32, i32, vp, vp, i64, i32, vp, vp, i64, i32, vp, i64, ctypes.c_float, vp, sz]
     L.deers_b200_rmsnorm_bwd_add.argtypes = [vp, i64, ctypes.c_int32, vp, vp, vp, vp, vp]
     L.deers_b200_embedding_fwd.argtypes = [vp, vp, vp, i64, ctypes.c_int32, i64, vp]
     L.deers_b200_embedding_bwd.argtypes = [vp, vp, vp, i64, ctypes.c_int32, i64, vp]

@@ -13,7 +13,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB = os.path.join(LIB_DIR, "libdeers_b200.so")
 SOURCES = ["ctx.cu", "attn_f32.cu", "umma_selftest.cu", "attn_fwd_f16_sm100.cu", "attn_bwd_f16_sm100.cu",
-           "rope_pack.cu", "optim.cu", "rmsnorm.cu", "attn_decode.cu", "gemm_f16_sm100.cu", "gemm_f32.cu",
+           "rope_pack.cu", "optim.cu", "rmsnorm.cu", "attn_decode.cu", "gemm_f16_sm100.cu", "gemm_f16x3_sm100.cu", "gemm_f32.cu",
            "gpt_ops.cu", "gpt_model.cu", "comm.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC,-fvisibility=hidden", "--use_fast_math=false"]

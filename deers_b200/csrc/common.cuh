@@ -147,3 +147,13 @@ int launch_cross_entropy_bwd(deers_ctx* ctx, const float* logits, long long ld, 
 // AdamW with the trainer's rule "no update when the gradient norm is not finite" (optim.cu)
 int launch_adamw(deers_ctx* ctx, int n_tensors, const deers_optim_tensor* tensors, const deers_adamw_hyper* h,
                  const float* norm_dev, double max_norm, bool skip_nonfinite);
+// f32-accurate tensor-core GEMM on split f16 operands (gemm_f16x3_sm100.cu) and the split writers
+size_t gemm_f16x3_workspace_bytes(const deers_ctx* ctx, int M, int N, int K);
+int launch_split_f16x3(deers_ctx* ctx, long long rows, int cols, const float* src, long long ld_src, float scale,
+                       void* hi, void* lo, long long ld_dst);
+int launch_gemm_f16x3(deers_ctx* ctx, int M, int N, int K, const void* a_hi, const void* a_lo, long long lda, int a_mn,
+                      const void* b_hi, const void* b_lo, long long ldb, int b_mn, float* c, long long ldc, float out_scale,
+                      void* workspace, size_t ws_bytes);
+int launch_cross_entropy_bwd_split(deers_ctx* ctx, const float* logits, long long ld, const long long* targets,
+                                   const float* lse, long long rows, long long V, float upstream, float scale, void* hi,
+                                   void* lo, long long ldd);

@@ -55,6 +55,11 @@ struct deers_gpt {
     void* optim_scratch;
     float *loss_dev, *norm_dev;
     long long *ids_dev, *tgt_dev;
+    // The head on the tensor core (gemm_f16x3_sm100.cu): f16 pairs of xf, of the head weight and of dlogits
+    bool tc_head;
+    void *xf_hi, *xf_lo, *w_hi, *w_lo, *dl_hi, *dl_lo;
+    void* x3_ws;
+    size_t x3_ws_bytes;
     // pinned staging for train_step_host
     long long* ids_pin;
     float* out_pin;
@@ -135,7 +140,15 @@ int forward(deers_gpt* m, const long long* ids, int B, int T) {
         x = a.x2;
     }
     GPT_TRY(launch_rmsnorm_fwd(ctx, N, C, c.rms_norm_eps, x, m->xf, m->invf));               // gpt.rs:347
-    GPT_TRY(gemm(m, (int)N, V, C, m->xf, C, 0, W + m->off_lm, m->Vld, 1, m->logits, m->Vld)); // lm_head
+    if (m->tc_head) {
+        // lm_head on the tensor core at f32 accuracy: both operands as f16 pairs (the weight changes every step)
+        GPT_TRY(launch_split_f16x3(ctx, N, C, m->xf, C, 1.0f, m->xf_hi, m->xf_lo, C));
+        GPT_TRY(launch_split_f16x3(ctx, C, V, W + m->off_lm, m->Vld, 1.0f, m->w_hi, m->w_lo, m->Vld));
+        GPT_TRY(launch_gemm_f16x3(ctx, (int)N, V, C, m->xf_hi, m->xf_lo, C, 0, m->w_hi, m->w_lo, m->Vld, 1, m->logits, m->Vld,
+                                  1.0f, m->x3_ws, m->x3_ws_bytes));
+    } else {
+        GPT_TRY(gemm(m, (int)N, V, C, m->xf, C, 0, W + m->off_lm, m->Vld, 1, m->logits, m->Vld)); // lm_head
+    }
     return DEERS_OK;
 }
 
@@ -148,10 +161,20 @@ int loss_and_backward(deers_gpt* m, const long long* ids, const long long* targe
     float* W = m->arena[0];
     float* G = m->arena[1];
     GPT_TRY(launch_cross_entropy_fwd(ctx, m->logits, Vld, targets, N, V, m->ce_lse, m->picked, m->loss_dev));
-    GPT_TRY(launch_cross_entropy_bwd(ctx, m->logits, Vld, targets, m->ce_lse, N, V, 1.0f, m->logits, Vld));
     const float* x_last = c.n_layer ? m->la[c.n_layer - 1].x2 : m->x0;
-    GPT_TRY(gemm(m, C, V, (int)N, m->xf, C, 1, m->logits, Vld, 1, G + m->off_lm, Vld));      // d lm_head = xf^T dlogits
-    GPT_TRY(gemm(m, (int)N, C, V, m->logits, Vld, 0, W + m->off_lm, Vld, 0, m->dtmp, C));    // d xf = dlogits Wlm^T
+    if (m->tc_head) {
+        // dlogits leave the cross-entropy backward as f16 pairs scaled by rows * 4096 (|dlogit| <= 1 / rows)
+        const float dscale = (float)N * 4096.0f;
+        GPT_TRY(launch_cross_entropy_bwd_split(ctx, m->logits, Vld, targets, m->ce_lse, N, V, 1.0f, dscale, m->dl_hi, m->dl_lo, Vld));
+        GPT_TRY(launch_gemm_f16x3(ctx, C, V, (int)N, m->xf_hi, m->xf_lo, C, 1, m->dl_hi, m->dl_lo, Vld, 1, G + m->off_lm, Vld,
+                                  1.0f / dscale, m->x3_ws, m->x3_ws_bytes));                  // d lm_head = xf^T dlogits
+        GPT_TRY(launch_gemm_f16x3(ctx, (int)N, C, V, m->dl_hi, m->dl_lo, Vld, 0, m->w_hi, m->w_lo, Vld, 0, m->dtmp, C,
+                                  1.0f / dscale, m->x3_ws, m->x3_ws_bytes));                  // d xf = dlogits Wlm^T
+    } else {
+        GPT_TRY(launch_cross_entropy_bwd(ctx, m->logits, Vld, targets, m->ce_lse, N, V, 1.0f, m->logits, Vld));
+        GPT_TRY(gemm(m, C, V, (int)N, m->xf, C, 1, m->logits, Vld, 1, G + m->off_lm, Vld));      // d lm_head = xf^T dlogits
+        GPT_TRY(gemm(m, (int)N, C, V, m->logits, Vld, 0, W + m->off_lm, Vld, 0, m->dtmp, C));    // d xf = dlogits Wlm^T
+    }
     GPT_TRY(launch_rmsnorm_bwd(ctx, N, C, x_last, m->invf, m->dtmp, nullptr, m->dx_a));
     deers_attn_desc ad;
     attn_desc(m, B, T, &ad);
@@ -291,7 +314,9 @@ extern "C" int deers_b200_gpt_create(deers_ctx* ctx, const deers_gpt_config* cfg
     deers_gpt* m = new (std::nothrow) deers_gpt();
     if (!m) return DEERS_ERR_CUDA;
     m->ctx = ctx; m->cfg = *cfg; m->max_batch = max_batch; m->max_tokens = max_tokens; m->D = D;
-    m->Vld = (cfg->vocab_size + 3) / 4 * 4;                           // rows of the head and of the logits start 16-byte aligned
+    m->Vld = (cfg->vocab_size + 7) / 8 * 8;                           // rows of the head, of the logits and of their f16 pairs start 16-byte aligned
+    // Heads that fill the tensor core take the split-f16 products; small ones stay on the FFMA kernel.
+    m->tc_head = cfg->vocab_size >= 1024 && cfg->n_embd % 8 == 0 && cfg->n_embd >= 64;
     m->graph_enabled = true; m->graph_exec = nullptr; m->graph_B = m->graph_T = -1; m->eager_steps_BT = 0;
     const size_t C = cfg->n_embd, Hm = cfg->mlp_hidden_dim, V = cfg->vocab_size, N = (size_t)max_tokens;
 
@@ -367,7 +392,13 @@ extern "C" int deers_b200_gpt_create(deers_ctx* ctx, const deers_gpt_config* cfg
     m->gemm_ws_bytes = gws;
     const size_t opt_bytes = deers_b200_optim_scratch_bytes();
     const size_t id_bytes = ((size_t)N * sizeof(long long) + 255) / 256 * 256;
-    const size_t bytes = total * sizeof(float) + gws + 256 + opt_bytes + 256 + 2 * id_bytes;
+    auto up256 = [](size_t b) { return (b + 255) / 256 * 256; };
+    const size_t xf_h = up256(N * C * 2), w_h = up256(C * (size_t)m->Vld * 2), dl_h = up256(N * (size_t)m->Vld * 2);
+    // K-split partial tiles of the head's input gradient: parts * tokens <= 148 * 128 * 128 / C + tokens
+    const size_t x3 = m->tc_head ? up256(((size_t)148 * 16384 + N * C) * sizeof(float) * 2) : 0;
+    m->x3_ws_bytes = x3;
+    const size_t tc_bytes = m->tc_head ? 2 * (xf_h + w_h + dl_h) + x3 : 0;
+    const size_t bytes = total * sizeof(float) + gws + 256 + opt_bytes + 256 + 2 * id_bytes + tc_bytes;
     char* base = nullptr;
     if (!rc && cudaMalloc((void**)&base, bytes) != cudaSuccess) rc = DEERS_ERR_CUDA;
     if (!rc && cudaMemsetAsync(base, 0, bytes, ctx->stream) != cudaSuccess) rc = DEERS_ERR_CUDA;   // split-K counters start at zero
@@ -380,7 +411,13 @@ extern "C" int deers_b200_gpt_create(deers_ctx* ctx, const deers_gpt_config* cfg
         m->gemm_ws = gws ? q : nullptr; q += (gws + 255) / 256 * 256;
         m->optim_scratch = q; q += (opt_bytes + 255) / 256 * 256;
         m->ids_dev = (long long*)q; q += id_bytes;
-        m->tgt_dev = (long long*)q;
+        m->tgt_dev = (long long*)q; q += id_bytes;
+        if (m->tc_head) {
+            m->xf_hi = q; q += xf_h; m->xf_lo = q; q += xf_h;
+            m->w_hi = q; q += w_h; m->w_lo = q; q += w_h;
+            m->dl_hi = q; q += dl_h; m->dl_lo = q; q += dl_h;
+            m->x3_ws = q; q += x3;
+        }
         // rotary cache, f32 arithmetic of gpt.rs:12-46
         const int half = D / 2;
         std::vector<float> hc((size_t)cfg->sequence_len * half), hs(hc.size());

@@ -17,6 +17,8 @@
 // DEERS_ERR_KERNEL) and is skipped; nothing traps.
 #include "common.cuh"
 
+#include <cuda_fp16.h>
+
 namespace {
 
 __global__ void __launch_bounds__(256) embedding_fwd_kernel(const float* __restrict__ w, const long long* __restrict__ ids,
@@ -190,7 +192,69 @@ __global__ void __launch_bounds__(256) cross_entropy_bwd_kernel(const float* __r
     }
 }
 
+// The same gradient written as the f16 pair the tensor-core head products read (gemm_f16x3_sm100.cu):
+// v = dlogit * scale, hi = f16(v), lo = f16((v - hi) * 2^11).  |dlogit| <= 1/rows, so scale = rows * 4096 keeps
+// hi within +-4096 and the smallest probabilities that matter well inside the f16 range.
+__global__ void __launch_bounds__(256) cross_entropy_bwd_split_kernel(const float* __restrict__ logits, long long ld,
+                                                                      const long long* __restrict__ targets,
+                                                                      const float* __restrict__ lse, long long V, float g,
+                                                                      float upstream, float scale, __half* __restrict__ hi,
+                                                                      __half* __restrict__ lo, long long ldd) {
+    const long long row = blockIdx.y;
+    const float* x = logits + row * ld;
+    __half* dh = hi + row * ldd;
+    __half* dl = lo + row * ldd;
+    const float l = lse[row];
+    const long long t = targets[row];
+    const long long stride = (long long)gridDim.x * 256;
+    const bool vec = (ld % 4 == 0) && (ldd % 8 == 0) && ((((uintptr_t)logits) & 15u) == 0) &&
+                     ((((uintptr_t)hi | (uintptr_t)lo) & 15u) == 0);
+    for (long long q = (long long)blockIdx.x * 256 + threadIdx.x; q * 8 < V; q += stride) {
+        const long long j = q * 8;
+        float o[8];
+        if (vec && j + 8 <= V) {
+            const float4 a = *reinterpret_cast<const float4*>(x + j), b = *reinterpret_cast<const float4*>(x + j + 4);
+            o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
+        } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) o[e] = (j + e < V) ? x[j + e] : -INFINITY;
+        }
+        __half h8[8], l8[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const float pr = expf(o[e] - l);
+            const float gj = (j + e == t) ? g : 0.f;
+            const float d = __fmul_rn(__fsub_rn(gj, __fmul_rn(pr, g)), upstream) * scale;
+            h8[e] = __float2half_rn(d);
+            l8[e] = __float2half_rn((d - __half2float(h8[e])) * 2048.0f);
+        }
+        if (vec && j + 8 <= V) {
+            *reinterpret_cast<uint4*>(dh + j) = *reinterpret_cast<const uint4*>(h8);
+            *reinterpret_cast<uint4*>(dl + j) = *reinterpret_cast<const uint4*>(l8);
+        } else {
+            for (int e = 0; e < 8 && j + e < V; ++e) { dh[j + e] = h8[e]; dl[j + e] = l8[e]; }
+        }
+    }
+}
+
 }  // namespace
+
+int launch_cross_entropy_bwd_split(deers_ctx* ctx, const float* logits, long long ld, const long long* targets,
+                                   const float* lse, long long rows, long long V, float upstream, float scale, void* hi,
+                                   void* lo, long long ldd) {
+    long long per_row = (V / 8 + 255) / 256;
+    if (per_row < 1) per_row = 1;
+    if (per_row > 64) per_row = 64;
+    const dim3 grid((unsigned)per_row, (unsigned)rows);
+    {
+        KernelTimerScope ts(ctx, DEERS_K_GPT);
+        cross_entropy_bwd_split_kernel<<<grid, 256, 0, ctx->stream>>>(logits, ld, targets, lse, V, (float)(-1.0 / (double)rows),
+                                                                      upstream, scale, (__half*)hi, (__half*)lo, ldd);
+    }
+    ctx->launches += 1;
+    DEERS_CUDA_TRY(ctx, cudaGetLastError());
+    return DEERS_OK;
+}
 
 int launch_embedding_fwd(deers_ctx* ctx, const float* weight, const long long* ids, long long n_ids, int C, long long V,
                          float* out) {

@@ -255,6 +255,44 @@ def gemm_f32(a: torch.Tensor, b: torch.Tensor, a_mn_major: bool = False, b_mn_ma
     return c
 
 
+def split_f16x3(x: torch.Tensor, scale: float = 1.0):
+    """The f16 pair (hi, lo) of a 2-D f32 tensor: x * scale = hi + lo * 2^-11 (deers_b200_split_f16x3).  The pair
+    is returned as [rows, cols] views of buffers whose rows are padded to a multiple of 8 elements."""
+    _f32("x", x)
+    if x.dim() != 2 or x.stride(1) != 1:
+        raise LayoutMismatch("split_f16x3 wants a 2-D tensor with unit inner stride")
+    rows, cols = x.shape
+    ld = (cols + 7) // 8 * 8
+    ctx = Context.current(x.device)
+    hi = torch.zeros((rows, ld), dtype=torch.float16, device=x.device)
+    lo = torch.zeros((rows, ld), dtype=torch.float16, device=x.device)
+    _lib.check(_lib.lib().deers_b200_split_f16x3(ctx.handle, rows, cols, x.data_ptr(), x.stride(0), scale, hi.data_ptr(),
+                                                 lo.data_ptr(), ld), ctx.handle)
+    return hi[:, :cols], lo[:, :cols]
+
+
+def gemm_f16x3(a: torch.Tensor, b: torch.Tensor, a_mn_major: bool = False, b_mn_major: bool = True,
+               scale_a: float = 1.0, scale_b: float = 1.0) -> torch.Tensor:
+    """C = A * B in f32 through the tensor core on split f16 operands (deers_b200_gemm_f16x3); operand
+    conventions as gemm_f32."""
+    M, K = (a.shape[1], a.shape[0]) if a_mn_major else a.shape
+    Kb, N = b.shape if b_mn_major else (b.shape[1], b.shape[0])
+    if K != Kb:
+        raise LayoutMismatch(f"inner dimensions differ: {K} vs {Kb}")
+    a_hi, a_lo = split_f16x3(a, scale_a)
+    b_hi, b_lo = split_f16x3(b, scale_b)
+    ctx = Context.current(a.device)
+    L = _lib.lib()
+    ldc = (N + 3) // 4 * 4
+    c = torch.full((M, ldc), float("nan"), dtype=torch.float32, device=a.device)
+    nbytes = int(L.deers_b200_gemm_f16x3_workspace_bytes(ctx.handle, M, N, K))
+    ws = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=a.device)
+    _lib.check(L.deers_b200_gemm_f16x3(ctx.handle, M, N, K, a_hi.data_ptr(), a_lo.data_ptr(), a_hi.stride(0), int(a_mn_major),
+                                       b_hi.data_ptr(), b_lo.data_ptr(), b_hi.stride(0), int(b_mn_major), c.data_ptr(), ldc,
+                                       1.0 / (scale_a * scale_b), ws.data_ptr(), ws.numel()), ctx.handle)
+    return c[:, :N]
+
+
 def embedding(weight: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
     """`Embedding::forward` (src/nn.rs:214-221)."""
     _f32("weight", weight)

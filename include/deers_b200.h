@@ -370,6 +370,30 @@ int deers_b200_gemm_f32(deers_ctx* ctx, int32_t M, int32_t N, int32_t K, const f
                         const deers_gemm_epilogue* epilogue, void* workspace, size_t workspace_bytes);
 
 /*
+ * f32-accurate GEMM on the tensor core: C[M,N] = A * B in f32 where every f32 operand is carried as an f16 pair
+ * (x * s = hi + lo * 2^-11) and the product is three tcgen05 f16 products with f32 accumulation (main = hi*hi,
+ * correction = hi*lo + lo*hi; the dropped lo*lo term is below 2^-22 of a product).  Same role as
+ * deers_b200_gemm_f32 - the reference's f32 matmul (`src/storage/cuda.rs:1098-1128`, CUBLAS_COMPUTE_32F) behind
+ * `Linear::forward` and the matmul backward - for the products large enough to be worth the tensor core: the
+ * language-model head (`src/models/gpt.rs:351`) and its two backward products, 80 % of a training step's FLOPs.
+ *   split_f16x3   hi = f16(src * scale), lo = f16((src * scale - hi) * 2^11) for a [rows, cols] f32 matrix; scale is
+ *                 a power of two that brings the values into f16 range (1 for activations and weights; gradients
+ *                 of a mean-reduced loss want about rows * 4096).  hi / lo: f16 [rows][ld_dst].
+ *   gemm_f16x3    operand orders as deers_b200_gemm_f16 (a_mn_major, b_mn_major); lda, ldb multiples of 8, ldc a
+ *                 multiple of 4, pointers 16-byte aligned (DEERS_ERR_LAYOUT otherwise); any M, N, K.
+ *                 C = (A*B) * out_scale: pass 1 / (scale_a * scale_b).  Products with few output tiles and a long K
+ *                 are split along K and summed in a fixed order (bitwise reproducible); `workspace` then needs
+ *                 deers_b200_gemm_f16x3_workspace_bytes(ctx, M, N, K) bytes (0 otherwise).
+ * Enqueued on the context's stream; no allocation, no synchronisation.
+ */
+int deers_b200_split_f16x3(deers_ctx* ctx, int64_t rows, int32_t cols, const float* src, int64_t ld_src, float scale,
+                           void* hi, void* lo, int64_t ld_dst);
+size_t deers_b200_gemm_f16x3_workspace_bytes(deers_ctx* ctx, int32_t M, int32_t N, int32_t K);
+int deers_b200_gemm_f16x3(deers_ctx* ctx, int32_t M, int32_t N, int32_t K, const void* a_hi, const void* a_lo, int64_t lda,
+                          int32_t a_mn_major, const void* b_hi, const void* b_lo, int64_t ldb, int32_t b_mn_major, float* c,
+                          int64_t ldc, float out_scale, void* workspace, size_t workspace_bytes);
+
+/*
  * RMSNorm backward that also adds the gradient arriving over the residual connection:
  * dx = residual_grad + (dy*inv - x * (sum(dy*x) * inv^3 / C)).  In the block `x + f(norm(x))`
  * (`src/models/gpt.rs:236-240`) the reference's GradientStore adds the two contributions to x with a separate
@@ -521,7 +545,7 @@ uint64_t deers_b200_launch_count(deers_ctx* ctx);
  * milliseconds and the number of launches of one kernel kind since timing was
  * enabled (or since the last call with reset != 0).
  */
-enum { DEERS_K_FWD = 0, DEERS_K_BWD_PREP = 1, DEERS_K_BWD_MAIN = 2, DEERS_K_BWD_DQ = 3, DEERS_K_ROPE = 4, DEERS_K_OPTIM = 5, DEERS_K_NORM = 6, DEERS_K_DECODE = 7, DEERS_K_GEMM = 8, DEERS_K_GPT = 9, DEERS_K_COUNT = 10 };
+enum { DEERS_K_FWD = 0, DEERS_K_BWD_PREP = 1, DEERS_K_BWD_MAIN = 2, DEERS_K_BWD_DQ = 3, DEERS_K_ROPE = 4, DEERS_K_OPTIM = 5, DEERS_K_NORM = 6, DEERS_K_DECODE = 7, DEERS_K_GEMM = 8, DEERS_K_GPT = 9, DEERS_K_GEMM_X3 = 10, DEERS_K_COUNT = 11 };
 int deers_b200_kernel_timing(deers_ctx* ctx, int enable);
 int deers_b200_kernel_time(deers_ctx* ctx, int kind, int reset, double* total_ms, uint64_t* launches);
 

@@ -112,6 +112,48 @@ def test_gemm_f32_rejects_bad_arguments():
         gpt.gemm_f32(a, a, epilogue=_lib.EPI_ADD)            # residual missing -> DEERS_ERR_NULL
 
 
+# ---- f32-accurate tensor-core GEMM on split f16 operands ------------------------------------------------
+X3_SHAPES = [  # M, N, K
+    (128, 128, 64), (1, 1, 1), (200, 300, 100), (130, 70, 1000),
+    (1024, 5003, 192), (192, 5003, 1024), (1024, 192, 5003), (1024, 192, 50257), (300, 2048, 192),
+]
+
+
+@pytest.mark.parametrize("M,N,K", X3_SHAPES)
+@pytest.mark.parametrize("a_mn,b_mn", [(0, 1), (0, 0), (1, 1), (1, 0)])
+def test_gemm_f16x3_is_f32_accurate(M, N, K, a_mn, b_mn):
+    """Three f16 products carry an f32 product: closer to float64 than a sequential f32 sum would be."""
+    from deers_b200 import gpt
+    rng = np.random.default_rng(M + 3 * N + 5 * K)
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    b = (rng.standard_normal((K, N)) / np.sqrt(K)).astype(np.float32)
+    want = a.astype(np.float64) @ b.astype(np.float64)
+    ta = dev(a.T) if a_mn else dev(a)
+    tb = dev(b) if b_mn else dev(b.T)
+    got = gpt.gemm_f16x3(ta, tb, bool(a_mn), bool(b_mn))
+    got2 = gpt.gemm_f16x3(ta, tb, bool(a_mn), bool(b_mn))
+    torch.cuda.synchronize()
+    # operands are carried to 2^-22; what is left is the f32 accumulation of K terms in the tensor core
+    assert rel(got.cpu().numpy(), want) < 2e-6 * max(1.0, np.sqrt(K) / 16)
+    assert torch.equal(got, got2), "the K split adds its parts in a fixed order"
+
+
+def test_gemm_f16x3_scaled_gradients_and_exact_small_integers():
+    """Tiny values (gradients of a mean-reduced loss) go through with a power-of-two scale; small integers are exact."""
+    from deers_b200 import gpt
+    rng = np.random.default_rng(9)
+    a = (rng.standard_normal((256, 4096)) * 1e-7).astype(np.float32)          # like dlogits: |x| <= 1 / rows
+    b = (rng.standard_normal((4096, 192)) / 64).astype(np.float32)
+    want = a.astype(np.float64) @ b.astype(np.float64)
+    got = gpt.gemm_f16x3(dev(a), dev(b), scale_a=256.0 * 4096.0 * 1024.0)
+    assert rel(got.cpu().numpy(), want) < 2e-6
+    ai = rng.integers(-8, 9, (128, 64)).astype(np.float32)
+    bi = rng.integers(-8, 9, (64, 128)).astype(np.float32)
+    got = gpt.gemm_f16x3(dev(ai), dev(bi))
+    torch.cuda.synchronize()
+    assert np.array_equal(got.cpu().numpy(), ai @ bi)
+
+
 # ---- embedding, cross-entropy -------------------------------------------------------------------------
 def test_embedding_bit_exact_with_repeated_tokens():
     from deers_b200 import gpt
