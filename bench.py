@@ -695,6 +695,8 @@ def run_gpt_step(args):
     model = gpt.GPT(gpt.GPTConfig(c["vocab"], T, c["n_layer"], c["n_head"], c["n_embd"], c["mlp"], c["eps"],
                                   c["rope_base"]), dev, B)
     model.load_parameters(params)
+    if args.no_graph:
+        model.set_graph(False)
     rng = np.random.default_rng(1 + rank)
     n_batches = 8                                            # rotate batches so no step repeats the previous one's ids
     ids_h = [rng.integers(0, c["vocab"], (B, T)) for _ in range(n_batches)]
@@ -772,7 +774,7 @@ def run_gpt_step(args):
         kernels[name] = {"launches_per_step": n / k_steps, "ms_per_step": t_ms / k_steps}
     ctx.kernel_timing(False)
     ctx.sync()
-    model.set_graph(True)
+    model.set_graph(not args.no_graph)
 
     if rank == 0:
         peaks = load_peaks()
@@ -858,6 +860,9 @@ def main():
     ap.add_argument("--e2e-chunk-mb", type=int, default=128,
                     help="input bytes (Q,K,V,dO together) per chunk of the pipelined host call, in MiB")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true",
+                    help="cfg3: launch every kernel of the step eagerly instead of replaying the captured graph "
+                         "(what a per-kernel profiler capture wants)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--rope", action="store_true",
                     help="time the fused rotary embedding + head-major pack (q and k, forward and inverse) "
