@@ -766,7 +766,7 @@ def run_gpt_step(args):
         model.train_step(ids_d[i % n_batches], tgt_d[i % n_batches], **kw)
     eager_launches = (ctx.launch_count() - l0) / k_steps
     fams = {"gemm_f32": _lib.K_GEMM, "gemm_f16x3_head": _lib.K_GEMM_X3, "attn_fwd_f32": _lib.K_FWD, "attn_bwd_delta_f32": _lib.K_BWD_PREP,
-            "attn_bwd_dkdv_f32": _lib.K_BWD_MAIN, "attn_bwd_dq_f32": _lib.K_BWD_DQ, "rope_pack": _lib.K_ROPE,
+            "attn_bwd_f32 (dK/dV and dQ blocks in one launch)": _lib.K_BWD_MAIN, "rope_pack": _lib.K_ROPE,
             "rmsnorm": _lib.K_NORM, "embedding_cross_entropy": _lib.K_GPT, "grad_norm_adamw": _lib.K_OPTIM}
     kernels = {}
     for name, kind in fams.items():

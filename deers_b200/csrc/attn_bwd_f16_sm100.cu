@@ -133,15 +133,31 @@ enum DkvBar { A_KV_FULL = 0, A_KV_EMPTY = 1, A_Q_FULL = 2, A_Q_EMPTY = 5, A_DO_F
               A_ST_FULL = 12, A_ST_EMPTY = 14, A_S = 16, A_DP = 17, A_P = 18, A_DS = 19, A_DONE = 20, A_ACC_FREE = 21,
               A_COUNT = 22 };
 
+// Compute warpgroups of the dK / dV kernel: each owns 128 / DKV_NWG query columns of S^T / dP^T and
+// D / DKV_NWG columns of dK and dV.  Two and four measure the same (6.0 vs 6.1 ms at B64 H32 T2048 D128): the
+// kernel waits on the tensor pipe (a 128x128x16 product every 94-102 cycles), not on these threads.
+constexpr int DKV_NWG = 2;
+constexpr int DKV_THREADS = 64 + 128 * DKV_NWG;
+
+__device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t (&r)[32]) { tmem_ld_x32(taddr, r); }
+__device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t (&r)[16]) { tmem_ld_x16(taddr, r); }
+__device__ __forceinline__ void tmem_st(uint32_t taddr, const uint32_t (&r)[32]) { tmem_st_x32(taddr, r); }
+__device__ __forceinline__ void tmem_st(uint32_t taddr, const uint32_t (&r)[16]) { tmem_st_x16(taddr, r); }
+
 template <int D>
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(DKV_THREADS, 1)
 attn_bwd_dkdv_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                          const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
                          const BwdParams p) {
     using L = DkvSmem<D>;
     constexpr uint32_t TILE_BYTES = L::TILE;
     constexpr int DBLK = D / 64;
-    constexpr int DH = D / 2;                               // output columns per compute warpgroup
+    constexpr int NWG = DKV_NWG;
+    constexpr int NCT = 128 * NWG;                          // compute threads
+    constexpr int CW = BT / NWG;                            // query columns of S^T / dP^T per compute warpgroup
+    constexpr int DH = D / NWG;                             // output columns per compute warpgroup
+    constexpr int EC = DH < 32 ? DH : 32;                   // columns per TMEM load in the epilogue
+    static_assert(CW % 32 == 0 && (DH == 16 || DH % 32 == 0), "unsupported warpgroup split");
     constexpr uint32_t TMEM_COLS = 512;
     // S^T (later P^T in place) | dP^T (later dS^T in place) | dV | dK
     constexpr uint32_t TM_S = 0, TM_DP = 128, TM_DV = 256, TM_DK = 256 + D;
@@ -175,14 +191,14 @@ attn_bwd_dkdv_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         for (int s = 0; s < 3; ++s) { mbar_init(&bars[A_Q_FULL + s], 1); mbar_init(&bars[A_Q_EMPTY + s], 1); }
         for (int s = 0; s < 2; ++s) {
             mbar_init(&bars[A_DO_FULL + s], 1); mbar_init(&bars[A_DO_EMPTY + s], 1);
-            mbar_init(&bars[A_ST_FULL + s], 256);
+            mbar_init(&bars[A_ST_FULL + s], NCT);
         }
         mbar_init(&bars[A_S], 1);
         mbar_init(&bars[A_DP], 1);
-        mbar_init(&bars[A_P], 256);
-        mbar_init(&bars[A_DS], 256);
+        mbar_init(&bars[A_P], NCT);
+        mbar_init(&bars[A_DS], NCT);
         mbar_init(&bars[A_DONE], 1);
-        mbar_init(&bars[A_ACC_FREE], 256);
+        mbar_init(&bars[A_ACC_FREE], NCT);
         fence_barrier_init();
         tma_prefetch_desc(&tmap_q); tma_prefetch_desc(&tmap_k); tma_prefetch_desc(&tmap_v); tma_prefetch_desc(&tmap_do);
     }
@@ -259,8 +275,10 @@ attn_bwd_dkdv_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
                     umma_ss(tmem + TM_DP, v_km + kmajor_step(ks, BLOCK_BYTES), do_km + kmajor_step(ks, BLOCK_BYTES), IDESC_ST, ks > 0);
                 umma_commit(&bars[A_DP]);
             };
-            // A operand in TMEM: 32 packed columns per warpgroup half, halves 64 columns apart.
-            auto a_tmem = [&](uint32_t base, int ks) { return tmem + base + (uint32_t)(ks >> 2) * 64u + (uint32_t)(ks & 3) * 8u; };
+            // A operand in TMEM: CW / 2 packed columns per compute warpgroup, the groups CW columns apart.
+            auto a_tmem = [&](uint32_t base, int ks) {
+                return tmem + base + (uint32_t)(ks / (CW / 16)) * (uint32_t)CW + (uint32_t)(ks % (CW / 16)) * 8u;
+            };
             uint32_t gi = 0;
             bool ok = true;
             for (int4 cur = next_item(p, 0, n_items, nq), nxt = next_item(p, 1, n_items, nq), n4 = make_int4(0, 0, 0, 0); ok && cur.x >= 0;
@@ -314,8 +332,8 @@ attn_bwd_dkdv_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         }
     } else {
         // ------------------------------ compute threads ------------------------------
-        // Warpgroup g owns query columns [64g, 64g+64) of S^T / dP^T and columns
-        // [g*D/2, (g+1)*D/2) of dK and dV.  Thread r of a warpgroup owns TMEM lane r = KV row r.
+        // Warpgroup g owns query columns [CW*g, CW*g+CW) of S^T / dP^T and columns
+        // [g*DH, (g+1)*DH) of dK and dV.  Thread r of a warpgroup owns TMEM lane r = KV row r.
         const int g = (warp - 2) >> 2;
         const int lane_base = (warp & 3) * 32;
         const int r = lane_base + lane;
@@ -324,20 +342,21 @@ attn_bwd_dkdv_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         uint32_t gi = 0;
         bool alive = true;
         // The 128 lse * log2e and the 128 delta values of a query tile are staged in shared memory by the compute
-        // threads themselves: thread ct fetches element ct of the NEXT iteration's 256 values one iteration ahead
-        // (a plain global load, in flight during this iteration's products), stores it at the top of that
-        // iteration and arrives on the stage's barrier; everyone waits for all 256 before reading.  A stage is
+        // threads themselves: thread ct < 256 fetches element ct of the NEXT iteration's 256 values one iteration
+        // ahead (a plain global load, in flight during this iteration's products) and stores it at the top of that
+        // iteration; every compute thread then arrives on the stage's barrier and waits for all before reading.  A stage is
         // rewritten two iterations after it was read, and nobody gets there before all threads have passed the
         // barrier of the iteration in between, i.e. have finished reading.  (An earlier version had the producer
         // warp bring these rows in with bulk copies; repeated full-size runs then showed, once in a few dozen, one
         // warp seeing a stale 32-byte piece of the delta row in the first iteration of an item.)
         const int ct = (warp - 2) * 32 + lane;
+        const bool stager = ct < 2 * BT;
         const float* stat_src = (ct < BT) ? p.lse2 + ct : p.delta + (ct - BT);
         float* stat_dst = (ct < BT) ? lse2_s + ct : delta_s + (ct - BT);
         float stat_next = 0.f;
         {
             const int4 first = next_item(p, 0, n_items, nq);
-            if (first.x >= 0) stat_next = __ldg(stat_src + (long long)first.y * p.Tpad + (p.causal ? first.x : 0) * BT);
+            if (stager && first.x >= 0) stat_next = __ldg(stat_src + (long long)first.y * p.Tpad + (p.causal ? first.x : 0) * BT);
         }
 
         for (int4 cur = next_item(p, 0, n_items, nq), nxt = next_item(p, 1, n_items, nq), n4 = make_int4(0, 0, 0, 0); alive && cur.x >= 0;
@@ -352,22 +371,24 @@ attn_bwd_dkdv_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
             for (int it = 0; it < niter; ++it, ++gi) {
                 const int i = i0 + it;
                 const uint32_t ss = gi & 1u, par = gi & 1u;
-                const float* lse2 = lse2_s + ss * BT + 64 * g;
-                const float* dlt = delta_s + ss * BT + 64 * g;
-                stat_dst[ss * BT] = stat_next;              // this iteration's value, fetched one iteration ago
+                const float* lse2 = lse2_s + ss * BT + CW * g;
+                const float* dlt = delta_s + ss * BT + CW * g;
+                if (stager) stat_dst[ss * BT] = stat_next;  // this iteration's value, fetched one iteration ago
                 mbar_arrive(&bars[A_ST_FULL + ss]);
                 // next iteration's value: the next query tile of this item, or the first one of the next item
-                if (it + 1 < niter) stat_next = __ldg(stat_src + (long long)bh * p.Tpad + (i + 1) * BT);
-                else if (nxt.x >= 0) stat_next = __ldg(stat_src + (long long)nxt.y * p.Tpad + (p.causal ? nxt.x : 0) * BT);
+                if (stager) {
+                    if (it + 1 < niter) stat_next = __ldg(stat_src + (long long)bh * p.Tpad + (i + 1) * BT);
+                    else if (nxt.x >= 0) stat_next = __ldg(stat_src + (long long)nxt.y * p.Tpad + (p.causal ? nxt.x : 0) * BT);
+                }
                 if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[A_ST_FULL + ss], (gi >> 1) & 1u, DEERS_KERR_BWD_F16 | 13))) { alive = false; break; }
                 if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[A_S], par, DEERS_KERR_BWD_F16 | 14))) { alive = false; break; }
                 tc_fence_after_sync();
                 const bool diag = p.causal && (i == kt);
-                uint32_t pk[32];                            // P^T row, 64 query columns as f16 pairs
+                uint32_t pk[CW / 2];                        // P^T row, CW query columns as f16 pairs
 #pragma unroll
-                for (int c = 0; c < 2; ++c) {
+                for (int c = 0; c < CW / 32; ++c) {
                     uint32_t sr[32];
-                    tmem_ld_x32(tmem + TM_S + t_lane + 64 * g + c * 32, sr);
+                    tmem_ld_x32(tmem + TM_S + t_lane + CW * g + c * 32, sr);
                     tmem_wait_ld();
                     if (diag || !kv_valid) {                // only the diagonal / tail tile pays for masking
 #pragma unroll
@@ -375,8 +396,8 @@ attn_bwd_dkdv_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
                             const int cl = c * 32 + e * 2;  // column inside this warpgroup's half
                             float p0 = ex2(fmaf(__uint_as_float(sr[e * 2]), sl2, -lse2[cl]));
                             float p1 = ex2(fmaf(__uint_as_float(sr[e * 2 + 1]), sl2, -lse2[cl + 1]));
-                            if ((diag && (64 * g + cl) < r) || !kv_valid) p0 = 0.f;   // query index < key index: masked
-                            if ((diag && (64 * g + cl + 1) < r) || !kv_valid) p1 = 0.f;
+                            if ((diag && (CW * g + cl) < r) || !kv_valid) p0 = 0.f;   // query index < key index: masked
+                            if ((diag && (CW * g + cl + 1) < r) || !kv_valid) p1 = 0.f;
                             pk[c * 16 + e] = pack_half2(p0, p1);
                         }
                     } else {
@@ -388,19 +409,19 @@ attn_bwd_dkdv_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
                         }
                     }
                 }
-                // P^T replaces this warpgroup's half of S^T in TMEM (32 packed columns).
-                tmem_st_x32(tmem + TM_S + t_lane + 64 * g, pk);
+                // P^T replaces this warpgroup's part of S^T in TMEM (CW / 2 packed columns).
+                tmem_st(tmem + TM_S + t_lane + CW * g, pk);
                 tmem_wait_st();
                 tc_fence_before_sync();
                 mbar_arrive(&bars[A_P]);
 
                 if (!__all_sync(0xffffffffu, mbar_wait(ws, &bars[A_DP], par, DEERS_KERR_BWD_F16 | 15))) { alive = false; break; }
                 tc_fence_after_sync();
-                uint32_t dd[32];                            // dS^T row, 64 query columns as f16 pairs
+                uint32_t dd[CW / 2];                        // dS^T row, CW query columns as f16 pairs
 #pragma unroll
-                for (int c = 0; c < 2; ++c) {
+                for (int c = 0; c < CW / 32; ++c) {
                     uint32_t dr[32];
-                    tmem_ld_x32(tmem + TM_DP + t_lane + 64 * g + c * 32, dr);
+                    tmem_ld_x32(tmem + TM_DP + t_lane + CW * g + c * 32, dr);
                     tmem_wait_ld();
 #pragma unroll
                     for (int e = 0; e < 16; ++e) {
@@ -410,25 +431,27 @@ attn_bwd_dkdv_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
                                                     pf.y * (__uint_as_float(dr[e * 2 + 1]) - dlt[cl + 1]));
                     }
                 }
-                tmem_st_x32(tmem + TM_DP + t_lane + 64 * g, dd);
+                tmem_st(tmem + TM_DP + t_lane + CW * g, dd);
                 tmem_wait_st();
                 tc_fence_before_sync();
                 mbar_arrive(&bars[A_DS]);
                 if (p.ds) {
                     // The same dS^T row also goes to global memory, already swizzled, for the dQ kernel (off the
-                    // critical path: the tensor core has what it needs).  The row's eight 16-byte chunks are
-                    // transposed within 8-lane groups first, so that one store instruction writes four whole
-                    // 128-byte rows instead of 16 bytes in each of 32 rows.
+                    // critical path: the tensor core has what it needs).  The row's NCH 16-byte chunks are
+                    // transposed within NCH-lane groups first, so that one store instruction writes whole
+                    // NCH*16-byte row segments instead of 16 bytes in each of 32 rows.
+                    constexpr int NCH = CW / 8;                 // this warpgroup's chunks of a row
                     uint8_t* tile = reinterpret_cast<uint8_t*>(p.ds) + (((long long)bh * p.ds_pairs + ds_pair(p, i, kt, nq)) << 15) +
-                                    g * (int)BLOCK_BYTES;
-                    uint4 pc[8];
+                                    (CW * g / 64) * (int)BLOCK_BYTES;
+                    const int ch0 = (CW * g % 64) / 8;          // first chunk inside the 64-column block
+                    uint4 pc[NCH];
 #pragma unroll
-                    for (int ch = 0; ch < 8; ++ch) pc[ch] = make_uint4(dd[4 * ch], dd[4 * ch + 1], dd[4 * ch + 2], dd[4 * ch + 3]);
-                    transpose_pieces<8>(pc, (uint32_t)lane);
-                    const int rbase = lane_base + (lane & ~7);  // pc[c] is now chunk (lane & 7) of row rbase + c
+                    for (int ch = 0; ch < NCH; ++ch) pc[ch] = make_uint4(dd[4 * ch], dd[4 * ch + 1], dd[4 * ch + 2], dd[4 * ch + 3]);
+                    transpose_pieces<NCH>(pc, (uint32_t)lane);
+                    const int rbase = lane_base + (lane & ~(NCH - 1));  // pc[c] is now chunk (lane % NCH) of row rbase + c
 #pragma unroll
-                    for (int c = 0; c < 8; ++c)       // streaming stores: the tiles are read once, by the next kernel
-                        __stcs(reinterpret_cast<uint4*>(tile + sw128_chunk_offset(rbase + c, lane & 7)), pc[c]);
+                    for (int c = 0; c < NCH; ++c)     // streaming stores: the tiles are read once, by the next kernel
+                        __stcs(reinterpret_cast<uint4*>(tile + sw128_chunk_offset(rbase + c, ch0 + (lane & (NCH - 1)))), pc[c]);
                 }
             }
             if (!alive) break;
@@ -442,19 +465,19 @@ attn_bwd_dkdv_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
             constexpr int NP = DH / 8;
             uint4 kc[NP], vc[NP];
 #pragma unroll
-            for (int c = 0; c < DH / 32; ++c) {
-                uint32_t kr[32], vr[32];
-                tmem_ld_x32(tmem + TM_DK + t_lane + g * DH + c * 32, kr);
-                tmem_ld_x32(tmem + TM_DV + t_lane + g * DH + c * 32, vr);
+            for (int c = 0; c < DH / EC; ++c) {
+                uint32_t kr[EC], vr[EC];
+                tmem_ld(tmem + TM_DK + t_lane + g * DH + c * EC, kr);
+                tmem_ld(tmem + TM_DV + t_lane + g * DH + c * EC, vr);
                 tmem_wait_ld();
-                if (c == DH / 32 - 1) {                     // accumulators are in registers: release TMEM early
+                if (c == DH / EC - 1) {                     // accumulators are in registers: release TMEM early
                     tc_fence_before_sync();
                     mbar_arrive(&bars[A_ACC_FREE]);
                 }
 #pragma unroll
-                for (int q8 = 0; q8 < 4; ++q8) {
-                    kc[c * 4 + q8] = pack8_f16(kr + q8 * 8, p.scale);
-                    vc[c * 4 + q8] = pack8_f16(vr + q8 * 8, 1.0f);
+                for (int q8 = 0; q8 < EC / 8; ++q8) {
+                    kc[c * (EC / 8) + q8] = pack8_f16(kr + q8 * 8, p.scale);
+                    vc[c * (EC / 8) + q8] = pack8_f16(vr + q8 * 8, 1.0f);
                 }
             }
             transpose_pieces<NP>(kc, (uint32_t)lane);
@@ -1053,7 +1076,7 @@ int bwd_launch(deers_ctx* ctx, const deers_attn_desc* d, const void* q, const vo
     DEERS_CUDA_TRY(ctx, cudaFuncSetAttribute(attn_bwd_dq_f16_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_b));
     {
         KernelTimerScope ts(ctx, DEERS_K_BWD_MAIN);
-        attn_bwd_dkdv_f16_kernel<D><<<persistent, 320, smem_a, ctx->stream>>>(tq, tk, tv, tdo, p);
+        attn_bwd_dkdv_f16_kernel<D><<<persistent, DKV_THREADS, smem_a, ctx->stream>>>(tq, tk, tv, tdo, p);
     }
     DEERS_CUDA_TRY(ctx, cudaGetLastError());
     if (keep_ds) {

@@ -284,8 +284,7 @@ __device__ __forceinline__ void recompute_p_ds(const F32Params& p, const float* 
 // at or below its diagonal and keeps dK/dV in registers, so no atomics are needed.
 // ---------------------------------------------------------------------------
 template <int DP>
-__global__ void __launch_bounds__(NT) attn_bwd_dkdv_f32_kernel(const F32Params p) {
-    extern __shared__ __align__(16) float smem[];
+__device__ __forceinline__ void attn_bwd_dkdv_f32_body(const F32Params& p, float* smem) {
     constexpr int LD = DP + 4;
     float* Ks = smem;
     float* Vs = Ks + BN * LD;
@@ -361,8 +360,7 @@ __global__ void __launch_bounds__(NT) attn_bwd_dkdv_f32_kernel(const F32Params p
 // at or left of its diagonal.
 // ---------------------------------------------------------------------------
 template <int DP>
-__global__ void __launch_bounds__(NT) attn_bwd_dq_f32_kernel(const F32Params p) {
-    extern __shared__ __align__(16) float smem[];
+__device__ __forceinline__ void attn_bwd_dq_f32_body(const F32Params& p, float* smem) {
     constexpr int LD = DP + 4;
     float* Ks = smem;
     float* Vs = Ks + BN * LD;
@@ -425,6 +423,16 @@ __global__ void __launch_bounds__(NT) attn_bwd_dq_f32_kernel(const F32Params p) 
     }
 }
 
+// dK/dV and dQ in one launch: the two walks share nothing but their inputs, so blockIdx.z picks the role
+// (z = 0: one KV tile per block, z = 1: one query tile per block) and both sets of blocks run side by side;
+// at the model's shapes each alone fills well under one block per SM.
+template <int DP>
+__global__ void __launch_bounds__(NT) attn_bwd_f32_kernel(const F32Params p) {
+    extern __shared__ __align__(16) float smem[];
+    if (blockIdx.z == 0) attn_bwd_dkdv_f32_body<DP>(p, smem);
+    else attn_bwd_dq_f32_body<DP>(p, smem);
+}
+
 Strides3 s3(const int64_t* s) { return Strides3{(long long)s[0], (long long)s[1], (long long)s[2]}; }
 
 bool rows_vec_ok(const void* ptr, const int64_t* s) {
@@ -462,22 +470,16 @@ int bwd_impl(deers_ctx* ctx, const F32Params& p) {
     DEERS_CUDA_TRY(ctx, cudaGetLastError());
     const size_t smem_kv = (size_t)(4 * BM * (DP + 4) + 2 * BM * PLD + 2 * BM) * sizeof(float);
     const size_t smem_q = (size_t)(4 * BM * (DP + 4) + BM * PLD + 2 * BM) * sizeof(float);
-    int rc = set_smem(ctx, attn_bwd_dkdv_f32_kernel<DP>, smem_kv);
+    const size_t smem = smem_kv > smem_q ? smem_kv : smem_q;
+    int rc = set_smem(ctx, attn_bwd_f32_kernel<DP>, smem);
     if (rc) return rc;
-    rc = set_smem(ctx, attn_bwd_dq_f32_kernel<DP>, smem_q);
-    if (rc) return rc;
-    dim3 grid((p.T + BM - 1) / BM, p.B * p.H);
+    dim3 grid((p.T + BM - 1) / BM, p.B * p.H, 2);
     {
         KernelTimerScope ts(ctx, DEERS_K_BWD_MAIN);
-        attn_bwd_dkdv_f32_kernel<DP><<<grid, NT, smem_kv, ctx->stream>>>(p);
+        attn_bwd_f32_kernel<DP><<<grid, NT, smem, ctx->stream>>>(p);
     }
     DEERS_CUDA_TRY(ctx, cudaGetLastError());
-    {
-        KernelTimerScope ts(ctx, DEERS_K_BWD_DQ);
-        attn_bwd_dq_f32_kernel<DP><<<grid, NT, smem_q, ctx->stream>>>(p);
-    }
-    DEERS_CUDA_TRY(ctx, cudaGetLastError());
-    ctx->launches += 3;
+    ctx->launches += 2;
     return DEERS_OK;
 }
 

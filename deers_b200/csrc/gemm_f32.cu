@@ -10,8 +10,10 @@
 //   ADD       C = R + acc                 the residual connections of the block (gpt.rs:237-239)
 //   RELU_SQ   r = max(acc, 0); C = r*r; AUX = r     relu and y*y of the MLP (gpt.rs:194-196)
 //   MUL_AUX2  t = acc * AUX; C = t + t    the backward of y*y and relu in one (ops.rs:210-214, 560-568)
-// 256 threads own a BM x BN tile (register patches of TM x TN, operands double-buffered in shared
-// memory, 16 deep).  Shapes with few output tiles and a long reduction (weight gradients, the head's
+// 256 * KS threads own a BM x BN tile (register patches of TM x TN, operands double-buffered in shared
+// memory, 16 * KS deep; with KS = 2 the two halves of the block each multiply 16 of a stage's 32 k and the
+// patches are added through shared memory at the end: twice the warps per tile for the small shapes whose
+// grids do not fill the SMs and that otherwise wait on shared-memory latency with two warps per scheduler).  Shapes with few output tiles and a long reduction (weight gradients, the head's
 // input gradient) are split along K across gridDim.z: every part writes its partial tile to the
 // workspace, the part that arrives last (one atomic counter per tile, no waiting) adds the parts in
 // index order and runs the epilogue, so results do not depend on arrival order.
@@ -45,19 +47,21 @@ __device__ __forceinline__ float4 ld4(const float* p, int valid, bool vec) {
     return v;
 }
 
-// Loads one BROWS x GK operand tile into registers.  contiguous-K storage: rows = tile rows (m or n),
-// 4 threads cover the 16 k of a row; contiguous-MN storage: rows = k, float4 along m / n.
-template <int BR>
+// Loads one BROWS x GKS operand tile into registers.  contiguous-K storage: rows = tile rows (m or n),
+// GKS / 4 threads cover the k of a row; contiguous-MN storage: rows = k, float4 along m / n.
+template <int BR, int KS>
 struct TileLoader {
-    static constexpr int NV = BR * GK / 4 / 256;         // float4 per thread
+    static constexpr int GKS = GK * KS;
+    static constexpr int NT = 256 * KS;
+    static constexpr int NV = BR * GKS / 4 / NT;         // float4 per thread
     float4 v[NV];
     __device__ __forceinline__ void load(const float* base, long long ld, int mn_major, bool vec, int r0, int rmax,
                                          int k0, int kmax) {
 #pragma unroll
         for (int i = 0; i < NV; ++i) {
-            const int idx = threadIdx.x + i * 256;
+            const int idx = threadIdx.x + i * NT;
             if (!mn_major) {
-                const int row = idx >> 2, kq = (idx & 3) * 4;
+                const int row = idx / (GKS / 4), kq = (idx % (GKS / 4)) * 4;
                 const int gr = r0 + row, gk = k0 + kq;
                 const int valid = gr < rmax ? kmax - gk : 0;
                 v[i] = ld4(base + (long long)gr * ld + gk, valid, vec);
@@ -72,9 +76,9 @@ struct TileLoader {
     __device__ __forceinline__ void store(float (*s)[BR + 4], int mn_major) const {
 #pragma unroll
         for (int i = 0; i < NV; ++i) {
-            const int idx = threadIdx.x + i * 256;
+            const int idx = threadIdx.x + i * NT;
             if (!mn_major) {
-                const int row = idx >> 2, kq = (idx & 3) * 4;
+                const int row = idx / (GKS / 4), kq = (idx % (GKS / 4)) * 4;
                 s[kq + 0][row] = v[i].x; s[kq + 1][row] = v[i].y; s[kq + 2][row] = v[i].z; s[kq + 3][row] = v[i].w;
             } else {
                 const int k = idx / (BR / 4), rq = (idx % (BR / 4)) * 4;
@@ -84,13 +88,15 @@ struct TileLoader {
     }
 };
 
-template <int BM, int BN, int TM, int TN>
-__global__ void __launch_bounds__(256) gemm_f32_kernel(const GemmArgs g) {
-    static_assert((BM / TM) * (BN / TN) == 256, "256 threads per tile");
-    __shared__ __align__(16) float As[2][GK][BM + 4];
-    __shared__ __align__(16) float Bs[2][GK][BN + 4];
+template <int BM, int BN, int TM, int TN, int KS>
+__global__ void __launch_bounds__(256 * KS) gemm_f32_kernel(const GemmArgs g) {
+    static_assert((BM / TM) * (BN / TN) == 256, "256 threads per tile and k half");
+    constexpr int GKS = GK * KS;
+    __shared__ __align__(16) float As[2][GKS][BM + 4];
+    __shared__ __align__(16) float Bs[2][GKS][BN + 4];
     __shared__ int s_last;
-    const int tx = threadIdx.x % (BN / TN), ty = threadIdx.x / (BN / TN);
+    const int tid = threadIdx.x % 256, kh = threadIdx.x / 256;      // position in the tile, k half
+    const int tx = tid % (BN / TN), ty = tid / (BN / TN);
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     const int kbeg = blockIdx.z * g.k_chunk;
     const int kend = min(g.K, kbeg + g.k_chunk);
@@ -101,9 +107,9 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(const GemmArgs g) {
 #pragma unroll
         for (int j = 0; j < TN; ++j) acc[i][j] = 0.f;
 
-    TileLoader<BM> la;
-    TileLoader<BN> lb;
-    const int nk = (kend - kbeg + GK - 1) / GK;
+    TileLoader<BM, KS> la;
+    TileLoader<BN, KS> lb;
+    const int nk = (kend - kbeg + GKS - 1) / GKS;
     if (nk > 0) {
         la.load(g.a, g.lda, g.a_mn, g.a_vec, m0, g.M, kbeg, kend);
         lb.load(g.b, g.ldb, g.b_mn, g.b_vec, n0, g.N, kbeg, kend);
@@ -114,11 +120,11 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(const GemmArgs g) {
     for (int kt = 0; kt < nk; ++kt) {
         const int cur = kt & 1;
         if (kt + 1 < nk) {
-            la.load(g.a, g.lda, g.a_mn, g.a_vec, m0, g.M, kbeg + (kt + 1) * GK, kend);
-            lb.load(g.b, g.ldb, g.b_mn, g.b_vec, n0, g.N, kbeg + (kt + 1) * GK, kend);
+            la.load(g.a, g.lda, g.a_mn, g.a_vec, m0, g.M, kbeg + (kt + 1) * GKS, kend);
+            lb.load(g.b, g.ldb, g.b_mn, g.b_vec, n0, g.N, kbeg + (kt + 1) * GKS, kend);
         }
 #pragma unroll
-        for (int k = 0; k < GK; ++k) {
+        for (int k = kh * GK; k < (kh + 1) * GK; ++k) {
             float af[TM], bf[TN];
             // a thread's rows / columns come in groups of four, the groups BM/2 (BN/2) apart, so that the
             // lanes of a warp read consecutive 16-byte pieces
@@ -144,17 +150,45 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(const GemmArgs g) {
         __syncthreads();
     }
 
+    // ---- the k halves of the block meet: the upper half hands its patch over through shared memory (the
+    // operand buffers are free after the loop's last barrier) and only stays for the barriers below
+    const bool owner = kh == 0;
+    if (KS > 1) {
+        static_assert(KS == 1 || sizeof(As) >= 256 * TM * TN * sizeof(float), "patch exchange fits in the A buffers");
+        float4* red = reinterpret_cast<float4*>(&As[0][0][0]);
+        if (!owner) {
+#pragma unroll
+            for (int i = 0; i < TM; ++i)
+#pragma unroll
+                for (int j = 0; j < TN / 4; ++j)
+                    red[(i * (TN / 4) + j) * 256 + tid] =
+                        make_float4(acc[i][j * 4], acc[i][j * 4 + 1], acc[i][j * 4 + 2], acc[i][j * 4 + 3]);
+        }
+        __syncthreads();
+        if (owner) {
+#pragma unroll
+            for (int i = 0; i < TM; ++i)
+#pragma unroll
+                for (int j = 0; j < TN / 4; ++j) {
+                    const float4 t = red[(i * (TN / 4) + j) * 256 + tid];
+                    acc[i][j * 4] += t.x; acc[i][j * 4 + 1] += t.y; acc[i][j * 4 + 2] += t.z; acc[i][j * 4 + 3] += t.w;
+                }
+        }
+    }
+
     // ---- split-K: park the partial tile; the last part to arrive adds all parts in index order
     if (gridDim.z > 1) {
         const int tile = blockIdx.y * gridDim.x + blockIdx.x;
         float4* mine = reinterpret_cast<float4*>(g.partial) +
                        ((size_t)tile * gridDim.z + blockIdx.z) * (BM * BN / 4);
+        if (owner) {
 #pragma unroll
-        for (int i = 0; i < TM; ++i)
+            for (int i = 0; i < TM; ++i)
 #pragma unroll
-            for (int j = 0; j < TN / 4; ++j)
-                mine[(i * (TN / 4) + j) * 256 + threadIdx.x] =
-                    make_float4(acc[i][j * 4], acc[i][j * 4 + 1], acc[i][j * 4 + 2], acc[i][j * 4 + 3]);
+                for (int j = 0; j < TN / 4; ++j)
+                    mine[(i * (TN / 4) + j) * 256 + tid] =
+                        make_float4(acc[i][j * 4], acc[i][j * 4 + 1], acc[i][j * 4 + 2], acc[i][j * 4 + 3]);
+        }
         __threadfence();
         __syncthreads();
         if (threadIdx.x == 0) {
@@ -163,7 +197,7 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(const GemmArgs g) {
             if (s_last) g.counters[tile] = 0;                     // ready for the next launch
         }
         __syncthreads();
-        if (!s_last) return;
+        if (!s_last || !owner) return;
         __threadfence();
 #pragma unroll
         for (int i = 0; i < TM; ++i)
@@ -176,13 +210,14 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(const GemmArgs g) {
             for (int i = 0; i < TM; ++i)
 #pragma unroll
                 for (int j = 0; j < TN / 4; ++j) {
-                    const float4 t = __ldcg(&p[(i * (TN / 4) + j) * 256 + threadIdx.x]);
+                    const float4 t = __ldcg(&p[(i * (TN / 4) + j) * 256 + tid]);
                     acc[i][j * 4] += t.x; acc[i][j * 4 + 1] += t.y; acc[i][j * 4 + 2] += t.z; acc[i][j * 4 + 3] += t.w;
                 }
         }
     }
 
     // ---- epilogue
+    if (!owner) return;
 #pragma unroll
     for (int i = 0; i < TM; ++i) {
         const int m = m0 + (i / 4) * (BM / (TM / 4)) + ty * 4 + (i % 4);
@@ -228,7 +263,7 @@ struct GemmPlan {
 };
 
 GemmPlan plan_gemm(int M, int N, int K, int sm_count) {
-    static const int kBM[3] = {128, 64, 64}, kBN[3] = {128, 128, 64};
+    static const int kBM[3] = {128, 64, 64}, kBN[3] = {128, 128, 64}, kKS[3] = {1, 1, 2};
     GemmPlan p{};
     int pick = 2;
     for (int c = 0; c < 3; ++c) {
@@ -249,8 +284,9 @@ GemmPlan plan_gemm(int M, int N, int K, int sm_count) {
         if (parts > max_parts) parts = max_parts;
         if (parts > 64) parts = 64;
     }
-    int chunk = ((K + parts - 1) / parts + GK - 1) / GK * GK;
-    if (chunk < GK) chunk = GK;
+    const int gks = GK * kKS[pick];
+    int chunk = ((K + parts - 1) / parts + gks - 1) / gks * gks;
+    if (chunk < gks) chunk = gks;
     p.k_chunk = chunk;
     p.parts = (K + chunk - 1) / chunk;
     if (p.parts < 1) p.parts = 1;
@@ -296,9 +332,9 @@ int launch_gemm_f32(deers_ctx* ctx, int M, int N, int K, const float* a, long lo
     const dim3 grid(p.tiles_n, p.tiles_m, p.parts);
     {
         KernelTimerScope ts(ctx, DEERS_K_GEMM);
-        if (p.cfg == 0) gemm_f32_kernel<128, 128, 8, 8><<<grid, 256, 0, ctx->stream>>>(g);
-        else if (p.cfg == 1) gemm_f32_kernel<64, 128, 4, 8><<<grid, 256, 0, ctx->stream>>>(g);
-        else gemm_f32_kernel<64, 64, 4, 4><<<grid, 256, 0, ctx->stream>>>(g);
+        if (p.cfg == 0) gemm_f32_kernel<128, 128, 8, 8, 1><<<grid, 256, 0, ctx->stream>>>(g);
+        else if (p.cfg == 1) gemm_f32_kernel<64, 128, 4, 8, 1><<<grid, 256, 0, ctx->stream>>>(g);
+        else gemm_f32_kernel<64, 64, 4, 4, 2><<<grid, 512, 0, ctx->stream>>>(g);
     }
     ctx->launches += 1;
     DEERS_CUDA_TRY(ctx, cudaGetLastError());

@@ -11,6 +11,9 @@
 // gradient added inside the RMSNorm backward, dQ / dK rotated back straight into the fused [N, 3C]
 // gradient buffer next to dV, and one GEMM each for d[Wq|Wk|Wv] and for the sum of the three input
 // gradients.  Every launch is one of this library's kernels; there is no host round trip in a step.
+// The weight gradients are off the critical path (nothing in the backward reads them): they run on a second
+// stream, forked from the main one where their operands are complete and joined before the gradient norm;
+// captured, the two streams become two branches of the step's graph.
 #include "common.cuh"
 
 #include <math.h>
@@ -51,7 +54,13 @@ struct deers_gpt {
     float *dx_a, *dx_b, *dtmp, *dh, *dqkv, *dqk, *attn_ws;
     size_t attn_ws_bytes;
     void* gemm_ws;
+    void* gemm_ws_side;          // split-K workspace of the weight-gradient stream
     size_t gemm_ws_bytes;
+    // second stream for the weight gradients; events are markers only (no timing)
+    cudaStream_t side;
+    cudaEvent_t ev_fork, ev_join, ev_done[4];
+    bool done_valid[4];          // ev_done[i] was recorded in the current backward pass
+    bool on_side;                // launches currently go to the side stream
     void* optim_scratch;
     float *loss_dev, *norm_dev;
     long long *ids_dev, *tgt_dev;
@@ -59,6 +68,7 @@ struct deers_gpt {
     bool tc_head;
     void *xf_hi, *xf_lo, *w_hi, *w_lo, *dl_hi, *dl_lo;
     void* x3_ws;
+    void* x3_ws_side;
     size_t x3_ws_bytes;
     // pinned staging for train_step_host
     long long* ids_pin;
@@ -81,8 +91,51 @@ namespace {
 int gemm(deers_gpt* m, int M, int N, int K, const float* a, long long lda, int a_mn, const float* b, long long ldb, int b_mn,
          float* c, long long ldc, int epi = DEERS_EPI_NONE, const float* r = nullptr, long long ldr = 0,
          float* aux = nullptr) {
-    return launch_gemm_f32(m->ctx, M, N, K, a, lda, a_mn, b, ldb, b_mn, c, ldc, epi, r, ldr, aux, m->gemm_ws,
-                           m->gemm_ws_bytes, true);
+    return launch_gemm_f32(m->ctx, M, N, K, a, lda, a_mn, b, ldb, b_mn, c, ldc, epi, r, ldr, aux,
+                           m->on_side ? m->gemm_ws_side : m->gemm_ws, m->gemm_ws_bytes, true);
+}
+
+// Launches made while a SideScope lives go to the weight-gradient stream, ordered after everything the main
+// stream holds at construction.  done(i) marks the side stream's progress for a later wait_done(i) on the
+// main stream (before it overwrites a buffer the side work reads).  With kernel timing on, or without a
+// second stream, everything stays on the main stream.
+struct SideScope {
+    deers_gpt* m;
+    cudaStream_t main;
+    bool active;
+    int rc;
+    explicit SideScope(deers_gpt* m_) : m(m_), main(m_->ctx->stream), active(m_->side && !m_->ctx->timing), rc(DEERS_OK) {
+        if (!active) return;
+        if (cudaEventRecord(m->ev_fork, main) != cudaSuccess || cudaStreamWaitEvent(m->side, m->ev_fork, 0) != cudaSuccess) {
+            rc = DEERS_ERR_CUDA;
+            active = false;
+            return;
+        }
+        m->ctx->stream = m->side;
+        m->on_side = true;
+    }
+    int done(int i) {
+        if (!active) return rc;
+        if (cudaEventRecord(m->ev_done[i], m->side) != cudaSuccess) return DEERS_ERR_CUDA;
+        m->done_valid[i] = true;
+        return DEERS_OK;
+    }
+    ~SideScope() {
+        if (active) { m->ctx->stream = main; m->on_side = false; }
+    }
+};
+
+int wait_done(deers_gpt* m, int i) {
+    if (!m->done_valid[i]) return DEERS_OK;
+    return cudaStreamWaitEvent(m->ctx->stream, m->ev_done[i], 0) == cudaSuccess ? DEERS_OK : DEERS_ERR_CUDA;
+}
+
+// The main stream waits for all side work enqueued so far.
+int join_side(deers_gpt* m) {
+    if (!m->side || m->ctx->timing) return DEERS_OK;
+    if (cudaEventRecord(m->ev_join, m->side) != cudaSuccess || cudaStreamWaitEvent(m->ctx->stream, m->ev_join, 0) != cudaSuccess)
+        return DEERS_ERR_CUDA;
+    return DEERS_OK;
 }
 
 void attn_desc(const deers_gpt* m, int B, int T, deers_attn_desc* d) {
@@ -160,20 +213,29 @@ int loss_and_backward(deers_gpt* m, const long long* ids, const long long* targe
     const int Vld = m->Vld;
     float* W = m->arena[0];
     float* G = m->arena[1];
+    for (bool& v : m->done_valid) v = false;
     GPT_TRY(launch_cross_entropy_fwd(ctx, m->logits, Vld, targets, N, V, m->ce_lse, m->picked, m->loss_dev));
     const float* x_last = c.n_layer ? m->la[c.n_layer - 1].x2 : m->x0;
     if (m->tc_head) {
         // dlogits leave the cross-entropy backward as f16 pairs scaled by rows * 4096 (|dlogit| <= 1 / rows)
         const float dscale = (float)N * 4096.0f;
         GPT_TRY(launch_cross_entropy_bwd_split(ctx, m->logits, Vld, targets, m->ce_lse, N, V, 1.0f, dscale, m->dl_hi, m->dl_lo, Vld));
-        GPT_TRY(launch_gemm_f16x3(ctx, C, V, (int)N, m->xf_hi, m->xf_lo, C, 1, m->dl_hi, m->dl_lo, Vld, 1, G + m->off_lm, Vld,
-                                  1.0f / dscale, m->x3_ws, m->x3_ws_bytes));                  // d lm_head = xf^T dlogits
         GPT_TRY(launch_gemm_f16x3(ctx, (int)N, C, V, m->dl_hi, m->dl_lo, Vld, 0, m->w_hi, m->w_lo, Vld, 0, m->dtmp, C,
                                   1.0f / dscale, m->x3_ws, m->x3_ws_bytes));                  // d xf = dlogits Wlm^T
+        {
+            SideScope side(m);
+            GPT_TRY(side.rc);
+            GPT_TRY(launch_gemm_f16x3(ctx, C, V, (int)N, m->xf_hi, m->xf_lo, C, 1, m->dl_hi, m->dl_lo, Vld, 1, G + m->off_lm, Vld,
+                                      1.0f / dscale, m->x3_ws_side, m->x3_ws_bytes));         // d lm_head = xf^T dlogits
+        }
     } else {
         GPT_TRY(launch_cross_entropy_bwd(ctx, m->logits, Vld, targets, m->ce_lse, N, V, 1.0f, m->logits, Vld));
-        GPT_TRY(gemm(m, C, V, (int)N, m->xf, C, 1, m->logits, Vld, 1, G + m->off_lm, Vld));      // d lm_head = xf^T dlogits
         GPT_TRY(gemm(m, (int)N, C, V, m->logits, Vld, 0, W + m->off_lm, Vld, 0, m->dtmp, C));    // d xf = dlogits Wlm^T
+        {
+            SideScope side(m);
+            GPT_TRY(side.rc);
+            GPT_TRY(gemm(m, C, V, (int)N, m->xf, C, 1, m->logits, Vld, 1, G + m->off_lm, Vld));  // d lm_head = xf^T dlogits
+        }
     }
     GPT_TRY(launch_rmsnorm_bwd(ctx, N, C, x_last, m->invf, m->dtmp, nullptr, m->dx_a));
     deers_attn_desc ad;
@@ -185,23 +247,47 @@ int loss_and_backward(deers_gpt* m, const long long* ids, const long long* targe
         LayerAct& a = m->la[l];
         const float* x_in = l ? m->la[l - 1].x2 : m->x0;
         // MLP branch: x2 = x1 + relu(n2 Wup)^2 Wdown
-        GPT_TRY(gemm(m, Hm, C, (int)N, a.h, Hm, 1, m->dx_a, C, 1, G + w.down, C));           // d Wdown = h^T dx
+        {
+            SideScope side(m);
+            GPT_TRY(side.rc);
+            GPT_TRY(gemm(m, Hm, C, (int)N, a.h, Hm, 1, m->dx_a, C, 1, G + w.down, C));       // d Wdown = h^T dx
+            GPT_TRY(side.done(0));
+        }
+        GPT_TRY(wait_done(m, 1));                                                            // the previous d Wup has read dh
         GPT_TRY(gemm(m, (int)N, Hm, C, m->dx_a, C, 0, W + w.down, C, 0, m->dh, Hm, DEERS_EPI_MUL_AUX2, nullptr, 0, a.r));
-        GPT_TRY(gemm(m, C, Hm, (int)N, a.n2, C, 1, m->dh, Hm, 1, G + w.up, Hm));             // d Wup = n2^T du
+        {
+            SideScope side(m);
+            GPT_TRY(side.rc);
+            GPT_TRY(gemm(m, C, Hm, (int)N, a.n2, C, 1, m->dh, Hm, 1, G + w.up, Hm));         // d Wup = n2^T du
+            GPT_TRY(side.done(1));
+        }
         GPT_TRY(gemm(m, (int)N, C, Hm, m->dh, Hm, 0, W + w.up, Hm, 0, m->dtmp, C));          // d n2 = du Wup^T
+        GPT_TRY(wait_done(m, 2));                                                            // the previous d Wout has read dx_b
         GPT_TRY(launch_rmsnorm_bwd(ctx, N, C, a.x1, a.inv2, m->dtmp, m->dx_a, m->dx_b));     // d x1
         // attention branch: x1 = x + attn(n1) Wout
-        GPT_TRY(gemm(m, C, C, (int)N, a.o, C, 1, m->dx_b, C, 1, G + w.out, C));              // d Wout = o^T dx1
+        {
+            SideScope side(m);
+            GPT_TRY(side.rc);
+            GPT_TRY(gemm(m, C, C, (int)N, a.o, C, 1, m->dx_b, C, 1, G + w.out, C));          // d Wout = o^T dx1
+            GPT_TRY(side.done(2));
+        }
         GPT_TRY(gemm(m, (int)N, C, C, m->dx_b, C, 0, W + w.out, C, 0, m->dtmp, C));          // d o (token-major)
+        GPT_TRY(wait_done(m, 3));                                                            // the previous d Wqkv has read dqkv
         GPT_TRY(deers_b200_attn_bwd(ctx, &ad, a.qk, a.qk + (size_t)H * T * D, a.qkv + 2 * C, a.o, a.lse, m->dtmp, m->dqk,
                                     m->dqk + (size_t)H * T * D, m->dqkv + 2 * C, m->attn_ws, m->attn_ws_bytes));
         GPT_TRY(deers_b200_rope_pack(ctx, &rd, m->dqk, m->cosv, m->sinv, m->dqkv));          // d q | d k back to [N, 3C]
-        GPT_TRY(gemm(m, C, 3 * C, (int)N, a.n1, C, 1, m->dqkv, 3 * C, 1, G + w.qkv, 3 * C)); // d [Wq|Wk|Wv]
+        {
+            SideScope side(m);
+            GPT_TRY(side.rc);
+            GPT_TRY(gemm(m, C, 3 * C, (int)N, a.n1, C, 1, m->dqkv, 3 * C, 1, G + w.qkv, 3 * C)); // d [Wq|Wk|Wv]
+            GPT_TRY(side.done(3));
+        }
         GPT_TRY(gemm(m, (int)N, C, 3 * C, m->dqkv, 3 * C, 0, W + w.qkv, 3 * C, 0, m->dtmp, C)); // d n1 (three terms in one)
+        GPT_TRY(wait_done(m, 0));                                                            // this layer's d Wdown has read dx_a
         GPT_TRY(launch_rmsnorm_bwd(ctx, N, C, x_in, a.inv1, m->dtmp, m->dx_b, m->dx_a));     // d x
     }
     GPT_TRY(launch_embedding_bwd(ctx, m->dx_a, ids, N, C, V, G + m->off_wte));
-    return DEERS_OK;
+    return join_side(m);
 }
 
 int grad_norm(deers_gpt* m) {
@@ -318,6 +404,17 @@ extern "C" int deers_b200_gpt_create(deers_ctx* ctx, const deers_gpt_config* cfg
     // Heads that fill the tensor core take the split-f16 products; small ones stay on the FFMA kernel.
     m->tc_head = cfg->vocab_size >= 1024 && cfg->n_embd % 8 == 0 && cfg->n_embd >= 64;
     m->graph_enabled = true; m->graph_exec = nullptr; m->graph_B = m->graph_T = -1; m->eager_steps_BT = 0;
+    m->on_side = false;
+    {
+        // the weight-gradient stream and its markers; without them the step simply runs on one stream
+        bool ok = cudaStreamCreateWithFlags(&m->side, cudaStreamNonBlocking) == cudaSuccess;
+        if (!ok) m->side = nullptr;
+        cudaEvent_t* evs[6] = {&m->ev_fork, &m->ev_join, &m->ev_done[0], &m->ev_done[1], &m->ev_done[2], &m->ev_done[3]};
+        for (cudaEvent_t* e : evs)
+            if (cudaEventCreateWithFlags(e, cudaEventDisableTiming) != cudaSuccess) { *e = nullptr; ok = false; }
+        if (!ok && m->side) { cudaStreamDestroy(m->side); m->side = nullptr; }
+        cudaGetLastError();
+    }
     const size_t C = cfg->n_embd, Hm = cfg->mlp_hidden_dim, V = cfg->vocab_size, N = (size_t)max_tokens;
 
     // ---- parameter-shaped arenas
@@ -397,8 +494,8 @@ extern "C" int deers_b200_gpt_create(deers_ctx* ctx, const deers_gpt_config* cfg
     // K-split partial tiles of the head's input gradient: parts * tokens <= 148 * 128 * 128 / C + tokens
     const size_t x3 = m->tc_head ? up256(((size_t)148 * 16384 + N * C) * sizeof(float) * 2) : 0;
     m->x3_ws_bytes = x3;
-    const size_t tc_bytes = m->tc_head ? 2 * (xf_h + w_h + dl_h) + x3 : 0;
-    const size_t bytes = total * sizeof(float) + gws + 256 + opt_bytes + 256 + 2 * id_bytes + tc_bytes;
+    const size_t tc_bytes = m->tc_head ? 2 * (xf_h + w_h + dl_h) + 2 * x3 : 0;
+    const size_t bytes = total * sizeof(float) + 2 * (gws + 256) + opt_bytes + 256 + 2 * id_bytes + tc_bytes;
     char* base = nullptr;
     if (!rc && cudaMalloc((void**)&base, bytes) != cudaSuccess) rc = DEERS_ERR_CUDA;
     if (!rc && cudaMemsetAsync(base, 0, bytes, ctx->stream) != cudaSuccess) rc = DEERS_ERR_CUDA;   // split-K counters start at zero
@@ -409,6 +506,7 @@ extern "C" int deers_b200_gpt_create(deers_ctx* ctx, const deers_gpt_config* cfg
         m->norm_dev = m->loss_dev + 1;
         char* q = (char*)p;
         m->gemm_ws = gws ? q : nullptr; q += (gws + 255) / 256 * 256;
+        m->gemm_ws_side = gws ? q : nullptr; q += (gws + 255) / 256 * 256;
         m->optim_scratch = q; q += (opt_bytes + 255) / 256 * 256;
         m->ids_dev = (long long*)q; q += id_bytes;
         m->tgt_dev = (long long*)q; q += id_bytes;
@@ -417,6 +515,7 @@ extern "C" int deers_b200_gpt_create(deers_ctx* ctx, const deers_gpt_config* cfg
             m->w_hi = q; q += w_h; m->w_lo = q; q += w_h;
             m->dl_hi = q; q += dl_h; m->dl_lo = q; q += dl_h;
             m->x3_ws = q; q += x3;
+            m->x3_ws_side = q; q += x3;
         }
         // rotary cache, f32 arithmetic of gpt.rs:12-46
         const int half = D / 2;
@@ -451,6 +550,12 @@ extern "C" void deers_b200_gpt_destroy(deers_gpt* m) {
     cudaSetDevice(m->ctx->device);
     cudaStreamSynchronize(m->ctx->stream);
     drop_graph(m);
+    if (m->side) { cudaStreamSynchronize(m->side); cudaStreamDestroy(m->side); }
+    {
+        cudaEvent_t evs[6] = {m->ev_fork, m->ev_join, m->ev_done[0], m->ev_done[1], m->ev_done[2], m->ev_done[3]};
+        for (cudaEvent_t e : evs)
+            if (e) cudaEventDestroy(e);
+    }
     for (int a = 0; a < 4; ++a)
         if (m->arena[a]) cudaFree(m->arena[a]);
     if (m->act_base) cudaFree(m->act_base);
