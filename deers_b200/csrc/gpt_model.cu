@@ -173,6 +173,14 @@ int forward(deers_gpt* m, const long long* ids, int B, int T) {
     const int C = c.n_embd, Hm = c.mlp_hidden_dim, V = c.vocab_size, H = c.n_head, D = m->D;
     const long long N = (long long)B * T;
     float* W = m->arena[0];
+    for (bool& v : m->done_valid) v = false;
+    if (m->tc_head) {
+        // the head weight's f16 pair (it changes every step) is made beside the blocks, not in front of the head
+        SideScope side(m);
+        GPT_TRY(side.rc);
+        GPT_TRY(launch_split_f16x3(ctx, C, V, W + m->off_lm, m->Vld, 1.0f, m->w_hi, m->w_lo, m->Vld));
+        GPT_TRY(side.done(0));
+    }
     GPT_TRY(launch_embedding_fwd(ctx, W + m->off_wte, ids, N, C, V, m->x0));                 // gpt.rs:343
     deers_attn_desc ad;
     attn_desc(m, B, T, &ad);
@@ -196,7 +204,7 @@ int forward(deers_gpt* m, const long long* ids, int B, int T) {
     if (m->tc_head) {
         // lm_head on the tensor core at f32 accuracy: both operands as f16 pairs (the weight changes every step)
         GPT_TRY(launch_split_f16x3(ctx, N, C, m->xf, C, 1.0f, m->xf_hi, m->xf_lo, C));
-        GPT_TRY(launch_split_f16x3(ctx, C, V, W + m->off_lm, m->Vld, 1.0f, m->w_hi, m->w_lo, m->Vld));
+        GPT_TRY(wait_done(m, 0));
         GPT_TRY(launch_gemm_f16x3(ctx, (int)N, V, C, m->xf_hi, m->xf_lo, C, 0, m->w_hi, m->w_lo, m->Vld, 1, m->logits, m->Vld,
                                   1.0f, m->x3_ws, m->x3_ws_bytes));
     } else {

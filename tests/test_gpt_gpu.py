@@ -328,6 +328,31 @@ def test_gpt_host_step_and_graph_toggle(cfg3_case):
     assert all(np.isfinite(v) for pair in runs[0] for v in pair)
 
 
+def test_gpt_two_stream_backward_equals_single_stream(cfg3_case):
+    """The weight gradients run on a second stream (a second branch of the captured graph).  With kernel timing
+    on, every launch stays on the main stream in program order: losses, gradients and updated weights of three
+    steps must be bitwise the same both ways, eager and replayed (a missed ordering edge between the branches
+    would show as a difference)."""
+    params, ids, tgt, _ = cfg3_case
+    outs = []
+    for single_stream in (False, True):
+        m = build_model(CFG3, 4, 256, params)
+        if single_stream:
+            m.ctx.kernel_timing(True)
+        losses = [m.train_step_host(ids, tgt, lr=5e-4, weight_decay=0.1, max_grad_norm=1.0) for _ in range(3)]
+        m.ctx.sync()
+        if single_stream:
+            m.ctx.kernel_timing(False)
+        else:
+            assert m.graph_active()
+        outs.append((losses, [m.grad(i) for i in range(m.num_parameters())], [m.parameter(i) for i in range(m.num_parameters())]))
+    assert outs[0][0] == outs[1][0]
+    for i, (g0, g1) in enumerate(zip(outs[0][1], outs[1][1])):
+        assert np.array_equal(g0, g1), i
+    for i, (w0, w1) in enumerate(zip(outs[0][2], outs[1][2])):
+        assert np.array_equal(w0, w1), i
+
+
 def test_gpt_rejects_bad_shapes():
     from deers_b200 import gpt
     from deers_b200.errors import CudaError
