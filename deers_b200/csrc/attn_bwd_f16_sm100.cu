@@ -1139,6 +1139,7 @@ int deers_b200_attn_bwd_f16_static(deers_ctx* ctx, const deers_attn_desc* d, con
     const int rc = deers_check_bwd_args(d, q, k, v, o, lse, d_o, dq, dk, dv);
     if (rc) return rc;
     if (d->dtype != DEERS_F16) return DEERS_ERR_DTYPE;
+    if (d->D != 64 && d->D != 128) return DEERS_ERR_UNSUPPORTED;      // the zero-padded path needs room for copies
     if (ctx->device < 0 || ctx->device >= 64) return DEERS_ERR_DEVICE;
     const size_t need = attn_bwd_f16_workspace_bytes(d, false);
     if (need > sizeof(float) * kStaticScratchFloats) {

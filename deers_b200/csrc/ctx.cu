@@ -302,7 +302,8 @@ int deers_check_desc(const deers_attn_desc* d) {
     if (d->dtype == DEERS_F32) {
         if (d->D > 128) return DEERS_ERR_SHAPE;
     } else {
-        if (d->D != 64 && d->D != 128) return DEERS_ERR_SHAPE;           // tcgen05 tile shapes
+        // tcgen05 tile shapes are 64 and 128; other multiples of 8 run zero-padded to the next of the two
+        if (d->D > 128 || d->D % 8 != 0) return DEERS_ERR_SHAPE;
     }
     if (!(d->scale == d->scale)) return DEERS_ERR_SHAPE;
     return DEERS_OK;
@@ -332,8 +333,69 @@ static size_t delta_bytes(const deers_attn_desc* d) {
     return align_up((size_t)d->B * d->H * d->T * sizeof(float), 256);
 }
 
+// ---------------------------------------------------------------------------
+// f16 head dims other than 64 / 128 (the reference derives head_dim = n_embd / n_head freely,
+// src/models/gpt.rs:86-100): operands are copied into dense [B,H,T,Dp] buffers, Dp = 64 or 128, with zero
+// columns behind D (zero columns change neither Q K^T nor P V), the native kernels run on those, and the first D
+// columns of the results are copied back.  A compatibility path: it costs one extra pass over every tensor.
+// ---------------------------------------------------------------------------
+static int padded_dim(const deers_attn_desc* d) { return d->D <= 64 ? 64 : 128; }
+static bool needs_pad(const deers_attn_desc* d) { return d->dtype == DEERS_F16 && d->D != 64 && d->D != 128; }
+static size_t padded_tensor_bytes(const deers_attn_desc* d) {
+    return align_up((size_t)d->B * d->H * d->T * padded_dim(d) * 2, 256);
+}
+static deers_attn_desc padded_desc(const deers_attn_desc* d) {
+    deers_attn_desc p = *d;
+    p.D = padded_dim(d);
+    const int64_t s[4] = {(int64_t)d->H * d->T * p.D, (int64_t)d->T * p.D, p.D, 1};
+    for (int i = 0; i < 4; ++i) {
+        p.q_strides[i] = p.k_strides[i] = p.v_strides[i] = p.o_strides[i] = p.do_strides[i] = s[i];
+        p.dq_strides[i] = p.dk_strides[i] = p.dv_strides[i] = s[i];
+    }
+    return p;
+}
+
+// One thread per 16-byte piece (8 halves) of a padded row.  TO_PADDED: strided [.., D] -> dense [.., DP] with
+// zero fill; otherwise dense [.., DP] -> strided [.., D].
+template <bool TO_PADDED>
+__global__ void __launch_bounds__(256) pad_rows_f16_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, int H, int T,
+                                                           int D8, int DP8, long long sb, long long sh, long long st,
+                                                           long long rows) {
+    const long long total = rows * DP8;
+    for (long long i = (long long)blockIdx.x * 256 + threadIdx.x; i < total; i += (long long)gridDim.x * 256) {
+        const long long row = i / DP8;
+        const int c = (int)(i % DP8);
+        const long long t = row % T, h = (row / T) % H, b = row / ((long long)T * H);
+        const long long strided = (b * sb + h * sh + t * st) / 8 + c;         // strides are multiples of 8 halves
+        if (TO_PADDED) dst[i] = c < D8 ? src[strided] : make_uint4(0u, 0u, 0u, 0u);
+        else if (c < D8) dst[strided] = src[i];
+    }
+}
+
+static int pad_copy(deers_ctx* ctx, const deers_attn_desc* d, const void* strided, const int64_t* s, void* dense, bool to_padded) {
+    const long long rows = (long long)d->B * d->H * d->T;
+    const int D8 = d->D / 8, DP8 = padded_dim(d) / 8;
+    long long want = (rows * DP8 + 255) / 256;
+    const long long cap = 32LL * ctx->sm_count;
+    const unsigned grid = (unsigned)(want < cap ? want : cap);
+    if (to_padded)
+        pad_rows_f16_kernel<true><<<grid, 256, 0, ctx->stream>>>((const uint4*)strided, (uint4*)dense, d->H, d->T, D8, DP8, s[0], s[1], s[2], rows);
+    else
+        pad_rows_f16_kernel<false><<<grid, 256, 0, ctx->stream>>>((const uint4*)dense, (uint4*)const_cast<void*>(strided), d->H, d->T, D8, DP8, s[0], s[1], s[2], rows);
+    ctx->launches += 1;
+    DEERS_CUDA_TRY(ctx, cudaGetLastError());
+    return DEERS_OK;
+}
+
 extern "C" size_t deers_b200_attn_workspace_bytes(const deers_attn_desc* d, int pass) {
-    if (deers_check_desc(d) != DEERS_OK || pass == 0) return 0;
+    if (deers_check_desc(d) != DEERS_OK) return 0;
+    if (needs_pad(d)) {
+        // pass 0: Q, K, V, O padded; passes 1, 2: the eight padded tensors of the backward + its own workspace
+        const deers_attn_desc p = padded_desc(d);
+        if (pass == 0) return 4 * padded_tensor_bytes(d);
+        return 8 * padded_tensor_bytes(d) + align_up(attn_bwd_f16_workspace_bytes(&p, pass >= 2), 256);
+    }
+    if (pass == 0) return 0;
     // pass 1: the least the backward needs; pass 2: what lets the f16 backward keep its dS tiles
     return d->dtype == DEERS_F16 ? attn_bwd_f16_workspace_bytes(d, pass >= 2) : delta_bytes(d);
 }
@@ -341,7 +403,6 @@ extern "C" size_t deers_b200_attn_workspace_bytes(const deers_attn_desc* d, int 
 extern "C" int deers_b200_attn_fwd(deers_ctx* ctx, const deers_attn_desc* d, const void* q,
                                    const void* k, const void* v, void* o, float* lse, void* workspace,
                                    size_t workspace_bytes) {
-    (void)workspace; (void)workspace_bytes;
     if (!ctx) return DEERS_ERR_NULL;
     int rc = deers_check_desc(d);
     if (rc) return rc;
@@ -354,6 +415,17 @@ extern "C" int deers_b200_attn_fwd(deers_ctx* ctx, const deers_attn_desc* d, con
     DEERS_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
     if (d->dtype == DEERS_F32)
         return launch_attn_fwd_f32(ctx, d, (const float*)q, (const float*)k, (const float*)v, (float*)o, lse);
+    if (needs_pad(d)) {
+        const size_t tb = padded_tensor_bytes(d);
+        if (!workspace || workspace_bytes < 4 * tb || ((uintptr_t)workspace & 255u) != 0) return DEERS_ERR_WORKSPACE;
+        char* w = (char*)workspace;
+        const deers_attn_desc p = padded_desc(d);
+        if ((rc = pad_copy(ctx, d, q, d->q_strides, w, true))) return rc;
+        if ((rc = pad_copy(ctx, d, k, d->k_strides, w + tb, true))) return rc;
+        if ((rc = pad_copy(ctx, d, v, d->v_strides, w + 2 * tb, true))) return rc;
+        if ((rc = launch_attn_fwd_f16(ctx, &p, w, w + tb, w + 2 * tb, w + 3 * tb, lse))) return rc;
+        return pad_copy(ctx, d, o, d->o_strides, w + 3 * tb, false);
+    }
     return launch_attn_fwd_f16(ctx, d, q, k, v, o, lse);
 }
 
@@ -373,6 +445,23 @@ extern "C" int deers_b200_attn_bwd(deers_ctx* ctx, const deers_attn_desc* d, con
                                    (const float*)o, lse, (const float*)d_o, (float*)dq, (float*)dk,
                                    (float*)dv, (float*)workspace);
     const bool keep_ds = workspace_bytes >= deers_b200_attn_workspace_bytes(d, 2);
+    if (needs_pad(d)) {
+        const size_t tb = padded_tensor_bytes(d);
+        char* w = (char*)workspace;
+        const deers_attn_desc p = padded_desc(d);
+        const void* in[5] = {q, k, v, o, d_o};
+        const int64_t* in_s[5] = {d->q_strides, d->k_strides, d->v_strides, d->o_strides, d->do_strides};
+        for (int i = 0; i < 5; ++i)
+            if ((rc = pad_copy(ctx, d, in[i], in_s[i], w + i * tb, true))) return rc;
+        if ((rc = launch_attn_bwd_f16(ctx, &p, w, w + tb, w + 2 * tb, w + 3 * tb, lse, w + 4 * tb, w + 5 * tb, w + 6 * tb,
+                                      w + 7 * tb, w + 8 * tb, keep_ds)))
+            return rc;
+        void* out[3] = {dq, dk, dv};
+        const int64_t* out_s[3] = {d->dq_strides, d->dk_strides, d->dv_strides};
+        for (int i = 0; i < 3; ++i)
+            if ((rc = pad_copy(ctx, d, out[i], out_s[i], w + (5 + i) * tb, false))) return rc;
+        return DEERS_OK;
+    }
     return launch_attn_bwd_f16(ctx, d, q, k, v, o, lse, d_o, dq, dk, dv, workspace, keep_ds);
 }
 
@@ -460,6 +549,7 @@ extern "C" int deers_b200_attn_fwd_bwd_host(deers_ctx* ctx, const deers_attn_des
     if (!ctx || !q_host || !k_host || !v_host || !do_host || !o_host || !dq_host || !dk_host || !dv_host) return DEERS_ERR_NULL;
     int rc = deers_check_desc(d);
     if (rc) return rc;
+    if (needs_pad(d)) return DEERS_ERR_UNSUPPORTED;                   // f16 head dims other than 64 / 128: device calls only
     if (chunk_slices < 1) return DEERS_ERR_SHAPE;
     const size_t need = deers_b200_attn_host_scratch_bytes(d, chunk_slices);
     if (!device_scratch || scratch_bytes < need || ((uintptr_t)device_scratch & 255u) != 0) return DEERS_ERR_WORKSPACE;

@@ -203,8 +203,11 @@ public:
         const auto& s = q_.layout().shape;
         lse_ = std::make_shared<CudaStorage>((size_t)(s[0] * s[1] * s[2]) * sizeof(float), DType::F32);
         deers_attn_desc d = desc(out_layout);
+        // scratch only for f16 head dims other than 64 / 128 (zero-padded copies)
+        const size_t fwd_ws = deers_b200_attn_workspace_bytes(&d, 0);
+        std::shared_ptr<CudaStorage> ws = fwd_ws ? std::make_shared<CudaStorage>(fwd_ws, DType::F32) : nullptr;
         rt.check(deers_b200_attn_fwd(rt.ctx(), &d, q_.storage().ptr(), k_.storage().ptr(), v_.storage().ptr(), o->ptr(),
-                                     (float*)lse_->ptr(), nullptr, 0));
+                                     (float*)lse_->ptr(), ws ? ws->ptr() : nullptr, fwd_ws));
         o_ = Tensor(o, out_layout);                                     // kept for the backward, like LogSumExp.lse
         return Tensor(o, out_layout, shared_from_this());
     }

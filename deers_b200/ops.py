@@ -161,8 +161,12 @@ def attention_fwd(q, k, v, scale: float, causal: bool = True, token_major_out: b
         o = torch.empty(q.shape, dtype=q.dtype, device=q.device)
     lse = torch.empty(q.shape[:3], dtype=torch.float32, device=q.device)
     d = _desc(q, k, v, o, scale=scale, causal=causal)
+    # The forward needs scratch only for f16 head dims other than 64 / 128 (zero-padded copies of Q, K, V, O).
+    need = int(_lib.lib().deers_b200_attn_workspace_bytes(ctypes.byref(d), 0))
+    ws = torch.empty(need, dtype=torch.uint8, device=q.device) if need else None
     _lib.check(_lib.lib().deers_b200_attn_fwd(ctx.handle, ctypes.byref(d), q.data_ptr(), k.data_ptr(),
-                                              v.data_ptr(), o.data_ptr(), lse.data_ptr(), None, 0), ctx.handle)
+                                              v.data_ptr(), o.data_ptr(), lse.data_ptr(),
+                                              ws.data_ptr() if need else None, need), ctx.handle)
     return o, lse
 
 

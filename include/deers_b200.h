@@ -119,7 +119,10 @@ int deers_b200_sync(deers_ctx* ctx);
 
 /*
  * Scratch memory a pass needs (pass 0 = forward, 1 = backward, 2 = fast backward), in bytes.
- * Forward needs none.  Backward keeps rowsum(dO * O) per row (and, for f16, the
+ * Forward needs none, except for f16 head dims other than 64 and 128: the tensor-core tiles are 64 or 128
+ * wide, the reference derives head_dim = n_embd / n_head freely (`src/models/gpt.rs:86-100`), so any
+ * multiple of 8 up to 128 is accepted and runs on zero-padded copies kept in the workspace (four tensors of
+ * B*H*T*Dp halves forward, eight more bytes-wise for the backward; Dp = 64 or 128).  Backward keeps rowsum(dO * O) per row (and, for f16, the
  * row lse in log2 units), padded to whole tiles.  The reference allocates the equivalent temporaries
  * inside each op (`src/storage/cuda.rs:637-644`; its backward also keeps the whole [B,H,T,T]
  * probability tensor alive from the forward, `src/ops.rs:1162-1175`).
@@ -138,6 +141,8 @@ size_t deers_b200_attn_workspace_bytes(const deers_attn_desc* desc, int pass);
  * `:613-648`, causal_mask + Broadcast + EWiseAdd, softmax `src/tensor.rs:408-458`,
  * MatMul) — the storage-level hook is a new `BackendStorage::attention_fwd` added
  * the way `log_softmax_fwd` was (`src/storage.rs:284-302,379-418`).
+ * `workspace` (256-byte aligned, deers_b200_attn_workspace_bytes(desc, 0) bytes) may be NULL when that size
+ * is 0; DEERS_ERR_WORKSPACE otherwise.
  */
 int deers_b200_attn_fwd(deers_ctx* ctx, const deers_attn_desc* desc, const void* q, const void* k,
                         const void* v, void* o, float* lse, void* workspace, size_t workspace_bytes);

@@ -70,6 +70,34 @@ def test_forward_rescale_path():
     assert_close(lse.cpu().numpy(), want_lse, TOL_F16, "lse")
 
 
+@pytest.mark.parametrize("shape", [
+    (2, 3, 300, 32),     # the reference GPT's head_dim (n_embd 192 / 6 heads) in f16
+    (1, 2, 130, 16),
+    (1, 2, 257, 96),     # padded to 128
+    (1, 1, 64, 8),
+])
+def test_head_dims_other_than_64_and_128(shape):
+    """The reference derives head_dim = n_embd / n_head freely (src/models/gpt.rs:86-100).  f16 head dims that
+    are not a tensor-core tile width run on zero-padded copies: forward and backward against the oracle, and
+    the workspace sizes the padded path asks for."""
+    from deers_b200 import ops
+    from tests.gpu_util import check_case
+    check_case(*shape, torch.float16, TOL_F16, seed=sum(shape))
+    q = torch.empty(shape, dtype=torch.float16, device="cuda")
+    rows_bytes = shape[0] * shape[1] * shape[2] * (64 if shape[3] <= 64 else 128) * 2
+    assert ops.workspace_bytes(q, pass_=0) >= 4 * rows_bytes
+    assert ops.workspace_bytes(q, pass_=1) >= 8 * rows_bytes
+    assert ops.workspace_bytes(torch.empty((1, 1, 128, 64), dtype=torch.float16, device="cuda"), pass_=0) == 0
+
+
+def test_head_dim_not_a_multiple_of_8_is_refused():
+    from deers_b200 import ops
+    from deers_b200.errors import DeersError
+    q = torch.zeros((1, 1, 64, 20), dtype=torch.float16, device="cuda")
+    with pytest.raises(DeersError):
+        ops.attention_fwd(q, q, q, 0.2)
+
+
 def test_cfg2_forward_backward():
     # BASELINE config 2: f16, B=8, T=1024, H=12, head_dim=64; every slice checked.
     from tests.gpu_util import check_case
