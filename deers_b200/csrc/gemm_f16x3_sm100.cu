@@ -30,6 +30,11 @@ constexpr uint32_t X_SMEM = X_STAGES * X_STAGE + 256;
 constexpr uint32_t X_MN_BLOCK = XK * 128;          // 8 KB: 64 K-rows x 64 columns of an MN-major operand
 constexpr float X_LO = 1.0f / 2048.0f;
 
+// warp 0 TMA, warp 1 MMA, then two epilogue warpgroups that each take half of a tile's columns: with one, the
+// head's forward product waits on its epilogue (206 MB of logits through 4 warps per SM), not on the tensor pipe
+constexpr int X_EPI_WG = 2;
+constexpr int X_THREADS = 64 + 128 * X_EPI_WG;
+
 enum XBar { X_FULL = 0, X_EMPTY = 3, X_ACC_FULL = 6, X_ACC_EMPTY = 8, X_COUNT = 10 };
 
 struct X3Params {
@@ -43,7 +48,7 @@ struct X3Params {
 };
 
 template <int A_MN, int B_MN>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(X_THREADS, 1)
 gemm_f16x3_kernel(const __grid_constant__ CUtensorMap tm_ah, const __grid_constant__ CUtensorMap tm_al,
                   const __grid_constant__ CUtensorMap tm_bh, const __grid_constant__ CUtensorMap tm_bl, const X3Params p) {
     extern __shared__ __align__(1024) uint8_t smem[];
@@ -65,7 +70,7 @@ gemm_f16x3_kernel(const __grid_constant__ CUtensorMap tm_ah, const __grid_consta
         }
         *skip_s = skip;
         for (int s = 0; s < X_STAGES; ++s) { mbar_init(&bars[X_FULL + s], 1); mbar_init(&bars[X_EMPTY + s], 1); }
-        for (int s = 0; s < 2; ++s) { mbar_init(&bars[X_ACC_FULL + s], 1); mbar_init(&bars[X_ACC_EMPTY + s], 128); }
+        for (int s = 0; s < 2; ++s) { mbar_init(&bars[X_ACC_FULL + s], 1); mbar_init(&bars[X_ACC_EMPTY + s], 128 * X_EPI_WG); }
         fence_barrier_init();
         tma_prefetch_desc(&tm_ah); tma_prefetch_desc(&tm_al); tma_prefetch_desc(&tm_bh); tma_prefetch_desc(&tm_bl);
     }
@@ -169,6 +174,8 @@ gemm_f16x3_kernel(const __grid_constant__ CUtensorMap tm_ah, const __grid_consta
         // ------------------------------ epilogue ------------------------------
         const int lane_base = (warp & 3) * 32;
         const uint32_t t_lane = (uint32_t)lane_base << 16;
+        const int ewg = (warp - 2) >> 2;                         // which share of the columns
+        constexpr int CHUNKS = XN / 32 / X_EPI_WG;
         int n = 0;
         for (int u = blockIdx.x; u < n_units; u += gridDim.x, ++n) {
             int tm, tn, kb0, kb1;
@@ -180,12 +187,12 @@ gemm_f16x3_kernel(const __grid_constant__ CUtensorMap tm_ah, const __grid_consta
             float* cbase = p.c + (p.parts > 1 ? (long long)part * p.M * p.ldc : 0);
             const int row0 = tm * XM + lane_base + (lane & ~7);
 #pragma unroll 1
-            for (int chunk = 0; chunk < XN / 32; ++chunk) {      // 32 columns at a time
+            for (int chunk = ewg * CHUNKS; chunk < (ewg + 1) * CHUNKS; ++chunk) {      // 32 columns at a time
                 uint32_t rm[32], rc[32];
                 tmem_ld_x32(tmem + buf * 256u + t_lane + chunk * 32, rm);
                 tmem_ld_x32(tmem + buf * 256u + 128u + t_lane + chunk * 32, rc);
                 tmem_wait_ld();
-                if (chunk == XN / 32 - 1) {                      // both accumulators are in registers
+                if (chunk == (ewg + 1) * CHUNKS - 1) {           // this warpgroup's share of both accumulators is in registers
                     tc_fence_before_sync();
                     mbar_arrive(&bars[X_ACC_EMPTY + buf]);
                 }
@@ -297,7 +304,7 @@ X3Plan x3_plan(int M, int N, int K, int sm_count) {
     const long long tiles = (long long)((M + XM - 1) / XM) * ((N + XN - 1) / XN);
     X3Plan pl{1, (K + XK - 1) / XK * XK};
     if (tiles < sm_count) {
-        int parts = (int)((sm_count + tiles - 1) / tiles);
+        int parts = (int)(sm_count / tiles);                          // all (tile, part) units in one wave of CTAs
         const int kblocks = (K + XK - 1) / XK;
         const int max_parts = kblocks / 8 > 1 ? kblocks / 8 : 1;      // at least eight K blocks per part
         if (parts > max_parts) parts = max_parts;
@@ -314,7 +321,7 @@ int x3_launch(deers_ctx* ctx, const CUtensorMap* t, const X3Params& p, unsigned 
     DEERS_CUDA_TRY(ctx, cudaFuncSetAttribute(gemm_f16x3_kernel<A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)X_SMEM));
     {
         KernelTimerScope ts(ctx, DEERS_K_GEMM_X3);
-        gemm_f16x3_kernel<A_MN, B_MN><<<grid, 192, X_SMEM, ctx->stream>>>(t[0], t[1], t[2], t[3], p);
+        gemm_f16x3_kernel<A_MN, B_MN><<<grid, X_THREADS, X_SMEM, ctx->stream>>>(t[0], t[1], t[2], t[3], p);
     }
     ctx->launches += 1;
     DEERS_CUDA_TRY(ctx, cudaGetLastError());
