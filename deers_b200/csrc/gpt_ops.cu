@@ -7,7 +7,7 @@
 //                   with atomics (scatter order undefined); here the first occurrence of a token id
 //                   owns the row and adds the later occurrences in order, so the result is reproducible
 //                   and equals the CPU backend's left-to-right sum.
-//   cross_entropy   one block per row reads the logits once (online max / sum of exponentials),
+//   cross_entropy   one block per row reads the logits once (running maximum / sum of exponentials),
 //                   writes lse[row] and the picked log-probability; a one-block kernel adds the rows in a
 //                   fixed order: loss = sum * (float)(-1/rows).
 //   cross_entropy_bwd  dlogits = (onehot * g - softmax * g) * upstream, g = (float)(-1/rows): the chain
@@ -84,44 +84,49 @@ __global__ void __launch_bounds__(256) embedding_bwd_kernel(const float* __restr
     }
 }
 
-__device__ __forceinline__ void online_merge(float& m, float& s, float m2, float s2) {
-    const float mx = fmaxf(m, m2);
-    if (mx == -INFINITY) { s = 0.f; m = mx; return; }
-    s = s * __expf(m - mx) + s2 * __expf(m2 - mx);
-    m = mx;
+// Row logsumexp + picked log-probability (src/storage/cpu.rs:759-770 computes the maximum first and then the
+// sum of expf(x - max); the same value up to f32 rounding of a different summation order).
+// Merges two (maximum, sum of exponentials relative to it) pairs.
+__device__ __forceinline__ void lse_merge(float& m, float& s, float m2, float s2) {
+    const float M = fmaxf(m, m2);
+    if (M == -INFINITY) { s = 0.f; return; }                      // both parts empty
+    s = s * expf(m - M) + s2 * expf(m2 - M);
+    m = M;
 }
 
-// Row logsumexp + picked log-probability.  Two sweeps over the row (it stays in L2 between them): the
-// maximum first, then the sum of expf(x - max), the order of operations of src/storage/cpu.rs:759-770.
+// One pass over the row: every thread keeps a running maximum and the sum of exponentials relative to it (the
+// sum is rescaled when the maximum grows), four values at a time when the row is 16-byte aligned; the 256 pairs
+// are merged at the end.  A two-pass version (maximum, then sum) read the 206 MB of logits twice from DRAM.
 __global__ void __launch_bounds__(256) cross_entropy_fwd_kernel(const float* __restrict__ logits, long long ld,
                                                                 const long long* __restrict__ targets, long long V,
                                                                 float* __restrict__ lse, float* __restrict__ picked,
                                                                 unsigned int* err) {
-    __shared__ float red[8];
+    __shared__ float red_m[8], red_s[8];
     const long long row = blockIdx.x;
     const float* x = logits + row * ld;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    float m = -INFINITY;
-    for (long long j = threadIdx.x; j < V; j += 256) m = fmaxf(m, x[j]);
+    float m = -INFINITY, s = 0.f;
+    const bool vec = (((uintptr_t)x) & 15u) == 0;
+    const long long V4 = vec ? V / 4 : 0;
+    for (long long j = threadIdx.x; j < V4; j += 256) {
+        const float4 v = *reinterpret_cast<const float4*>(x + 4 * j);
+        const float vm = fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w));
+        if (vm > m) { s *= expf(m - vm); m = vm; }                // m = -inf at first: s = 0 * 0
+        s += expf(v.x - m) + expf(v.y - m) + expf(v.z - m) + expf(v.w - m);
+    }
+    for (long long j = 4 * V4 + threadIdx.x; j < V; j += 256) {
+        const float v = x[j];
+        if (v > m) { s *= expf(m - v); m = v; }
+        s += expf(v - m);
+    }
 #pragma unroll
-    for (int off = 16; off >= 1; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
-    if (lane == 0) red[warp] = m;
-    __syncthreads();
-    m = red[0];
-#pragma unroll
-    for (int w = 1; w < 8; ++w) m = fmaxf(m, red[w]);
-    __syncthreads();
-    float s = 0.f;
-    for (long long j = threadIdx.x; j < V; j += 256) s += expf(x[j] - m);
-#pragma unroll
-    for (int off = 16; off >= 1; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-    if (lane == 0) red[warp] = s;
+    for (int off = 16; off >= 1; off >>= 1)
+        lse_merge(m, s, __shfl_xor_sync(0xffffffffu, m, off), __shfl_xor_sync(0xffffffffu, s, off));
+    if (lane == 0) { red_m[warp] = m; red_s[warp] = s; }
     __syncthreads();
     if (threadIdx.x == 0) {
-        float tot = 0.f;
-#pragma unroll
-        for (int w = 0; w < 8; ++w) tot += red[w];
-        const float l = logf(tot) + m;
+        for (int w = 1; w < 8; ++w) lse_merge(m, s, red_m[w], red_s[w]);
+        const float l = logf(s) + m;
         lse[row] = l;
         const long long t = targets[row];
         if (t < 0 || t >= V) {
@@ -133,7 +138,6 @@ __global__ void __launch_bounds__(256) cross_entropy_fwd_kernel(const float* __r
     }
 }
 
-// loss = (sum of picked in a fixed tree order) * (float)(-1/rows)
 __global__ void __launch_bounds__(1024) cross_entropy_loss_kernel(const float* __restrict__ picked, long long rows,
                                                                   float neg_inv_rows, float* __restrict__ loss) {
     __shared__ float red[32];
