@@ -793,14 +793,20 @@ def run_gpt_step(args):
         tc_peak = peaks["tflops_burst" if at_max_clock else "tflops_sustained"]
         head = {"bound": "tensor", "kernel": "gemm_f16x3_kernel + split / reduce (lm_head forward, wgrad, dgrad)",
                 "achieved": head_flops / (head_ms * 1e-3) / 1e12 if head_ms else None, "peak": tc_peak, "unit": "TFLOP/s",
-                "frac": (head_flops / (head_ms * 1e-3) / 1e12 / tc_peak) if head_ms else None, "traffic": None,
+                "frac": (head_flops / (head_ms * 1e-3) / 1e12 / tc_peak) if head_ms else None,
+                # DRAM bytes per step of the three products, the two splits and the reduction, from the ncu capture of
+                # this very workload (profiles/gpt_step_cfg3_kernels.md); None at other model sizes
+                "traffic": 725.0e6 if (n_tok, C_, V_) == (1024, 192, 50257) else None,
                 "flops_per_step": head_flops, "kernel_ms_per_step": head_ms,
                 "note": "algorithmic f32 FLOPs; the kernel executes three f16 products per f32 product",
                 "peak_source": f"{peaks['source']} {'burst' if at_max_clock else 'sustained'} bf16"}
         block = {"bound": "fp32 FFMA pipe (the reference computes these products in full f32, CUBLAS_COMPUTE_32F)",
                  "kernel": "gemm_f32_kernel (the 72 Linear forward / dgrad / wgrad products of the blocks)",
                  "achieved": block_flops / (block_ms * 1e-3) / 1e12 if block_ms else None, "peak": ffma_peak, "unit": "TFLOP/s",
-                 "frac": (block_flops / (block_ms * 1e-3) / 1e12 / ffma_peak) if block_ms else None, "traffic": None,
+                 "frac": (block_flops / (block_ms * 1e-3) / 1e12 / ffma_peak) if block_ms else None,
+                 # DRAM bytes per step: 72 launches x 2.24 MB, the mean of the four forward shapes captured by ncu at this
+                 # workload (operands and results live in L2; profiles/gpt_step_cfg3_kernels.md); None at other sizes
+                 "traffic": 161.0e6 if (n_tok, C_, Hm_, c["n_layer"]) == (1024, 192, 768, 6) else None,
                  "flops_per_step": block_flops, "kernel_ms_per_step": block_ms,
                  "peak_source": f"148 SMs x 128 FFMA lanes x 2 x {sm_max:.0f} MHz (nominal; MEASURED_PEAKS.json holds no f32 figure)"}
         roofline = dict(head if head_ms >= block_ms else block)
@@ -1120,10 +1126,10 @@ def main():
         if dtype == "f16":
             achieved = dkdv_flops / (bwd_avg * 1e-3) / 1e12
             # DRAM traffic of this kernel from an ncu capture of a small case (the 128 slices of B=8, H=16 at
-            # T=2048, D=128: 914.2 MB when it also writes the dS tiles, 376.0 MB when it does not; summaries
+            # T=2048, D=128: 922.3 MB when it also writes the dS tiles, 376.0 MB when it does not; summaries
             # under profiles/), scaled by the slices one launch processes; traffic is proportional to the
             # slice count.
-            per128 = 376.0e6 if args.bwd == "recompute" else 914.2e6
+            per128 = 376.0e6 if args.bwd == "recompute" else 922.3e6
             traffic = per128 / 128 * n_local if (T == 2048 and D == 128) else None
             roofline = {"bound": "tensor", "kernel": "attn_bwd_dkdv_f16_kernel", "achieved": achieved, "peak": peak,
                         "unit": UNIT, "frac": achieved / peak, "traffic": traffic,
