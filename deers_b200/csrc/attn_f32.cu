@@ -55,6 +55,46 @@ __device__ __forceinline__ void load_tile(float* __restrict__ dst, const float* 
     }
 }
 
+// The same tile in two halves, global -> registers (fetch) and registers -> shared memory (put), so that the
+// next tile of a walk is in flight while the current one is multiplied.  Used for head dims up to 64 (two or
+// four float4 per thread and tile); at 128 the kernels have no registers to spare and load in place.
+template <int DP>
+struct TileRegs {
+    static constexpr int C4 = DP / 4;
+    static constexpr int NV = BM * C4 / NT;
+    float4 v[NV];
+    __device__ __forceinline__ void fetch(const float* __restrict__ src, int row0, int T, int D, long long st, int vec) {
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int idx = threadIdx.x + i * NT;
+            const int r = idx / C4, c = (idx % C4) * 4;
+            const int row = row0 + r;
+            float4 val = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (row < T) {
+                const float* p = src + (long long)row * st + c;
+                if (vec) {
+                    if (c < D) val = *reinterpret_cast<const float4*>(p);
+                } else {
+                    if (c + 0 < D) val.x = p[0];
+                    if (c + 1 < D) val.y = p[1];
+                    if (c + 2 < D) val.z = p[2];
+                    if (c + 3 < D) val.w = p[3];
+                }
+            }
+            v[i] = val;
+        }
+    }
+    __device__ __forceinline__ void put(float* __restrict__ dst) const {
+        constexpr int LD = DP + 4;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int idx = threadIdx.x + i * NT;
+            *reinterpret_cast<float4*>(dst + (idx / C4) * LD + (idx % C4) * 4) = v[i];
+        }
+    }
+};
+__host__ __device__ constexpr bool prefetch_tiles(int DP) { return DP <= 64; }
+
 // s[r][c] = sum_d A[ty*4+r][d] * Bm[tx+16c][d] for two [64][DP+4] shared tiles.
 template <int DP>
 __device__ __forceinline__ void tile_nt(const float* __restrict__ A, const float* __restrict__ Bm,
@@ -176,11 +216,24 @@ __global__ void __launch_bounds__(NT) attn_fwd_f32_kernel(const F32Params p) {
     const float sl2 = p.scale * LOG2E;
     const int last = p.causal ? qt : (p.T + BN - 1) / BN - 1;
 
+    TileRegs<prefetch_tiles(DP) ? DP : 16> kr, vr;     // unused (and tiny) when the tiles are loaded in place
+    if constexpr (prefetch_tiles(DP)) {
+        kr.fetch(kb, 0, p.T, p.D, p.sk.t, p.vec);
+        vr.fetch(vb, 0, p.T, p.D, p.sv.t, p.vec);
+    }
     for (int j = 0; j <= last; ++j) {
         const int k0 = j * BN;
         __syncthreads();                       // previous tile fully consumed (and Q visible)
-        load_tile<DP>(Ks, kb, k0, p.T, p.D, p.sk.t, p.vec);
-        load_tile<DP>(Vs, vb, k0, p.T, p.D, p.sv.t, p.vec);
+        if constexpr (prefetch_tiles(DP)) {
+            kr.put(Ks); vr.put(Vs);
+            if (j < last) {                    // the next tile travels while this one is multiplied
+                kr.fetch(kb, k0 + BN, p.T, p.D, p.sk.t, p.vec);
+                vr.fetch(vb, k0 + BN, p.T, p.D, p.sv.t, p.vec);
+            }
+        } else {
+            load_tile<DP>(Ks, kb, k0, p.T, p.D, p.sk.t, p.vec);
+            load_tile<DP>(Vs, vb, k0, p.T, p.D, p.sv.t, p.vec);
+        }
         __syncthreads();
 
         float s[4][4];
@@ -313,11 +366,27 @@ __device__ __forceinline__ void attn_bwd_dkdv_f32_body(const F32Params& p, float
 
     const float* qb = p.q + b * p.sq.b + h * p.sq.h;
     const float* gb = p.d_o + b * p.sdo.b + h * p.sdo.h;
-    for (int i = p.causal ? kt : 0; i < nq; ++i) {
+    const int i_first = p.causal ? kt : 0;
+    TileRegs<prefetch_tiles(DP) ? DP : 16> qr, gr;
+    if constexpr (prefetch_tiles(DP)) {
+        if (i_first < nq) {
+            qr.fetch(qb, i_first * BM, p.T, p.D, p.sq.t, p.vec);
+            gr.fetch(gb, i_first * BM, p.T, p.D, p.sdo.t, p.vec);
+        }
+    }
+    for (int i = i_first; i < nq; ++i) {
         const int q0 = i * BM;
         __syncthreads();
-        load_tile<DP>(Qs, qb, q0, p.T, p.D, p.sq.t, p.vec);
-        load_tile<DP>(dOs, gb, q0, p.T, p.D, p.sdo.t, p.vec);
+        if constexpr (prefetch_tiles(DP)) {
+            qr.put(Qs); gr.put(dOs);
+            if (i + 1 < nq) {
+                qr.fetch(qb, q0 + BM, p.T, p.D, p.sq.t, p.vec);
+                gr.fetch(gb, q0 + BM, p.T, p.D, p.sdo.t, p.vec);
+            }
+        } else {
+            load_tile<DP>(Qs, qb, q0, p.T, p.D, p.sq.t, p.vec);
+            load_tile<DP>(dOs, gb, q0, p.T, p.D, p.sdo.t, p.vec);
+        }
         if (threadIdx.x < BM) {
             const int row = q0 + threadIdx.x;
             lse_s[threadIdx.x] = row < p.T ? p.lse[(long long)bh * p.T + row] : 0.f;
@@ -394,11 +463,24 @@ __device__ __forceinline__ void attn_bwd_dq_f32_body(const F32Params& p, float* 
     const float* kb = p.k + b * p.sk.b + h * p.sk.h;
     const float* vb = p.v + b * p.sv.b + h * p.sv.h;
     const int last = p.causal ? qt : (p.T + BN - 1) / BN - 1;
+    TileRegs<prefetch_tiles(DP) ? DP : 16> kr, vr;
+    if constexpr (prefetch_tiles(DP)) {
+        kr.fetch(kb, 0, p.T, p.D, p.sk.t, p.vec);
+        vr.fetch(vb, 0, p.T, p.D, p.sv.t, p.vec);
+    }
     for (int j = 0; j <= last; ++j) {
         const int k0 = j * BN;
         __syncthreads();
-        load_tile<DP>(Ks, kb, k0, p.T, p.D, p.sk.t, p.vec);
-        load_tile<DP>(Vs, vb, k0, p.T, p.D, p.sv.t, p.vec);
+        if constexpr (prefetch_tiles(DP)) {
+            kr.put(Ks); vr.put(Vs);
+            if (j < last) {
+                kr.fetch(kb, k0 + BN, p.T, p.D, p.sk.t, p.vec);
+                vr.fetch(vb, k0 + BN, p.T, p.D, p.sv.t, p.vec);
+            }
+        } else {
+            load_tile<DP>(Ks, kb, k0, p.T, p.D, p.sk.t, p.vec);
+            load_tile<DP>(Vs, vb, k0, p.T, p.D, p.sv.t, p.vec);
+        }
         __syncthreads();
         float pp[4][4], ds[4][4];
         recompute_p_ds<DP>(p, Qs, Ks, dOs, Vs, lse_s, delta_s, q0, k0, ty, tx, pp, ds);
