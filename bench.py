@@ -961,16 +961,22 @@ def main():
     ws_bytes = ops.workspace_bytes(q, scale, pass_=1 if args.bwd == "recompute" else 2)
     workspace = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=dev)
     nccl_gather = shard.OverlappedGather(n_total, T, D, tdtype, dev) if world > 1 else None
-    peer_gather, peer_error = None, None
+    # Two gather buffers, used by alternate steps: the pushes of step i then have until the end of step i + 1
+    # (whose forward writes the other buffer) to leave, a whole step instead of one backward.  At 8 GPUs a rank
+    # sends 7/8 of a GB per step, which takes longer than its backward.
+    peer_gather, peer_gather_b, peer_error = None, None, None
     if world > 1:
         try:
             peer_gather = shard.PeerGather(n_total, T, D, tdtype, dev, ctx)
+            peer_gather_b = shard.PeerGather(n_total, T, D, tdtype, dev, ctx)
         except Exception as err:                             # peer mappings unavailable on this box: say so, use NCCL
             peer_error = f"{type(err).__name__}: {err}"
-        ok = torch.tensor([1 if peer_gather is not None else 0], device=dev)
+        ok = torch.tensor([1 if peer_gather_b is not None else 0], device=dev)
         dist.all_reduce(ok, op=dist.ReduceOp.MIN)            # all ranks take the same path
         if int(ok.item()) == 0:
-            peer_gather = None
+            peer_gather = peer_gather_b = None
+    peer_pair = (peer_gather, peer_gather_b)
+    step_no = [0]
     gather_mode = args.gather if world > 1 else "none"
     if gather_mode == "peer" and peer_gather is None:
         gather_mode = "nccl"
@@ -978,16 +984,18 @@ def main():
     def step(mode=None):
         mode = gather_mode if mode is None else mode
         if mode == "peer":
-            # the forward writes this rank's O straight into its slices of the gather buffer
-            o, lse = ops.attention_fwd(q, k, v, scale, True, out=peer_gather.local().view(Bs, Hs, T, D))
-            peer_gather.start()                              # pushes run on the copy engines under the backward
+            # the forward writes this rank's O straight into its slices of this step's gather buffer
+            pg, pg_prev = peer_pair[step_no[0] & 1], peer_pair[(step_no[0] & 1) ^ 1]
+            step_no[0] += 1
+            o, lse = ops.attention_fwd(q, k, v, scale, True, out=pg.local().view(Bs, Hs, T, D))
+            pg.start()                                       # pushes run on the copy engines under the following kernels
         else:
             o, lse = ops.attention_fwd(q, k, v, scale, True)
             if mode == "nccl":
                 nccl_gather.start(o)
         grads = ops.attention_bwd(q, k, v, o, lse, do, scale, True, workspace=workspace)
         if mode == "peer":
-            peer_gather.join()                               # the step ends when this rank's pushes have left
+            pg_prev.join()                                   # the previous step's pushes have left: its buffer is free again
         elif mode == "nccl":
             nccl_gather.finish()
         return o, grads
@@ -1011,6 +1019,9 @@ def main():
         a.record()
         for _ in range(steps or args.steps):
             step(mode)
+        if (gather_mode if mode is None else mode) == "peer":
+            for pg in peer_pair:                             # every push of the block ends inside the timed region
+                pg.join()
         b_.record()
         barrier()
         t = torch.tensor([a.elapsed_time(b_) / (steps or args.steps)], device=dev, dtype=torch.float64)
@@ -1168,7 +1179,7 @@ def main():
                 "config": {"workload": workload_name(args.workload, dtype, B, T, H, D),
                            "flops_per_step": total_flops, "flop_convention": "7*B*H*T^2*D (causal fwd 2, bwd 5)",
                            "parallelism": f"(b x h) shards over {world} GPU(s), {n_local} slices on rank 0",
-                           "gather": ({"peer": "all-gather of O inside the timed step: copy-engine pushes (deers_b200_allgather_o), overlapping the backward",
+                           "gather": ({"peer": "all-gather of O inside the timed step: copy-engine pushes (deers_b200_allgather_o) from two alternating buffers, overlapping the backward and the next forward; all pushes of a block are joined before its closing timestamp",
                                        "nccl": "all-gather of O inside the timed step: NCCL on a side stream, overlapping the backward",
                                        "none": "none (compute only)"}[gather_mode] if world > 1 else "n/a (1 GPU)"),
                            "gather_probe": gather_probe,
