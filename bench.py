@@ -854,7 +854,7 @@ def main():
     ap.add_argument("--shape", default=None, help="B,T,H,D: a custom shape (profiling captures on a small case)")
     ap.add_argument("--dtype", default=None, choices=["f16", "f32"], help="dtype for --shape")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--gather", default="peer", choices=["peer", "nccl", "none"],
+    ap.add_argument("--gather", default="auto", choices=["auto", "peer", "nccl", "none"],
                     help="N>1: the all-gather of O that the sharded workload names, inside the timed step.  peer "
                          "(default): the C ABI's copy-engine pushes into every rank's buffer, started after the forward "
                          "and overlapping the backward; nccl: a library all-gather on a side stream; none: O stays "
@@ -978,8 +978,9 @@ def main():
     peer_pair = (peer_gather, peer_gather_b)
     step_no = [0]
     gather_mode = args.gather if world > 1 else "none"
-    if gather_mode == "peer" and peer_gather is None:
+    if gather_mode in ("peer", "auto") and peer_gather is None:
         gather_mode = "nccl"
+    gather_choice = None                                     # filled in by --gather auto
 
     def step(mode=None):
         mode = gather_mode if mode is None else mode
@@ -1006,6 +1007,9 @@ def main():
         torch.cuda.synchronize()
 
     sampler = ClockSampler(local) if rank == 0 else None     # started early: nvidia-smi needs a moment
+    auto_gather = gather_mode == "auto"
+    if auto_gather:
+        gather_mode = "peer"                                 # warm up on the peer path; the choice follows below
     for _ in range(args.warmup):
         step()
     barrier()
@@ -1029,6 +1033,23 @@ def main():
             dist.all_reduce(t, op=dist.ReduceOp.MAX)         # max over ranks
         return float(t.item())
 
+    if auto_gather:
+        # Which all-gather of O rides best beside the kernels depends on the number of GPUs: the copy-engine pushes
+        # with all of a rank's world - 1 pushes in flight, two at a time or one after the other, or the library
+        # all-gather.  Each candidate runs three short blocks of the same step; the quickest one is then timed.
+        candidates = [("peer", lanes) for lanes in sorted({1, min(2, world - 1), world - 1})] + [("nccl", None)]
+        results = {}
+        for mode, lanes in candidates:
+            if lanes:
+                for pg in peer_pair:
+                    pg.set_lanes(lanes)
+            results[mode + (f"_lanes{lanes}" if lanes else "")] = statistics.median([timed_block(mode, 5) for _ in range(3)])
+        picked = min(results, key=results.get)               # the same on every rank: the times are maxima over ranks
+        gather_mode = "nccl" if picked == "nccl" else "peer"
+        if gather_mode == "peer":
+            for pg in peer_pair:
+                pg.set_lanes(int(picked.split("lanes")[1]))
+        gather_choice = {"step_ms": results, "picked": picked}
     first = timed_block()
     n_blocks = int(min(400, max(3, round(2000.0 / max(first * args.steps, 1e-3)))))
     launches0 = ctx.launch_count()
@@ -1182,6 +1203,7 @@ def main():
                            "gather": ({"peer": "all-gather of O inside the timed step: copy-engine pushes (deers_b200_allgather_o) from two alternating buffers, overlapping the backward and the next forward; all pushes of a block are joined before its closing timestamp",
                                        "nccl": "all-gather of O inside the timed step: NCCL on a side stream, overlapping the backward",
                                        "none": "none (compute only)"}[gather_mode] if world > 1 else "n/a (1 GPU)"),
+                           "gather_choice": gather_choice,
                            "gather_probe": gather_probe,
                            "timing": f"median of {n_blocks} blocks of {args.steps} steps ({sum(blocks) * args.steps / 1e3:.2f} s of device time), max over ranks per block",
                            "ms_x_median_sm_mhz": (ms_max * clocks["sm_mhz"]) if clocks and clocks.get("sm_mhz") else None,

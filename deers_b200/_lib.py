@@ -32,7 +32,7 @@ SYMBOLS = [
     "deers_b200_gpt_forward",
     "deers_b200_gpt_forward_backward", "deers_b200_gpt_train_step", "deers_b200_gpt_train_step_host",
     "deers_b200_shard_range", "deers_b200_comm_init_all", "deers_b200_comm_export", "deers_b200_comm_init_ipc",
-    "deers_b200_comm_destroy", "deers_b200_allgather_o", "deers_b200_allgather_join", "deers_b200_allgather_flush",
+    "deers_b200_comm_destroy", "deers_b200_comm_set_lanes", "deers_b200_allgather_o", "deers_b200_allgather_join", "deers_b200_allgather_flush",
     "deers_b200_selftest_wait", "deers_b200_split_f16x3", "deers_b200_gemm_f16x3_workspace_bytes", "deers_b200_gemm_f16x3",
 ]
 IPC_HANDLE_BYTES = 72
@@ -173,6 +173,7 @@ def lib() -> ctypes.CDLL:
     L.deers_b200_comm_destroy.argtypes = [vp]
     L.deers_b200_comm_destroy.restype = None
     L.deers_b200_allgather_o.argtypes = [vp, sz, sz]
+    L.deers_b200_comm_set_lanes.argtypes = [vp, i32]
     L.deers_b200_allgather_join.argtypes = [vp]
     L.deers_b200_allgather_flush.argtypes = [vp]
     L.deers_b200_status_string.argtypes = [i32]

@@ -139,6 +139,11 @@ class PeerGather:
         _lib.check(_lib.lib().deers_b200_allgather_o(self.handle, (self.begin + first) * self.slice_bytes,
                                                      count * self.slice_bytes), self.ctx.handle)
 
+    def set_lanes(self, lanes: int) -> None:
+        """How many of the world - 1 pushes of a `start()` are in flight at once (default: one)."""
+        from . import _lib
+        _lib.check(_lib.lib().deers_b200_comm_set_lanes(self.handle, int(lanes)), self.ctx.handle)
+
     def join(self) -> None:
         from . import _lib
         _lib.check(_lib.lib().deers_b200_allgather_join(self.handle), self.ctx.handle)

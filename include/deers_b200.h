@@ -509,6 +509,9 @@ int deers_b200_gpt_train_step_host(deers_gpt* model, const int64_t* ids_host, co
  *                   copy per peer over NVLink, each on its own stream, ordered after the work already enqueued on
  *                   the context's stream.  The copies run on the copy engines and take no SM from the kernels that
  *                   follow (the persistent backward kernels want one CTA on every SM).  Returns at once.
+ *   comm_set_lanes  how many of a call's world - 1 pushes are in flight at once (1 .. world - 1; default 1).  The
+ *                   pushes are dealt round-robin onto that many copy streams; with one lane they leave one after the
+ *                   other, each with the whole link, in an order in which no two ranks send to the same GPU at a time.
  *   allgather_join  makes the context's stream wait for this rank's pushes (no host wait).
  *   allgather_flush host-side wait for this rank's pushes.  A peer's slices are complete in this rank's buffer once
  *                   THAT peer's pushes have finished: exchange that fact on the host (the transport that carried the
@@ -524,6 +527,7 @@ int deers_b200_comm_export(deers_ctx* ctx, void* buffer, unsigned char* handle);
 int deers_b200_comm_init_ipc(deers_ctx* ctx, int32_t rank, int32_t world, void* local_buffer, size_t bytes,
                              const unsigned char* handles, deers_comm** out);
 void deers_b200_comm_destroy(deers_comm* comm);
+int deers_b200_comm_set_lanes(deers_comm* comm, int32_t lanes);
 int deers_b200_allgather_o(deers_comm* comm, size_t offset, size_t bytes);
 int deers_b200_allgather_join(deers_comm* comm);
 int deers_b200_allgather_flush(deers_comm* comm);

@@ -53,9 +53,17 @@ def test_workspace_bytes():
     assert L.deers_b200_attn_workspace_bytes(ctypes.byref(d), 1) >= 4 * 6 * 256 * 4
     L.deers_b200_attn_desc_compact(ctypes.byref(d), 8, 12, 1024, 64, _lib.F16, 1, 0.125)
     assert L.deers_b200_attn_workspace_bytes(ctypes.byref(d), 1) >= 8 * 12 * 1024 * 4
-    # Unsupported requests need no workspace because they are rejected.
+    # f16 head dims other than 64 / 128 (multiples of 8) run zero-padded: the forward needs four padded tensors,
+    # the backward eight more bytes-wise plus its own scratch.
     L.deers_b200_attn_desc_compact(ctypes.byref(d), 1, 1, 16, 48, _lib.F16, 1, 1.0)
-    assert L.deers_b200_attn_workspace_bytes(ctypes.byref(d), 1) == 0
+    padded = 1 * 1 * 16 * 64 * 2
+    assert L.deers_b200_attn_workspace_bytes(ctypes.byref(d), 0) >= 4 * padded
+    assert L.deers_b200_attn_workspace_bytes(ctypes.byref(d), 1) >= 8 * padded
+    # Unsupported requests need no workspace because they are rejected.
+    for bad in (20, 136):
+        L.deers_b200_attn_desc_compact(ctypes.byref(d), 1, 1, 16, bad, _lib.F16, 1, 1.0)
+        assert L.deers_b200_attn_workspace_bytes(ctypes.byref(d), 0) == 0
+        assert L.deers_b200_attn_workspace_bytes(ctypes.byref(d), 1) == 0
 
 
 def test_null_arguments_are_rejected_not_crashed():
