@@ -977,12 +977,7 @@ def main():
             peer_gather = peer_gather_b = None
     peer_pair = (peer_gather, peer_gather_b)
     step_no = [0]
-    # With one push in flight per rank the rotation only avoids two ranks sending to the same GPU while the ranks
-    # are in phase; nothing else in this workload couples them, and over a 20-step block they drift apart.  A
-    # 4-byte all-reduce between the forward and the pushes (what the gradient all-reduce of a training step does
-    # anyway) brings them back into phase every step.
-    align = [False]
-    align_word = torch.zeros(1, device=dev) if world > 1 else None
+
     gather_mode = args.gather if world > 1 else "none"
     if gather_mode in ("peer", "auto") and peer_gather is None:
         gather_mode = "nccl"
@@ -995,8 +990,6 @@ def main():
             pg, pg_prev = peer_pair[step_no[0] & 1], peer_pair[(step_no[0] & 1) ^ 1]
             step_no[0] += 1
             o, lse = ops.attention_fwd(q, k, v, scale, True, out=pg.local().view(Bs, Hs, T, D))
-            if align[0]:
-                dist.all_reduce(align_word)
             pg.start()                                       # pushes run on the copy engines under the following kernels
         else:
             o, lse = ops.attention_fwd(q, k, v, scale, True)
@@ -1043,24 +1036,20 @@ def main():
 
     if auto_gather:
         # Which all-gather of O rides best beside the kernels depends on the number of GPUs: the copy-engine pushes
-        # with all of a rank's world - 1 pushes in flight, two at a time or one after the other, or the library
-        # all-gather.  Each candidate runs three short blocks of the same step; the quickest one is then timed.
-        candidates = [("peer", lanes, False) for lanes in sorted({1, world - 1})]
-        if world > 2:
-            candidates.append(("peer", 1, True))
-        candidates.append(("nccl", None, False))
+        # one after the other or all of a rank's world - 1 at once, or the library all-gather.  Each candidate runs
+        # five blocks of the same step; the quickest one is then timed.
+        candidates = [("peer", lanes) for lanes in sorted({1, world - 1})] + [("nccl", None)]
         results, setting = {}, {}
-        for mode, lanes, aligned in candidates:
+        for mode, lanes in candidates:
             if lanes:
                 for pg in peer_pair:
                     pg.set_lanes(lanes)
-            align[0] = aligned
-            name = mode + (f"_lanes{lanes}" if lanes else "") + ("_aligned" if aligned else "")
-            # whole blocks, like the timed ones: ranks that nothing couples drift apart only over many steps
+            name = mode + (f"_lanes{lanes}" if lanes else "")
+            # whole blocks, like the timed ones: the first few steps of a gather run faster than its steady state
             results[name] = statistics.median([timed_block(mode) for _ in range(5)])
-            setting[name] = (mode, lanes, aligned)
+            setting[name] = (mode, lanes)
         picked = min(results, key=results.get)               # the same on every rank: the times are maxima over ranks
-        gather_mode, lanes, align[0] = setting[picked]
+        gather_mode, lanes = setting[picked]
         if lanes:
             for pg in peer_pair:
                 pg.set_lanes(lanes)
@@ -1215,8 +1204,7 @@ def main():
                 "config": {"workload": workload_name(args.workload, dtype, B, T, H, D),
                            "flops_per_step": total_flops, "flop_convention": "7*B*H*T^2*D (causal fwd 2, bwd 5)",
                            "parallelism": f"(b x h) shards over {world} GPU(s), {n_local} slices on rank 0",
-                           "gather": ({"peer": "all-gather of O inside the timed step: copy-engine pushes (deers_b200_allgather_o) from two alternating buffers, overlapping the backward and the next forward; all pushes of a block are joined before its closing timestamp"
-                                               + ("; a 4-byte all-reduce per step keeps the ranks' pushes in phase" if align[0] else ""),
+                           "gather": ({"peer": "all-gather of O inside the timed step: copy-engine pushes (deers_b200_allgather_o) from two alternating buffers, overlapping the backward and the next forward; all pushes of a block are joined before its closing timestamp",
                                        "nccl": "all-gather of O inside the timed step: NCCL on a side stream, overlapping the backward",
                                        "none": "none (compute only)"}[gather_mode] if world > 1 else "n/a (1 GPU)"),
                            "gather_choice": gather_choice,
