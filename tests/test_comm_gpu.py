@@ -26,7 +26,7 @@ def test_single_process_comm_init_all_gathers_byte_ranges():
     """deers_b200_comm_init_all: one process, one context per GPU; every rank pushes its byte range."""
     from deers_b200 import _lib
     L = _lib.lib()
-    n, nbytes = 2, 1 << 20
+    n, nbytes = min(torch.cuda.device_count(), 4), 1 << 20
     ctxs, bufs = [], []
     for g in range(n):
         h = ctypes.c_void_p()
@@ -44,6 +44,8 @@ def test_single_process_comm_init_all_gathers_byte_ranges():
         bufs[g][g * half:(g + 1) * half] = g + 1            # each rank fills only its own range
         torch.cuda.synchronize(g)
     for g in range(n):
+        if g % 2:
+            _lib.check(L.deers_b200_comm_set_lanes(comms[g], n), ctxs[g])      # clamped to n - 1: all pushes at once
         _lib.check(L.deers_b200_allgather_o(comms[g], g * half, half), ctxs[g])
     for g in range(n):
         _lib.check(L.deers_b200_allgather_flush(comms[g]), ctxs[g])
@@ -79,7 +81,9 @@ def _worker(rank, world, port, result_dir):
         got = gather.wait_all()
         torch.cuda.synchronize()
         assert torch.equal(got, full_o.view(B * H, T, D)), "gathered O must equal the unsharded O bit for bit"
-        # a second round with other values: the buffers and mappings are reused
+        # a second round with other values: the buffers and mappings are reused; this time with every push in
+        # flight at once instead of one after the other
+        gather.set_lanes(world - 1)
         gather.local().fill_(float(rank + 1))
         gather.start()
         got = gather.wait_all()
@@ -98,6 +102,6 @@ def _worker(rank, world, port, result_dir):
 def test_two_process_peer_gather_equals_unsharded_forward(tmp_path):
     """One process per GPU: handles exchanged over the process group, O pushed by the copy engines."""
     import torch.multiprocessing as mp
-    world = 2
+    world = min(torch.cuda.device_count(), 4)                # more than two ranks exercise the push rotation
     mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
     assert all((tmp_path / f"ok{r}").exists() for r in range(world))
